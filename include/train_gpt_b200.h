@@ -1,0 +1,157 @@
+/* train_gpt_b200 -- C ABI of the B200 (sm_100a) kernels behind train-gpt's FP8
+ * hot path.  Every entry point takes plain device pointers, sizes and a CUDA
+ * stream (passed as void*; NULL = the legacy default stream), launches
+ * asynchronously on that stream and returns an int status:
+ *
+ *     0  TG_OK
+ *    -1  TG_ERR_SHAPE      a size or stride the kernel cannot take (see each call)
+ *    -2  TG_ERR_ALIGN      a pointer or row pitch is not 16-byte aligned
+ *    -3  TG_ERR_ARCH       the current device is not compute capability 10.x
+ *    -4  TG_ERR_CUDA       a CUDA runtime/driver call failed (see tg_last_cuda_error)
+ *    -5  TG_ERR_TOO_LARGE  a size beyond a stated fixed maximum
+ *
+ * The caller owns every buffer, including scratch.  No entry point allocates
+ * device memory, synchronises the device, or throws across the boundary.  All
+ * matrices are row-major and dense unless a leading dimension is passed.
+ *
+ * "e4m3" is float8_e4m3fn (1-4-3, bias 7, max 448, no infinities), one byte per
+ * element.  Scales are float32 and always equal max(amax/448, 1e-30) of their
+ * tile, with amax taken over |x| after the upcast of the bf16 input to float32,
+ * and q = RNE_e4m3(x / scale) with a true (IEEE) division -- train-gpt fp8.py:39-47.
+ *
+ * "Reference" below is ammar1510/train-gpt; citations are file:line in that tree.
+ */
+#ifndef TRAIN_GPT_B200_H_
+#define TRAIN_GPT_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TG_OK 0
+#define TG_ERR_SHAPE (-1)
+#define TG_ERR_ALIGN (-2)
+#define TG_ERR_ARCH (-3)
+#define TG_ERR_CUDA (-4)
+#define TG_ERR_TOO_LARGE (-5)
+
+/* Library version (major*100 + minor). */
+int tg_version(void);
+
+/* Text of the last CUDA error a launcher of this library saw on the calling thread
+ * ("" if none).  The pointer stays valid until the next failing call on that thread. */
+const char* tg_last_cuda_error(void);
+
+/* ---- quantisers ------------------------------------------------------------------- */
+
+/* Replaces `_quantize_to_fp8(x_f32, 128)` as called on the activation at fp8.py:66
+ * (body fp8.py:39-47): tiles of 1 x 128 along the last axis.
+ *   x       [rows, cols] bf16          cols % 128 == 0
+ *   q       [rows, cols] e4m3
+ *   scales  [rows, cols/128] float32                                                  */
+int tg_quantize_rowwise(const void* x, void* q, float* scales,
+                        int64_t rows, int64_t cols, void* stream);
+
+/* Replaces `_quantize_to_fp8(b.T, 128)` at fp8.py:68 without materialising b.T: tiles
+ * of 128 rows x 1 column of x as stored.  q keeps x's layout; the scales come out
+ * as [ceil(rows/128), cols] (the transpose of the reference's (N, K/128) array).  A
+ * ragged last row block takes amax over the rows that exist.
+ *   x [rows, cols] bf16, cols % 8 == 0;  q [rows, cols] e4m3;
+ *   scales [ceil(rows/128), cols] float32                                             */
+int tg_quantize_colwise(const void* x, void* q, float* scales,
+                        int64_t rows, int64_t cols, void* stream);
+
+/* Tiles of 128 x 128, one scale per tile: the weight granularity the benchmark
+ * configurations name (the reference itself uses tg_quantize_colwise's).  Same scale
+ * rule, fp8.py:43-46.
+ *   x [rows, cols] bf16, cols % 128 == 0;  q [rows, cols] e4m3;
+ *   scales [ceil(rows/128), cols/128] float32                                         */
+int tg_quantize_block128(const void* x, void* q, float* scales,
+                         int64_t rows, int64_t cols, void* stream);
+
+/* ---- RMSNorm ---------------------------------------------------------------------- */
+
+/* mode for the norm entry points */
+#define TG_NORM_FUSED 0 /* kernels.py:44-53: bf16(f32(x) * rsqrt(var+eps) * f32(gamma)), one rounding */
+#define TG_NORM_PURE 1  /* kernels.py:30-33: rsqrt rounded to bf16, two bf16 multiplies              */
+
+/* Replaces `rms_norm(x, scale, eps)` (kernels.py:55-99, variance pass :66 included)
+ * or `_rms_norm_pure` (kernels.py:30-33), chosen by `mode`, in ONE pass over x.
+ *   x [rows, cols] bf16, gamma [cols] bf16, y [rows, cols] bf16, cols % 8 == 0,
+ *   cols <= 8192.  rnorm (may be NULL) [rows] float32 receives rsqrt(var+eps).        */
+int tg_rmsnorm_fwd(const void* x, const void* gamma, float eps, void* y, float* rnorm,
+                   int64_t rows, int64_t cols, int mode, void* stream);
+
+/* The composition the reference runs between a norm and the GEMM that consumes it --
+ * rms_norm (model.py:76-77, kernels.py:44-53) -> upcast (fp8.py:66) -> quantise
+ * (fp8.py:39-47) -- as one kernel: x is read once, the normalised value is rounded to
+ * bf16 exactly as the reference's norm output is, then quantised per 1 x 128 tile.
+ *   x [rows, cols] bf16, gamma [cols] bf16, cols % 128 == 0, cols <= 8192
+ *   q [rows, cols] e4m3, scales [rows, cols/128] float32
+ *   y     (may be NULL) [rows, cols] bf16: the norm output itself
+ *   rnorm (may be NULL) [rows] float32                                                */
+int tg_rmsnorm_quant_fwd(const void* x, const void* gamma, float eps, void* q, float* scales,
+                         void* y, float* rnorm, int64_t rows, int64_t cols, int mode,
+                         void* stream);
+
+/* Bytes of scratch tg_rmsnorm_bwd needs for a [rows, cols] problem (float32 partial
+ * column sums, one row of `cols` per thread block). */
+int64_t tg_rmsnorm_bwd_scratch_bytes(int64_t rows, int64_t cols);
+
+/* Replaces the custom-VJP `_bwd` of the norm (kernels.py:104-118): recomputes var and
+ * rnorm from x, returns dx = bf16(rnorm * (g*gamma - normed * mean(g*gamma*normed)))
+ * and dgamma = bf16(sum_rows g * normed).
+ *   x, g, dx [rows, cols] bf16; gamma, dgamma [cols] bf16; cols % 8 == 0, cols <= 8192
+ *   scratch: tg_rmsnorm_bwd_scratch_bytes(rows, cols) bytes, 16-byte aligned, contents
+ *   undefined on entry and exit.  Deterministic (no atomics).                         */
+int tg_rmsnorm_bwd(const void* x, const void* gamma, const void* g, float eps, void* dx,
+                   void* dgamma, void* scratch, int64_t rows, int64_t cols, void* stream);
+
+/* ---- block-scaled FP8 GEMM -------------------------------------------------------- */
+
+/* Operand storage, seen from the GEMM  D[m,n] = sum_k A[m,k] * B[n,k]. */
+#define TG_MAJOR_K 0  /* the operand is stored [m or n][k], k contiguous  */
+#define TG_MAJOR_MN 1 /* the operand is stored [k][m or n], m/n contiguous */
+
+#define TG_OUT_BF16 0
+#define TG_OUT_F32 1
+
+typedef struct tg_gemm_args {
+  /* D[m,n] = sum_kb SA(m,kb) * SB(n,kb) * sum_{k in block kb} A[m,k] * B[n,k]
+   * with 128-element contraction blocks, e4m3 operands, float32 accumulation.        */
+  const void* a;    /* e4m3; [M, K] if a_major == TG_MAJOR_K else [K, M]               */
+  const void* b;    /* e4m3; [N, K] if b_major == TG_MAJOR_K else [K, N]               */
+  int64_t lda, ldb; /* row pitch of a / b in elements (bytes); multiple of 16          */
+  int a_major, b_major;
+  const float* sa;  /* SA(m,kb) = sa[m*sa_stride_m + kb*sa_stride_kb]                  */
+  int64_t sa_stride_m, sa_stride_kb;
+  const float* sb;  /* SB(n,kb) = sb[(n/sb_gran_n)*sb_stride_n + kb*sb_stride_kb]      */
+  int64_t sb_stride_n, sb_stride_kb;
+  int sb_gran_n;    /* 1 (a scale per column n) or 128 (a scale per 128 columns)       */
+  void* d;          /* [M, N] bf16 or float32                                          */
+  int64_t ldd;      /* row pitch of d in elements; multiple of 8                       */
+  int out_dtype;    /* TG_OUT_BF16 / TG_OUT_F32                                        */
+  int64_t M, N, K;  /* K = contraction length; a ragged K (K % 128 != 0) is allowed
+                       only for MN-major operands whose scales were made by
+                       tg_quantize_colwise over the same ragged length                 */
+  uint32_t* status; /* device word, must be 0 on entry; a kernel whose bounded wait on
+                       a copy or MMA barrier runs out stores a non-zero code here and
+                       returns (results are then invalid).  May be NULL.              */
+} tg_gemm_args;
+
+/* Replaces `jax.nn.scaled_matmul` as called at fp8.py:70-76 (lhs (M,K), rhs (N,K),
+ * scales per 128 of K) followed by the bf16 cast of fp8.py:78 -- and, with other
+ * operand orders, the two backward GEMMs of fp8.py:96-97 in FP8:
+ *   forward  y  = x W      A = x_q  [M,K] K-major,  B = W_q [K,N] MN-major
+ *   dgrad    dx = g W^T    A = g_q  [M,N] K-major,  B = W_q [K,N] K-major (contracts N)
+ *   wgrad    dW = x^T g    A = x_q  [T,K] MN-major, B = g_q [T,N] MN-major (contracts T)
+ * No operand is transposed in memory: the TMA descriptors and the tcgen05 operand
+ * descriptors carry the orientation.                                                 */
+int tg_gemm_fp8_blockscaled(const tg_gemm_args* args, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TRAIN_GPT_B200_H_ */

@@ -1,0 +1,127 @@
+"""Bit-exact parity of the CUDA quantisers with the CPU oracle (bytes and scales)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import fp8_oracle as fo
+from tests.gpu_util import BF16, f8_bytes, normal_bf16, to_torch_bf16
+
+pytestmark = pytest.mark.gpu
+
+
+def _awkward(rng, shape):
+    x = normal_bf16(rng, shape, outlier_p=0.01).astype(np.float32)
+    if shape[0] > 6 and shape[1] >= 256:
+        x[3, 128:256] = 0.0          # all-zero tile -> scale 1e-30, bytes 0
+        x[4, 0:128] = 1e-36          # amax/448 under the floor
+        x[5, -128:] *= 1e-20
+        x[6, 7] = -0.0
+    return x.astype(BF16)
+
+
+def _bits(a):
+    return np.ascontiguousarray(a).view(np.uint32)
+
+
+def test_rowwise_matches_reference_vectors(golden):
+    from train_gpt_b200 import ops
+    x = np.asarray(golden["q_act_in"]).view(BF16)
+    q, s = ops.quantize_rowwise(to_torch_bf16(x))
+    assert np.array_equal(f8_bytes(q), golden["q_act_bytes"])
+    assert np.array_equal(_bits(s.cpu().numpy()), _bits(golden["q_act_scales"]))
+
+
+@pytest.mark.parametrize("shape", [(1, 128), (7, 384), (300, 1024), (4096, 768), (1000, 2048)])
+def test_rowwise_bit_exact(shape):
+    from train_gpt_b200 import ops
+    rng = np.random.default_rng(hash(shape) % 2**32)
+    x = _awkward(rng, shape)
+    q, s = ops.quantize_rowwise(to_torch_bf16(x))
+    q_ref, s_ref = fo.quantize_to_fp8(x.astype(np.float32))
+    assert np.array_equal(f8_bytes(q), q_ref.view(np.uint8))
+    assert np.array_equal(_bits(s.cpu().numpy()), _bits(s_ref))
+
+
+def test_rowwise_leading_dims_and_student_t():
+    from train_gpt_b200 import fp8
+    rng = np.random.default_rng(5)
+    x = rng.standard_t(3, size=(3, 50, 256)).astype(np.float32).astype(BF16)
+    q, s = fp8._quantize_to_fp8(to_torch_bf16(x).float(), 128)      # the reference passes the f32 upcast
+    q_ref, s_ref = fo.quantize_to_fp8(x.astype(np.float32))
+    assert q.shape == (3, 50, 256) and s.shape == (3, 50, 2)
+    assert np.array_equal(f8_bytes(q), q_ref.view(np.uint8)) and np.array_equal(_bits(s.cpu().numpy()), _bits(s_ref))
+
+
+def test_rowwise_nonfinite_tiles_are_flagged():
+    from train_gpt_b200 import ops
+    x = np.ones((2, 256), np.float32)
+    x[0, 5] = np.nan
+    x[1, 130] = np.inf
+    q, s = ops.quantize_rowwise(to_torch_bf16(x))
+    q_ref, s_ref = fo.quantize_to_fp8(x)
+    s = s.cpu().numpy()
+    b, b_ref = f8_bytes(q), q_ref.view(np.uint8)
+    assert np.isnan(s[0, 0]) and np.isinf(s[1, 1]) and np.array_equal(np.isnan(s), np.isnan(s_ref))
+    assert np.array_equal((b & 0x7F) == 0x7F, (b_ref & 0x7F) == 0x7F)     # same NaN positions
+    finite = (b_ref & 0x7F) != 0x7F
+    assert np.array_equal(b[finite], b_ref[finite])
+
+
+def test_weight_colwise_matches_reference_vectors(golden):
+    from train_gpt_b200 import fp8
+    b = np.asarray(golden["q_w_in"]).view(BF16)
+    q, s = fp8.quantize_weight(to_torch_bf16(b))                      # (K,N), (K/128,N)
+    assert np.array_equal(f8_bytes(q).T, golden["q_wt_bytes"])
+    assert np.array_equal(_bits(s.cpu().numpy().T), _bits(golden["q_wt_scales"]))
+
+
+@pytest.mark.parametrize("shape", [(128, 8), (256, 192), (200, 264), (768, 3072), (1000, 2048), (16, 8192)])
+def test_colwise_bit_exact(shape):
+    from train_gpt_b200 import ops
+    rng = np.random.default_rng(hash(shape) % 2**32)
+    x = _awkward(rng, shape)
+    q, s = ops.quantize_colwise(to_torch_bf16(x))
+    q_ref, s_ref = fo.quantize_colwise(x.astype(np.float32))
+    assert np.array_equal(f8_bytes(q), q_ref.view(np.uint8))
+    assert np.array_equal(_bits(s.cpu().numpy()), _bits(s_ref))
+
+
+@pytest.mark.parametrize("shape", [(128, 128), (256, 384), (200, 256), (768, 3072)])
+def test_block128_bit_exact(shape):
+    from train_gpt_b200 import ops
+    rng = np.random.default_rng(hash(shape) % 2**32)
+    x = _awkward(rng, shape)
+    q, s = ops.quantize_block128(to_torch_bf16(x))
+    q_ref, s_ref = fo.quantize_block2d(x.astype(np.float32))
+    assert np.array_equal(f8_bytes(q), q_ref.view(np.uint8))
+    assert np.array_equal(_bits(s.cpu().numpy()), _bits(s_ref))
+
+
+def test_empty_and_errors():
+    from train_gpt_b200 import ops
+    q, s = ops.quantize_rowwise(torch.empty(0, 128, dtype=torch.bfloat16, device="cuda"))
+    assert q.shape == (0, 128) and s.shape == (0, 1)
+    with pytest.raises(ValueError, match="not divisible by block_k"):
+        ops.quantize_rowwise(torch.empty(4, 100, dtype=torch.bfloat16, device="cuda"))
+
+
+def test_full_size_properties():
+    """Config-1-sized activation (32768 x 2048 with 0.1 % x50 outliers): properties that do not
+    need the oracle on 67 M elements, plus an oracle check of a strided row sample."""
+    from train_gpt_b200 import ops
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn(32768, 2048, device="cuda", generator=g)
+    x = torch.where(torch.rand(x.shape, device="cuda", generator=g) < 1e-3, x * 50, x).to(torch.bfloat16)
+    q, s = ops.quantize_rowwise(x)
+    amax = x.float().view(32768, 16, 128).abs().amax(-1)
+    assert torch.equal(s, torch.clamp_min(amax / 448.0, 1e-30))
+    deq = q.float().view(32768, 16, 128) * s[..., None]
+    err = (deq - x.float().view(32768, 16, 128)).abs()
+    assert bool((err <= amax[..., None] * (2.0 ** -4) + 1e-30).all())       # e4m3 half-ulp at the top binade
+    assert int(q.view(torch.uint8).view(32768, 16, 128).__and__(0x7F).amax(-1).min()) == 0x7E  # every tile hits 448
+    q2, s2 = ops.quantize_rowwise(x)
+    assert torch.equal(q.view(torch.uint8), q2.view(torch.uint8)) and torch.equal(s, s2)  # deterministic
+    rows = torch.arange(0, 32768, 257, device="cuda")
+    q_ref, s_ref = fo.quantize_to_fp8(x[rows].float().cpu().numpy())
+    assert np.array_equal(f8_bytes(q[rows]), q_ref.view(np.uint8))
+    assert np.array_equal(_bits(s[rows].cpu().numpy()), _bits(s_ref))

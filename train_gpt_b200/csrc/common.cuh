@@ -1,0 +1,97 @@
+// Shared device/host helpers for the train_gpt_b200 kernels (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/train_gpt_b200.h"
+
+namespace tg {
+
+constexpr float kE4M3Max = 448.0f;   // train-gpt fp8.py:26
+constexpr float kScaleFloor = 1e-30f;  // train-gpt fp8.py:44
+constexpr int kTile = 128;           // train-gpt fp8.py:27
+
+// Records a failing CUDA call for tg_last_cuda_error() and returns TG_ERR_CUDA.
+int record_cuda_error(cudaError_t e, const char* where);
+// TG_OK if the current device is compute capability 10.x, else TG_ERR_ARCH.
+int check_arch();
+int sm_count();
+
+#define TG_CUDA_CHECK(expr)                                        \
+  do {                                                             \
+    cudaError_t _e = (expr);                                       \
+    if (_e != cudaSuccess) return tg::record_cuda_error(_e, #expr); \
+  } while (0)
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+#ifdef __CUDACC__
+
+// max that returns NaN if either input is NaN (jnp.max / jnp.maximum semantics).
+__device__ __forceinline__ float max_nan(float a, float b) {
+  float r;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
+
+// two bf16 packed in a 32-bit word -> two floats (exact)
+__device__ __forceinline__ float bf16lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+
+// round two floats to bf16 (RNE) and pack (lo in bits 0..15)
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+// scale of a tile from its amax: max(amax / 448, 1e-30) with NaN propagation
+__device__ __forceinline__ float scale_from_amax(float amax) {
+  return max_nan(__fdiv_rn(amax, kE4M3Max), kScaleFloor);
+}
+
+// RNE_e4m3(lo), RNE_e4m3(hi) packed into 16 bits (lo in bits 0..7).  Inputs never exceed
+// 448*(1+2^-23) in magnitude here, so saturation never changes a finite result.
+__device__ __forceinline__ uint32_t cvt_e4m3x2(float lo, float hi) {
+  uint16_t r;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+// Quantise the 8 bf16 values held in w (as loaded from memory, element 0 in the low half
+// of w.x) with `scale`, returning 8 e4m3 bytes in memory order.
+__device__ __forceinline__ uint2 quantize8(const uint4& w, float scale) {
+  uint32_t b0 = cvt_e4m3x2(__fdiv_rn(bf16lo(w.x), scale), __fdiv_rn(bf16hi(w.x), scale));
+  uint32_t b1 = cvt_e4m3x2(__fdiv_rn(bf16lo(w.y), scale), __fdiv_rn(bf16hi(w.y), scale));
+  uint32_t b2 = cvt_e4m3x2(__fdiv_rn(bf16lo(w.z), scale), __fdiv_rn(bf16hi(w.z), scale));
+  uint32_t b3 = cvt_e4m3x2(__fdiv_rn(bf16lo(w.w), scale), __fdiv_rn(bf16hi(w.w), scale));
+  return make_uint2(b0 | (b1 << 16), b2 | (b3 << 16));
+}
+
+// |.|-max over the 8 bf16 values of w, NaN-propagating
+__device__ __forceinline__ float amax8(const uint4& w, float m = 0.f) {
+  m = max_nan(m, fabsf(bf16lo(w.x)));
+  m = max_nan(m, fabsf(bf16hi(w.x)));
+  m = max_nan(m, fabsf(bf16lo(w.y)));
+  m = max_nan(m, fabsf(bf16hi(w.y)));
+  m = max_nan(m, fabsf(bf16lo(w.z)));
+  m = max_nan(m, fabsf(bf16hi(w.z)));
+  m = max_nan(m, fabsf(bf16lo(w.w)));
+  m = max_nan(m, fabsf(bf16hi(w.w)));
+  return m;
+}
+
+__device__ __forceinline__ uint4 ld_nc_v4(const void* p) {
+  uint4 r;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "l"(p));
+  return r;
+}
+
+#endif  // __CUDACC__
+
+}  // namespace tg

@@ -1,0 +1,500 @@
+// Block-scaled e4m3 GEMM for sm_100a:  D[m,n] = sum_kb SA(m,kb) SB(n,kb) sum_{k in kb} A[m,k] B[n,k]
+//
+// Replaces jax.nn.scaled_matmul as train-gpt calls it (fp8.py:70-76) plus the bf16 cast of
+// fp8.py:78, and -- with other operand orientations -- the backward GEMMs of fp8.py:96-97.
+//
+// The scales are float32 (amax/448), not powers of two, so the tensor core's own
+// block-scale path (UE8M0 factors) cannot apply them bit-faithfully.  Instead every
+// 128-deep contraction block is issued as its own tcgen05.mma chain into a fresh TMEM
+// accumulator buffer, and four "promotion" warps pull each finished buffer out of TMEM
+// (tcgen05.ld), multiply by SA*SB and add into float32 register accumulators with packed
+// f32x2 FMAs while the tensor core fills the next buffer.  Four 128-column TMEM buffers
+// rotate (all 512 columns).
+//
+// Warp roles in the 192-thread CTA (persistent, one CTA per SM, tiles round-robin):
+//   warp 0      one lane issues TMA loads (A and B tiles, 128 x 128 bytes, 128B swizzle)
+//   warp 1      allocates TMEM; one lane issues tcgen05.mma + tcgen05.commit
+//   warps 2..5  promotion + store of the finished 128 x 128 tile (TMEM lane quarter = warp % 4)
+//
+// Operand orientation is data, not code: the TMA box is 128 bytes x 128 rows for both
+// K-major and MN-major storage (only the coordinates swap), and the shared-memory operand
+// descriptors / instruction descriptor carry the major-ness, so dgrad and wgrad read the
+// same buffers the forward wrote, untransposed.
+//
+// Every wait on an mbarrier is bounded: when the limit runs out the waiting role raises a
+// CTA-wide abort flag, stores a code in *status, and all roles fall through to the common
+// teardown (TMEM is always freed).
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace tg {
+
+constexpr int BM = 128;          // tile rows (TMEM lanes)
+constexpr int BN = 128;          // tile columns (TMEM columns per buffer)
+constexpr int BK = 128;          // contraction block = scale granularity (fp8.py:27)
+constexpr int UMMA_K = 32;       // K of one tcgen05.mma.kind::f8f6f4
+constexpr int kStages = 6;       // shared-memory pipeline depth
+constexpr int kTmemBufs = 4;     // accumulator buffers in TMEM
+constexpr int kTmemCols = kTmemBufs * BN;  // 512
+constexpr int kTileBytes = BM * BK;        // 16384, A or B tile
+constexpr int kGemmThreads = 192;
+constexpr int kPromoThreads = 128;
+constexpr long long kWaitLimitCycles = 4000000000LL;  // ~2 s at 2 GHz
+
+struct SmemLayout {
+  // offsets from the 1024-aligned base of dynamic shared memory
+  static constexpr int a = 0;
+  static constexpr int b = kStages * kTileBytes;
+  static constexpr int sb = 2 * kStages * kTileBytes;            // float[2][BN]
+  static constexpr int bars = sb + 2 * BN * 4;                   // uint64 barriers
+  static constexpr int n_bars = 2 * kStages + 2 * kTmemBufs + 1;
+  static constexpr int tmem_ptr = bars + n_bars * 8;
+  static constexpr int abort_flag = tmem_ptr + 4;
+  static constexpr int total = abort_flag + 4;
+};
+constexpr int kGemmSmemBytes = SmemLayout::total + 1024;  // slack for manual alignment
+
+struct GemmParams {
+  const float* sa;
+  long long sa_sm, sa_sk;
+  const float* sb;
+  long long sb_sn, sb_sk;
+  void* d;
+  long long ldd;
+  int M, N, nkb;
+  int a_mn, b_mn;       // 1 = MN-major storage
+  int tiles_m, tiles_n;
+  unsigned* status;
+};
+
+// ---- PTX wrappers ----------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait.  Returns false if the CTA is aborting (this call may be the one that
+// raises the abort, tagging *status with `who`).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          unsigned* status, unsigned who) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (uint32_t spin = 1;; ++spin) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spin & 63u) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kWaitLimitCycles) {
+        *abort_flag = 1;
+        if (status != nullptr) atomicCAS(status, 0u, who);
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void umma_f8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                        uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// 32 lanes x 32 consecutive columns of 32-bit: thread i <- lane (base_lane + i), v[j] <- column j
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+        "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+// Wait for this thread's outstanding tcgen05.ld.  The registers are listed as in/out
+// operands so that no use of them can be scheduled above the wait.
+__device__ __forceinline__ void tmem_wait_ld(uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.wait::ld.sync.aligned;"
+      : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]),
+        "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15]),
+        "+r"(v[16]), "+r"(v[17]), "+r"(v[18]), "+r"(v[19]), "+r"(v[20]), "+r"(v[21]), "+r"(v[22]), "+r"(v[23]),
+        "+r"(v[24]), "+r"(v[25]), "+r"(v[26]), "+r"(v[27]), "+r"(v[28]), "+r"(v[29]), "+r"(v[30]), "+r"(v[31])
+      :
+      : "memory");
+}
+
+__device__ __forceinline__ void promo_bar_sync() {
+  asm volatile("bar.sync 1, %0;" ::"n"(kPromoThreads) : "memory");
+}
+
+// Shared-memory operand descriptor, 128-byte swizzle, 8-row groups 1024 bytes apart.
+//   bits  0-13 start address >> 4      bits 16-29 leading byte offset >> 4
+//   bits 32-45 stride byte offset >> 4 bits 46-47 descriptor version (1 on sm_100)
+//   bits 61-63 layout (2 = 128B swizzle)
+// K-major: rows of 128 contraction bytes; 8 rows per swizzle atom; LBO unused.
+// MN-major: rows of 128 m/n bytes, one row per k; SBO = stride between 8-k groups; LBO =
+// stride between 128-wide m/n chunks (one chunk here).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= uint64_t((saddr >> 4) & 0x3FFFu);
+  d |= uint64_t(kTileBytes >> 4) << 16;
+  d |= uint64_t(1024 >> 4) << 32;
+  d |= uint64_t(1) << 46;
+  d |= uint64_t(2) << 61;
+  return d;
+}
+
+// ---- kernel ----------------------------------------------------------------------------
+
+template <int SB_GRAN, bool OUT_F32>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                            const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t bar0 = sbase + SmemLayout::bars;
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (kStages + s); };
+  auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * kStages + b); };
+  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * kStages + kTmemBufs + b); };
+  const uint32_t drain_bar = bar0 + 8u * (2 * kStages + 2 * kTmemBufs);
+  volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem + SmemLayout::tmem_ptr);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SmemLayout::abort_flag);
+  float* s_sb = reinterpret_cast<float*>(smem + SmemLayout::sb);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_tiles = p.tiles_m * p.tiles_n;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < kTmemBufs; ++b) {
+      mbar_init(tfull_bar(b), 1);
+      mbar_init(tempty_bar(b), kPromoThreads);
+    }
+    mbar_init(drain_bar, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_a)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_b)) : "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(sbase + SmemLayout::tmem_ptr, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ---------------------------------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
+        const int m0 = (tile / p.tiles_n) * BM, n0 = (tile % p.tiles_n) * BN;
+        for (int kb = 0; kb < p.nkb; ++kb, ++it) {
+          const int s = it % kStages;
+          if (!(ok = mbar_wait(empty_bar(s), ((it / kStages) & 1u) ^ 1u, abort_flag, p.status, 1u))) break;
+          mbar_expect_tx(full_bar(s), 2 * kTileBytes);
+          const int k0 = kb * BK;
+          tma_load_2d(sbase + SmemLayout::a + s * kTileBytes, &tmap_a, full_bar(s), p.a_mn ? m0 : k0, p.a_mn ? k0 : m0);
+          tma_load_2d(sbase + SmemLayout::b + s * kTileBytes, &tmap_b, full_bar(s), p.b_mn ? n0 : k0, p.b_mn ? k0 : n0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer -----------------------------------------
+    if (lane == 0) {
+      // instruction descriptor: D f32 (bit 4), A/B e4m3 (0), major bits 15/16, N>>3 at 17, M>>4 at 24
+      const uint32_t idesc = (1u << 4) | (uint32_t(p.a_mn) << 15) | (uint32_t(p.b_mn) << 16) |
+                             (uint32_t(BN >> 3) << 17) | (uint32_t(BM >> 4) << 24);
+      // descriptor start-address step per UMMA_K: 32 bytes along a K-major row, 32 rows of 128 B otherwise
+      const uint32_t a_step = p.a_mn ? (UMMA_K * 128) >> 4 : UMMA_K >> 4;
+      const uint32_t b_step = p.b_mn ? (UMMA_K * 128) >> 4 : UMMA_K >> 4;
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
+        for (int kb = 0; kb < p.nkb; ++kb, ++it) {
+          const int s = it % kStages, buf = it % kTmemBufs;
+          if (!(ok = mbar_wait(tempty_bar(buf), ((it / kTmemBufs) & 1u) ^ 1u, abort_flag, p.status, 2u))) break;
+          if (!(ok = mbar_wait(full_bar(s), (it / kStages) & 1u, abort_flag, p.status, 3u))) break;
+          tc_fence_after();
+          const uint64_t a_desc = make_smem_desc(sbase + SmemLayout::a + s * kTileBytes);
+          const uint64_t b_desc = make_smem_desc(sbase + SmemLayout::b + s * kTileBytes);
+          const uint32_t d_tmem = tmem_base + uint32_t(buf * BN);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_f8(d_tmem, a_desc + uint64_t(k * a_step), b_desc + uint64_t(k * b_step), idesc, k > 0 ? 1u : 0u);
+          umma_commit(empty_bar(s));    // shared-memory stage free once these MMAs retire
+          umma_commit(tfull_bar(buf));  // accumulator buffer ready for promotion
+        }
+      }
+      // make sure nothing issued here is still running when TMEM is freed
+      umma_commit(drain_bar);
+      mbar_wait(drain_bar, 0u, abort_flag, p.status, 4u);
+    }
+  } else {
+    // ------------------------------ promotion + store ----------------------------------
+    const int quarter = warp & 3;              // TMEM lanes this warp may touch
+    const int r = quarter * 32 + lane;         // row inside the tile
+    const int pt = threadIdx.x - 64;           // 0..127 among promotion threads
+    uint32_t it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+      const int m0 = (tile / p.tiles_n) * BM, n0 = (tile % p.tiles_n) * BN;
+      const int m = m0 + r;
+      const bool m_ok = m < p.M;
+      const float* sa_ptr = p.sa + (long long)(m_ok ? m : 0) * p.sa_sm;
+      const float* sb_ptr;
+      bool sb_ok = true;
+      if (SB_GRAN == 1) {
+        sb_ok = (n0 + pt) < p.N;
+        sb_ptr = p.sb + (long long)(sb_ok ? n0 + pt : 0) * p.sb_sn;
+      } else {
+        sb_ptr = p.sb + (long long)(n0 / 128) * p.sb_sn;
+      }
+      float2 acc[BN / 2];
+#pragma unroll
+      for (int j = 0; j < BN / 2; ++j) acc[j] = make_float2(0.f, 0.f);
+
+      float sa_next = m_ok ? __ldg(sa_ptr) : 0.f;
+      float sb_next = sb_ok ? __ldg(sb_ptr) : 0.f;
+      for (int kb = 0; kb < p.nkb; ++kb, ++it) {
+        const int buf = it % kTmemBufs;
+        const float sa_v = sa_next, sb_v = sb_next;
+        if (kb + 1 < p.nkb) {
+          sa_next = m_ok ? __ldg(sa_ptr + (long long)(kb + 1) * p.sa_sk) : 0.f;
+          sb_next = sb_ok ? __ldg(sb_ptr + (long long)(kb + 1) * p.sb_sk) : 0.f;
+        }
+        float* sb_stage = s_sb + (it & 1u) * BN;
+        if (SB_GRAN == 1) {
+          sb_stage[pt] = sb_v;
+          promo_bar_sync();
+        }
+        // After an abort the remaining iterations only keep the named barrier above in
+        // step (no thread may leave while others still wait on it); TMEM is not touched.
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar(buf), (it / kTmemBufs) & 1u, abort_flag, p.status, 5u));
+        if (!ok) continue;
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(buf * BN);
+        const float2 sa2 = make_float2(sa_v, sa_v);
+        const float s_scalar = sa_v * sb_v;
+        const float2 s2 = make_float2(s_scalar, s_scalar);
+        uint32_t v[2][32];
+        tmem_ld32(taddr, v[0]);
+#pragma unroll
+        for (int c = 0; c < BN / 32; ++c) {
+          tmem_wait_ld(v[c & 1]);
+          if (c + 1 < BN / 32) tmem_ld32(taddr + uint32_t((c + 1) * 32), v[(c + 1) & 1]);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float2 pv = make_float2(__uint_as_float(v[c & 1][2 * j]), __uint_as_float(v[c & 1][2 * j + 1]));
+            if (SB_GRAN == 1) {
+              const float2 sbv = *reinterpret_cast<const float2*>(sb_stage + c * 32 + 2 * j);
+              acc[c * 16 + j] = __ffma2_rn(__fmul2_rn(pv, sbv), sa2, acc[c * 16 + j]);
+            } else {
+              acc[c * 16 + j] = __ffma2_rn(pv, s2, acc[c * 16 + j]);
+            }
+          }
+        }
+        // all of this thread's reads of the buffer have completed (wait::ld above)
+        tc_fence_before();
+        mbar_arrive(tempty_bar(buf));
+      }
+      if (!ok) continue;
+      // ---- store the finished tile row: 128 columns, contiguous per thread -------------
+      if (m_ok) {
+        if (OUT_F32) {
+          float* drow = static_cast<float*>(p.d) + (long long)m * p.ldd + n0;
+#pragma unroll
+          for (int j = 0; j < BN / 4; ++j) {
+            if (n0 + j * 4 < p.N)
+              *reinterpret_cast<float4*>(drow + j * 4) =
+                  make_float4(acc[2 * j].x, acc[2 * j].y, acc[2 * j + 1].x, acc[2 * j + 1].y);
+          }
+        } else {
+          __nv_bfloat16* drow = static_cast<__nv_bfloat16*>(p.d) + (long long)m * p.ldd + n0;
+#pragma unroll
+          for (int j = 0; j < BN / 8; ++j) {
+            if (n0 + j * 8 < p.N) {
+              uint4 o;
+              o.x = pack_bf16x2(acc[4 * j].x, acc[4 * j].y);
+              o.y = pack_bf16x2(acc[4 * j + 1].x, acc[4 * j + 1].y);
+              o.z = pack_bf16x2(acc[4 * j + 2].x, acc[4 * j + 2].y);
+              o.w = pack_bf16x2(acc[4 * j + 3].x, acc[4 * j + 3].y);
+              *reinterpret_cast<uint4*>(drow + j * 8) = o;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // ------------------------------ teardown ----------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---- host ------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static int get_encode_fn(EncodeTiledFn* out) {
+  static EncodeTiledFn cached = nullptr;
+  if (cached == nullptr) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    TG_CUDA_CHECK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+    if (qres != cudaDriverEntryPointSuccess || fn == nullptr)
+      return record_cuda_error(cudaErrorSymbolNotFound, "cuTensorMapEncodeTiled entry point");
+    cached = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  *out = cached;
+  return TG_OK;
+}
+
+// 2-D byte tensor [outer][inner], row pitch `pitch` bytes, box 128 x 128, 128-byte swizzle.
+static int make_tmap(CUtensorMap* map, const void* base, int64_t inner, int64_t outer, int64_t pitch) {
+  EncodeTiledFn enc;
+  if (int rc = get_encode_fn(&enc)) return rc;
+  cuuint64_t dims[2] = {cuuint64_t(inner), cuuint64_t(outer)};
+  cuuint64_t strides[1] = {cuuint64_t(pitch)};
+  cuuint32_t box[2] = {128, 128};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return record_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
+  return TG_OK;
+}
+
+template <int SB_GRAN, bool OUT_F32>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t st) {
+  auto kern = gemm_fp8_blockscaled_kernel<SB_GRAN, OUT_F32>;
+  static bool attr_set = false;  // per instantiation; set once per process (per-device attribute: set each time on a new device)
+  static int attr_dev = -1;
+  int dev = 0;
+  TG_CUDA_CHECK(cudaGetDevice(&dev));
+  if (!attr_set || attr_dev != dev) {
+    TG_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes));
+    attr_set = true;
+    attr_dev = dev;
+  }
+  kern<<<grid, kGemmThreads, kGemmSmemBytes, st>>>(ta, tb, p);
+  TG_CUDA_CHECK(cudaGetLastError());
+  return TG_OK;
+}
+
+}  // namespace tg
+
+using namespace tg;
+
+extern "C" int tg_gemm_fp8_blockscaled(const tg_gemm_args* a, void* stream) {
+  if (a == nullptr) return TG_ERR_SHAPE;
+  if (a->M < 0 || a->N < 0 || a->K < 0) return TG_ERR_SHAPE;
+  if (a->M == 0 || a->N == 0) return TG_OK;
+  if (a->M > INT32_MAX || a->N > INT32_MAX || a->K > INT32_MAX) return TG_ERR_TOO_LARGE;
+  if ((a->a_major != TG_MAJOR_K && a->a_major != TG_MAJOR_MN) || (a->b_major != TG_MAJOR_K && a->b_major != TG_MAJOR_MN))
+    return TG_ERR_SHAPE;
+  if (a->sb_gran_n != 1 && a->sb_gran_n != 128) return TG_ERR_SHAPE;
+  if (a->out_dtype != TG_OUT_BF16 && a->out_dtype != TG_OUT_F32) return TG_ERR_SHAPE;
+  if (a->N % 8 != 0 || a->ldd % 8 != 0 || a->ldd < a->N) return TG_ERR_SHAPE;
+  if (a->lda % 16 != 0 || a->ldb % 16 != 0) return TG_ERR_SHAPE;
+  const int64_t a_inner = a->a_major == TG_MAJOR_K ? a->K : a->M, a_outer = a->a_major == TG_MAJOR_K ? a->M : a->K;
+  const int64_t b_inner = a->b_major == TG_MAJOR_K ? a->K : a->N, b_outer = a->b_major == TG_MAJOR_K ? a->N : a->K;
+  if (a->lda < a_inner || a->ldb < b_inner) return TG_ERR_SHAPE;
+  if (!aligned16(a->a) || !aligned16(a->b) || !aligned16(a->d)) return TG_ERR_ALIGN;
+  if (int rc = check_arch()) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (a->K == 0) {
+    const size_t esz = a->out_dtype == TG_OUT_F32 ? 4 : 2;
+    TG_CUDA_CHECK(cudaMemset2DAsync(a->d, size_t(a->ldd) * esz, 0, size_t(a->N) * esz, size_t(a->M), st));
+    return TG_OK;
+  }
+  CUtensorMap ta, tb;
+  if (int rc = make_tmap(&ta, a->a, a_inner, a_outer, a->lda)) return rc;
+  if (int rc = make_tmap(&tb, a->b, b_inner, b_outer, a->ldb)) return rc;
+  GemmParams p;
+  p.sa = a->sa; p.sa_sm = a->sa_stride_m; p.sa_sk = a->sa_stride_kb;
+  p.sb = a->sb; p.sb_sn = a->sb_stride_n; p.sb_sk = a->sb_stride_kb;
+  p.d = a->d; p.ldd = a->ldd;
+  p.M = int(a->M); p.N = int(a->N); p.nkb = int((a->K + BK - 1) / BK);
+  p.a_mn = a->a_major == TG_MAJOR_MN; p.b_mn = a->b_major == TG_MAJOR_MN;
+  p.tiles_m = int((a->M + BM - 1) / BM); p.tiles_n = int((a->N + BN - 1) / BN);
+  p.status = a->status;
+  const int64_t n_tiles = int64_t(p.tiles_m) * p.tiles_n;
+  if (n_tiles > INT32_MAX) return TG_ERR_TOO_LARGE;
+  const int sms = sm_count();
+  const int grid = int(n_tiles < sms ? n_tiles : sms);
+  const bool f32 = a->out_dtype == TG_OUT_F32;
+  if (a->sb_gran_n == 1) return f32 ? launch_gemm<1, true>(ta, tb, p, grid, st) : launch_gemm<1, false>(ta, tb, p, grid, st);
+  return f32 ? launch_gemm<128, true>(ta, tb, p, grid, st) : launch_gemm<128, false>(ta, tb, p, grid, st);
+}

@@ -1,0 +1,359 @@
+// RMSNorm forward (optionally fused with the 1x128 e4m3 quantiser) and backward.
+//
+// Reference semantics: train-gpt kernels.py:44-53 (+ the variance pass at :66) for the
+// fused single-rounding norm, kernels.py:30-33 for the "pure" three-rounding norm,
+// kernels.py:104-118 for the backward, fp8.py:39-47 + :66 for the quantiser that consumes
+// the norm's bf16 output.
+//
+// Layout: a row is split over WPR warps; each warp owns NCHUNK chunks of 256 columns and
+// each lane 8 consecutive columns (one 128-bit load) per chunk, so a half-warp owns
+// exactly one 128-column quantisation tile.  The whole row stays in registers between the
+// sum-of-squares pass and the normalise/quantise pass: x is read from HBM once.
+#include "common.cuh"
+
+namespace tg {
+
+constexpr int kNormWarps = 8;  // warps per thread block
+
+template <int WPR>
+__device__ __forceinline__ float row_sum(float v, float* s_red, int warp, int lane) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  if constexpr (WPR > 1) {
+    // s_red: [kNormWarps] floats; the caller separates uses with __syncthreads()
+    if (lane == 0) s_red[warp] = v;
+    __syncthreads();
+    const int g0 = (warp / WPR) * WPR;
+    v = s_red[g0];
+#pragma unroll
+    for (int i = 1; i < WPR; ++i) v += s_red[g0 + i];
+  }
+  return v;
+}
+
+template <int NCHUNK, int WPR, bool QUANT>
+__global__ void __launch_bounds__(kNormWarps * 32)
+rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma,
+                   float eps, uint8_t* __restrict__ q, float* __restrict__ scales,
+                   __nv_bfloat16* __restrict__ y, float* __restrict__ rnorm_out, int64_t rows,
+                   int cols, int mode) {
+  __shared__ float s_red[2][kNormWarps];
+  constexpr int RPB = kNormWarps / WPR;  // rows per block per iteration
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int col_base = (warp % WPR) * NCHUNK * 256 + lane * 8;
+  const float inv_note = 0.f;
+  (void)inv_note;
+
+  uint4 gm[NCHUNK];
+#pragma unroll
+  for (int c = 0; c < NCHUNK; ++c) {
+    const int col = col_base + c * 256;
+    gm[c] = (col < cols) ? *reinterpret_cast<const uint4*>(gamma + col) : make_uint4(0, 0, 0, 0);
+  }
+
+  int it = 0;
+  for (int64_t row_base = int64_t(blockIdx.x) * RPB; row_base < rows;
+       row_base += int64_t(gridDim.x) * RPB, ++it) {
+    const int64_t row = row_base + warp / WPR;
+    const bool row_ok = row < rows;
+    uint4 w[NCHUNK];
+#pragma unroll
+    for (int c = 0; c < NCHUNK; ++c) {
+      const int col = col_base + c * 256;
+      w[c] = (row_ok && col < cols) ? ld_nc_v4(x + row * cols + col) : make_uint4(0, 0, 0, 0);
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < NCHUNK; ++c) {
+      float a;
+      a = bf16lo(w[c].x); ss = fmaf(a, a, ss);
+      a = bf16hi(w[c].x); ss = fmaf(a, a, ss);
+      a = bf16lo(w[c].y); ss = fmaf(a, a, ss);
+      a = bf16hi(w[c].y); ss = fmaf(a, a, ss);
+      a = bf16lo(w[c].z); ss = fmaf(a, a, ss);
+      a = bf16hi(w[c].z); ss = fmaf(a, a, ss);
+      a = bf16lo(w[c].w); ss = fmaf(a, a, ss);
+      a = bf16hi(w[c].w); ss = fmaf(a, a, ss);
+    }
+    ss = row_sum<WPR>(ss, s_red[it & 1], warp, lane);
+    const float var = __fdiv_rn(ss, float(cols));
+    const float rn = __frsqrt_rn(var + eps);
+    if (row_ok && rnorm_out != nullptr && lane == 0 && (warp % WPR) == 0) rnorm_out[row] = rn;
+    const float rn_b = __bfloat162float(__float2bfloat16_rn(rn));  // kernels.py:32 `.astype(x.dtype)`
+
+#pragma unroll
+    for (int c = 0; c < NCHUNK; ++c) {
+      const int col = col_base + c * 256;
+      const uint32_t xi[4] = {w[c].x, w[c].y, w[c].z, w[c].w};
+      const uint32_t gi[4] = {gm[c].x, gm[c].y, gm[c].z, gm[c].w};
+      uint4 yo;
+      uint32_t* yp = &yo.x;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float lo, hi;
+        if (mode == TG_NORM_FUSED) {
+          lo = __fmul_rn(__fmul_rn(bf16lo(xi[j]), rn), bf16lo(gi[j]));
+          hi = __fmul_rn(__fmul_rn(bf16hi(xi[j]), rn), bf16hi(gi[j]));
+          yp[j] = pack_bf16x2(lo, hi);
+        } else {
+          const uint32_t t = pack_bf16x2(__fmul_rn(bf16lo(xi[j]), rn_b), __fmul_rn(bf16hi(xi[j]), rn_b));
+          yp[j] = pack_bf16x2(__fmul_rn(bf16lo(t), bf16lo(gi[j])), __fmul_rn(bf16hi(t), bf16hi(gi[j])));
+        }
+      }
+      const bool ok = row_ok && col < cols;
+      if (y != nullptr && ok) *reinterpret_cast<uint4*>(y + row * cols + col) = yo;
+      if constexpr (QUANT) {
+        float m = amax8(yo);
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) m = max_nan(m, __shfl_xor_sync(0xffffffffu, m, o));
+        const float s = scale_from_amax(m);
+        if (ok) {
+          *reinterpret_cast<uint2*>(q + row * cols + col) = quantize8(yo, s);
+          if ((lane & 15) == 0) scales[row * (cols / kTile) + col / kTile] = s;
+        }
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Backward.  Per row: S1 = sum x^2, rnorm = rsqrt(S1/D + eps), normed = x*rnorm,
+// gs = g*gamma, dot = mean(gs*normed), dx = rnorm*(gs - normed*dot); per column:
+// dgamma = sum_rows g*normed, accumulated per lane in registers over all rows the block
+// visits, combined across the block's warps in shared memory, written as one float32 row
+// of `partial` per block and reduced over blocks (in block order) by a second kernel.
+// ---------------------------------------------------------------------------------------
+template <int NCHUNK, int WPR>
+__global__ void __launch_bounds__(kNormWarps * 32)
+rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma,
+                   const __nv_bfloat16* __restrict__ g, float eps, __nv_bfloat16* __restrict__ dx,
+                   float* __restrict__ partial, int64_t rows, int cols) {
+  extern __shared__ float s_dyn[];  // [cols] column sums of this block
+  __shared__ float s_red[4][kNormWarps];
+  constexpr int RPB = kNormWarps / WPR;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int col_base = (warp % WPR) * NCHUNK * 256 + lane * 8;
+  const float inv_d = __fdiv_rn(1.0f, float(cols));
+
+  float acc[NCHUNK][8];
+#pragma unroll
+  for (int c = 0; c < NCHUNK; ++c)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[c][j] = 0.f;
+
+  int it = 0;
+  for (int64_t row_base = int64_t(blockIdx.x) * RPB; row_base < rows;
+       row_base += int64_t(gridDim.x) * RPB, ++it) {
+    const int64_t row = row_base + warp / WPR;
+    const bool row_ok = row < rows;
+    uint4 w[NCHUNK], gv[NCHUNK];
+#pragma unroll
+    for (int c = 0; c < NCHUNK; ++c) {
+      const int col = col_base + c * 256;
+      const bool ok = row_ok && col < cols;
+      w[c] = ok ? ld_nc_v4(x + row * cols + col) : make_uint4(0, 0, 0, 0);
+      gv[c] = ok ? ld_nc_v4(g + row * cols + col) : make_uint4(0, 0, 0, 0);
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < NCHUNK; ++c) {
+      const uint32_t xi[4] = {w[c].x, w[c].y, w[c].z, w[c].w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float a = bf16lo(xi[j]); ss = fmaf(a, a, ss);
+        a = bf16hi(xi[j]); ss = fmaf(a, a, ss);
+      }
+    }
+    ss = row_sum<WPR>(ss, s_red[(it & 1) * 2], warp, lane);
+    const float rn = __frsqrt_rn(__fdiv_rn(ss, float(cols)) + eps);
+
+    // gs*normed summed over the row; dgamma accumulation in the same sweep
+    float dsum = 0.f;
+#pragma unroll
+    for (int c = 0; c < NCHUNK; ++c) {
+      const int col = col_base + c * 256;
+      const uint4 gm = (col < cols) ? *reinterpret_cast<const uint4*>(gamma + col) : make_uint4(0, 0, 0, 0);
+      const uint32_t xi[4] = {w[c].x, w[c].y, w[c].z, w[c].w};
+      const uint32_t gi[4] = {gv[c].x, gv[c].y, gv[c].z, gv[c].w};
+      const uint32_t mi[4] = {gm.x, gm.y, gm.z, gm.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float n0 = __fmul_rn(bf16lo(xi[j]), rn), n1 = __fmul_rn(bf16hi(xi[j]), rn);
+        const float g0 = bf16lo(gi[j]), g1 = bf16hi(gi[j]);
+        acc[c][2 * j] = fmaf(g0, n0, acc[c][2 * j]);
+        acc[c][2 * j + 1] = fmaf(g1, n1, acc[c][2 * j + 1]);
+        dsum = fmaf(__fmul_rn(g0, bf16lo(mi[j])), n0, dsum);
+        dsum = fmaf(__fmul_rn(g1, bf16hi(mi[j])), n1, dsum);
+      }
+    }
+    dsum = row_sum<WPR>(dsum, s_red[(it & 1) * 2 + 1], warp, lane);
+    const float dot = __fmul_rn(dsum, inv_d);
+
+#pragma unroll
+    for (int c = 0; c < NCHUNK; ++c) {
+      const int col = col_base + c * 256;
+      if (!(row_ok && col < cols)) continue;
+      const uint4 gm = *reinterpret_cast<const uint4*>(gamma + col);
+      const uint32_t xi[4] = {w[c].x, w[c].y, w[c].z, w[c].w};
+      const uint32_t gi[4] = {gv[c].x, gv[c].y, gv[c].z, gv[c].w};
+      const uint32_t mi[4] = {gm.x, gm.y, gm.z, gm.w};
+      uint4 o;
+      uint32_t* op = &o.x;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float n0 = __fmul_rn(bf16lo(xi[j]), rn), n1 = __fmul_rn(bf16hi(xi[j]), rn);
+        const float gs0 = __fmul_rn(bf16lo(gi[j]), bf16lo(mi[j]));
+        const float gs1 = __fmul_rn(bf16hi(gi[j]), bf16hi(mi[j]));
+        // rnorm * (gs - normed*dot), the subtraction fused as kernels.py:114 allows XLA to
+        const float d0 = __fmul_rn(rn, fmaf(-n0, dot, gs0));
+        const float d1 = __fmul_rn(rn, fmaf(-n1, dot, gs1));
+        op[j] = pack_bf16x2(d0, d1);
+      }
+      *reinterpret_cast<uint4*>(dx + row * cols + col) = o;
+    }
+  }
+
+  // combine the block's warps in a fixed order, then publish the block's row of partials
+  for (int i = threadIdx.x; i < cols; i += blockDim.x) s_dyn[i] = 0.f;
+  __syncthreads();
+  for (int turn = 0; turn < RPB; ++turn) {
+    if (warp / WPR == turn) {
+#pragma unroll
+      for (int c = 0; c < NCHUNK; ++c) {
+        const int col = col_base + c * 256;
+        if (col < cols) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) s_dyn[col + j] += acc[c][j];
+        }
+      }
+    }
+    __syncthreads();
+  }
+  for (int i = threadIdx.x; i < cols; i += blockDim.x) partial[int64_t(blockIdx.x) * cols + i] = s_dyn[i];
+}
+
+__global__ void __launch_bounds__(256)
+rmsnorm_dgamma_reduce_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ dgamma,
+                             int n_blocks, int cols) {
+  const int col = blockIdx.x * blockDim.x + threadIdx.x;
+  if (col >= cols) return;
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  int b = 0;
+  for (; b + 4 <= n_blocks; b += 4) {
+    s0 += partial[int64_t(b) * cols + col];
+    s1 += partial[int64_t(b + 1) * cols + col];
+    s2 += partial[int64_t(b + 2) * cols + col];
+    s3 += partial[int64_t(b + 3) * cols + col];
+  }
+  for (; b < n_blocks; ++b) s0 += partial[int64_t(b) * cols + col];
+  dgamma[col] = __float2bfloat16_rn((s0 + s1) + (s2 + s3));
+}
+
+struct NormGeom {
+  int nchunk, wpr;
+};
+
+// Smallest (NCHUNK, WPR) with WPR * NCHUNK * 256 >= cols; NCHUNK <= 8 keeps the row in
+// registers, WPR <= 4 keeps at least two rows per block.
+static bool norm_geom(int64_t cols, NormGeom* g) {
+  if (cols <= 0 || cols > 8192) return false;
+  const int chunks = int((cols + 255) / 256);
+  int wpr = 1;
+  while (chunks > wpr * 8) wpr *= 2;
+  int nchunk = 1;
+  while (nchunk * wpr < chunks) nchunk *= 2;
+  g->nchunk = nchunk;
+  g->wpr = wpr;
+  return true;
+}
+
+static int norm_blocks(int64_t rows, int wpr, int per_sm) {
+  const int rpb = kNormWarps / wpr;
+  int64_t need = (rows + rpb - 1) / rpb;
+  const int64_t cap = int64_t(sm_count()) * per_sm;
+  return int(need < cap ? need : cap);
+}
+
+template <bool QUANT>
+static int launch_fwd(const void* x, const void* gamma, float eps, void* q, float* scales, void* y,
+                      float* rnorm, int64_t rows, int64_t cols, int mode, cudaStream_t st) {
+  NormGeom g;
+  if (!norm_geom(cols, &g)) return cols > 8192 ? TG_ERR_TOO_LARGE : TG_ERR_SHAPE;
+  const int blocks = norm_blocks(rows, g.wpr, 16);
+#define TG_FWD_CASE(NC, W)                                                                          \
+  if (g.nchunk == NC && g.wpr == W) {                                                               \
+    rmsnorm_fwd_kernel<NC, W, QUANT><<<blocks, kNormWarps * 32, 0, st>>>(                           \
+        static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(gamma), eps,        \
+        static_cast<uint8_t*>(q), scales, static_cast<__nv_bfloat16*>(y), rnorm, rows, int(cols),   \
+        mode);                                                                                      \
+  } else
+  TG_FWD_CASE(1, 1) TG_FWD_CASE(2, 1) TG_FWD_CASE(4, 1) TG_FWD_CASE(8, 1) TG_FWD_CASE(8, 2)
+  TG_FWD_CASE(8, 4) { return TG_ERR_SHAPE; }
+#undef TG_FWD_CASE
+  TG_CUDA_CHECK(cudaGetLastError());
+  return TG_OK;
+}
+
+constexpr int kBwdBlocksPerSm = 2;
+
+}  // namespace tg
+
+using namespace tg;
+
+extern "C" int tg_rmsnorm_fwd(const void* x, const void* gamma, float eps, void* y, float* rnorm,
+                              int64_t rows, int64_t cols, int mode, void* stream) {
+  if (rows < 0 || cols <= 0 || cols % 8 != 0 || (mode != TG_NORM_FUSED && mode != TG_NORM_PURE)) return TG_ERR_SHAPE;
+  if (rows == 0) return TG_OK;
+  if (!aligned16(x) || !aligned16(gamma) || !aligned16(y)) return TG_ERR_ALIGN;
+  if (int rc = check_arch()) return rc;
+  return launch_fwd<false>(x, gamma, eps, nullptr, nullptr, y, rnorm, rows, cols, mode,
+                           static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int tg_rmsnorm_quant_fwd(const void* x, const void* gamma, float eps, void* q,
+                                    float* scales, void* y, float* rnorm, int64_t rows,
+                                    int64_t cols, int mode, void* stream) {
+  if (rows < 0 || cols <= 0 || cols % kTile != 0 || (mode != TG_NORM_FUSED && mode != TG_NORM_PURE)) return TG_ERR_SHAPE;
+  if (rows == 0) return TG_OK;
+  if (!aligned16(x) || !aligned16(gamma) || !aligned16(q) || !aligned16(y)) return TG_ERR_ALIGN;
+  if (int rc = check_arch()) return rc;
+  return launch_fwd<true>(x, gamma, eps, q, scales, y, rnorm, rows, cols, mode,
+                          static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int64_t tg_rmsnorm_bwd_scratch_bytes(int64_t rows, int64_t cols) {
+  NormGeom g;
+  if (rows <= 0 || !norm_geom(cols, &g)) return 0;
+  return int64_t(norm_blocks(rows, g.wpr, kBwdBlocksPerSm)) * cols * int64_t(sizeof(float));
+}
+
+extern "C" int tg_rmsnorm_bwd(const void* x, const void* gamma, const void* g, float eps, void* dx,
+                              void* dgamma, void* scratch, int64_t rows, int64_t cols, void* stream) {
+  if (rows < 0 || cols <= 0 || cols % 8 != 0) return TG_ERR_SHAPE;
+  NormGeom geo;
+  if (!norm_geom(cols, &geo)) return cols > 8192 ? TG_ERR_TOO_LARGE : TG_ERR_SHAPE;
+  if (!aligned16(x) || !aligned16(gamma) || !aligned16(g) || !aligned16(dx) || !aligned16(scratch)) return TG_ERR_ALIGN;
+  if (int rc = check_arch()) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (rows == 0) {
+    TG_CUDA_CHECK(cudaMemsetAsync(dgamma, 0, size_t(cols) * 2, st));
+    return TG_OK;
+  }
+  const int blocks = norm_blocks(rows, geo.wpr, kBwdBlocksPerSm);
+  const size_t smem = size_t(cols) * sizeof(float);
+#define TG_BWD_CASE(NC, W)                                                                      \
+  if (geo.nchunk == NC && geo.wpr == W) {                                                       \
+    rmsnorm_bwd_kernel<NC, W><<<blocks, kNormWarps * 32, smem, st>>>(                           \
+        static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(gamma),         \
+        static_cast<const __nv_bfloat16*>(g), eps, static_cast<__nv_bfloat16*>(dx),             \
+        static_cast<float*>(scratch), rows, int(cols));                                         \
+  } else
+  TG_BWD_CASE(1, 1) TG_BWD_CASE(2, 1) TG_BWD_CASE(4, 1) TG_BWD_CASE(8, 1) TG_BWD_CASE(8, 2)
+  TG_BWD_CASE(8, 4) { return TG_ERR_SHAPE; }
+#undef TG_BWD_CASE
+  TG_CUDA_CHECK(cudaGetLastError());
+  rmsnorm_dgamma_reduce_kernel<<<int((cols + 255) / 256), 256, 0, st>>>(
+      static_cast<const float*>(scratch), static_cast<__nv_bfloat16*>(dgamma), blocks, int(cols));
+  TG_CUDA_CHECK(cudaGetLastError());
+  return TG_OK;
+}

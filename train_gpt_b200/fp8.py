@@ -1,0 +1,135 @@
+"""Per-block-scaled FP8 matmul: the call surface of train-gpt's `fp8.py` on B200 kernels.
+
+`block_scaled_matmul(a, b, block_k=128)` keeps the reference's signature, error messages
+and differentiation contract (train-gpt fp8.py:30-36, :50-78, :85-101): differentiable in
+`a` and `b`, `block_k` static, gradients returned in the inputs' dtypes.
+
+Keyword-only extras (defaults reproduce the reference):
+  weight_tile  (128, 1)    the reference's weight-scale granularity (it quantises `b.T`
+                           along K, fp8.py:68); (128, 128) is the benchmark granularity.
+  backward     "bf16_ste"  the reference's straight-through bf16 backward (fp8.py:85-98);
+                           "fp8" runs dgrad and wgrad as block-scaled e4m3 GEMMs as well.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import ops
+
+E4M3_MAX = 448.0        # fp8.py:26
+DEFAULT_BLOCK_K = 128   # fp8.py:27
+
+
+def _check_block(block_k: int):
+    if block_k != DEFAULT_BLOCK_K:
+        raise ValueError(f"block_k={block_k} is not supported by the sm_100a kernels (only {DEFAULT_BLOCK_K})")
+
+
+def _quantize_to_fp8(x_f32: torch.Tensor, block_k: int = DEFAULT_BLOCK_K):
+    """fp8.py:39-47.  The reference only ever passes an upcast bf16 tensor (fp8.py:66,68);
+    a float32 argument is therefore narrowed back to bf16 (exact for such inputs)."""
+    K = x_f32.shape[-1]
+    if K % block_k != 0:
+        raise ValueError(f"K={K} not divisible by block_k={block_k}")
+    _check_block(block_k)
+    x = x_f32 if x_f32.dtype == torch.bfloat16 else x_f32.to(torch.bfloat16)
+    return ops.quantize_rowwise(x)
+
+
+def quantize_weight(b: torch.Tensor, weight_tile=(128, 1)):
+    """Quantise b (K, N) for the forward GEMM without transposing it."""
+    if tuple(weight_tile) == (128, 1):
+        return ops.quantize_colwise(b)
+    if tuple(weight_tile) == (128, 128):
+        return ops.quantize_block128(b)
+    raise ValueError(f"unsupported weight_tile {weight_tile}")
+
+
+def _validate(a, b, block_k):
+    K = a.shape[-1]
+    K_b, N = b.shape
+    if K != K_b:                                                    # fp8.py:53-54
+        raise ValueError(f"contracted-dim mismatch: a K={K}, b K={K_b}")
+    if K % block_k != 0:                                            # fp8.py:55-56
+        raise ValueError(f"K={K} not divisible by block_k={block_k}")
+    _check_block(block_k)
+    return K, N
+
+
+def _fp8_forward(a, b, block_k=DEFAULT_BLOCK_K, weight_tile=(128, 1), a_quantized=None):
+    """fp8.py:50-78.  `a_quantized` = (q, scales) of `a` made earlier (e.g. by the fused
+    norm+quantise kernel) skips the activation quantiser."""
+    K, N = _validate(a, b, block_k)
+    leading = a.shape[:-1]
+    if a_quantized is None:
+        a_q, a_s = ops.quantize_rowwise(a.reshape(-1, K).to(torch.bfloat16))
+    else:
+        a_q, a_s = a_quantized[0].reshape(-1, K), a_quantized[1].reshape(-1, K // block_k)
+    b = b.to(torch.bfloat16)
+    pad = (-N) % 16 if tuple(weight_tile) == (128, 1) else 0
+    if pad:
+        # the TMA row pitch of the (K, N) weight must be a multiple of 16 bytes: widen with
+        # zero columns (their tiles quantise to zeros) and drop them from the result
+        b = torch.nn.functional.pad(b, (0, pad))
+    w_q, w_s = quantize_weight(b, weight_tile)
+    y = ops.gemm_fwd(a_q, a_s, w_q, w_s, weight_tile)
+    if pad:
+        y = y[:, :N]
+    return y.reshape(*leading, N)
+
+
+def _fp8_backward(block_k, residuals, g, weight_tile=(128, 1), mode="bf16_ste"):
+    """fp8.py:85-98 (mode "bf16_ste"), or the same two GEMMs in block-scaled e4m3."""
+    a, b = residuals
+    K = a.shape[-1]
+    N = b.shape[1]
+    leading = a.shape[:-1]
+    a_2d = a.reshape(-1, K).to(torch.bfloat16)
+    g_2d = g.reshape(-1, N).to(torch.bfloat16)
+    b_bf = b.to(torch.bfloat16)
+    if mode == "bf16_ste":
+        da = g_2d @ b_bf.T                                          # fp8.py:96 (cuBLAS bf16)
+        db = a_2d.T @ g_2d                                          # fp8.py:97
+    elif mode == "fp8":
+        if N % block_k != 0:
+            raise ValueError(f"N={N} not divisible by block_k={block_k} (needed by the FP8 dgrad)")
+        g_q, g_s = ops.quantize_rowwise(g_2d)
+        if tuple(weight_tile) == (128, 1):
+            w_q, w_s = ops.quantize_rowwise(b_bf)                   # tiles along N, the dgrad contraction
+        else:
+            w_q, w_s = ops.quantize_block128(b_bf)
+        da = ops.gemm_dgrad(g_q, g_s, w_q, w_s, weight_tile)
+        x_qc, x_sc = ops.quantize_colwise(a_2d)
+        g_qc, g_sc = ops.quantize_colwise(g_2d)
+        db = ops.gemm_wgrad(x_qc, x_sc, g_qc, g_sc)
+    else:
+        raise ValueError(f"unknown backward mode {mode!r}; use 'bf16_ste' or 'fp8'")
+    return da.reshape(*leading, K).to(a.dtype), db.to(b.dtype)
+
+
+class _BlockScaledMatmul(torch.autograd.Function):
+    """The custom VJP of fp8.py:30,101 as a torch.autograd.Function."""
+
+    @staticmethod
+    def forward(ctx, a, b, block_k, weight_tile, backward, a_quantized):
+        ctx.save_for_backward(a, b)                                 # fp8.py:81-82: unquantised residuals
+        ctx.cfg = (block_k, tuple(weight_tile), backward)
+        return _fp8_forward(a, b, block_k, weight_tile, a_quantized)
+
+    @staticmethod
+    def backward(ctx, g):
+        block_k, weight_tile, mode = ctx.cfg
+        da, db = _fp8_backward(block_k, ctx.saved_tensors, g, weight_tile, mode)
+        return da, db, None, None, None, None
+
+
+def block_scaled_matmul(a: torch.Tensor, b: torch.Tensor, block_k: int = DEFAULT_BLOCK_K, *,
+                        weight_tile=(128, 1), backward: str = "bf16_ste", a_quantized=None) -> torch.Tensor:
+    """Per-K-tile block-scaled FP8 matmul.
+
+    a: (..., K), b: (K, N) -> (..., N) bf16.  Requires K % block_k == 0.
+    """
+    _validate(a, b, block_k)
+    if backward not in ("bf16_ste", "fp8"):
+        raise ValueError(f"unknown backward mode {backward!r}; use 'bf16_ste' or 'fp8'")
+    return _BlockScaledMatmul.apply(a, b, block_k, tuple(weight_tile), backward, a_quantized)

@@ -1,0 +1,201 @@
+"""Kernel-level operators: torch CUDA tensors in, torch CUDA tensors out, every one a
+single call through the C ABI on torch's current stream.  torch is used for device
+memory and streams only; no arithmetic on the path runs in torch.
+
+Quantised tensors are `torch.float8_e4m3fn`; scales are float32.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+from ._lib import GemmArgs, TG_MAJOR_K, TG_MAJOR_MN, TG_NORM_FUSED, TG_NORM_PURE, TG_OUT_BF16, TG_OUT_F32
+
+F8 = torch.float8_e4m3fn
+TILE = 128
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def _need(t: torch.Tensor, dtype, name: str) -> torch.Tensor:
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor (there is no CPU path)")
+    if t.dtype != dtype:
+        raise TypeError(f"{name} must be {dtype}, got {t.dtype}")
+    return t if t.is_contiguous() else t.contiguous()
+
+
+def _cdiv(a: int, b: int) -> int:
+    return -(-a // b)
+
+
+# ---- quantisers ---------------------------------------------------------------------------
+
+def quantize_rowwise(x: torch.Tensor):
+    """1x128 tiles along the last axis (train-gpt fp8.py:39-47 as called at :66).
+    x (..., K) bf16 -> q (..., K) e4m3, scales (..., K/128) f32."""
+    x = _need(x, torch.bfloat16, "x")
+    K = x.shape[-1]
+    if K % TILE:
+        raise ValueError(f"K={K} not divisible by block_k={TILE}")
+    rows = x.numel() // K if K else 0
+    q = torch.empty(x.shape, dtype=F8, device=x.device)
+    s = torch.empty((*x.shape[:-1], K // TILE), dtype=torch.float32, device=x.device)
+    _lib.check(_lib.load().tg_quantize_rowwise(_ptr(x), _ptr(q), _ptr(s), rows, K, _stream()), "tg_quantize_rowwise")
+    return q, s
+
+
+def quantize_colwise(x: torch.Tensor):
+    """128x1 tiles of a 2-D tensor (what `_quantize_to_fp8(b.T)` at fp8.py:68 computes,
+    without the transpose).  x (R, C) bf16 -> q (R, C) e4m3, scales (ceil(R/128), C) f32."""
+    x = _need(x, torch.bfloat16, "x")
+    if x.dim() != 2:
+        raise ValueError("quantize_colwise takes a 2-D tensor")
+    R, Cc = x.shape
+    q = torch.empty((R, Cc), dtype=F8, device=x.device)
+    s = torch.empty((_cdiv(R, TILE), Cc), dtype=torch.float32, device=x.device)
+    _lib.check(_lib.load().tg_quantize_colwise(_ptr(x), _ptr(q), _ptr(s), R, Cc, _stream()), "tg_quantize_colwise")
+    return q, s
+
+
+def quantize_block128(x: torch.Tensor):
+    """128x128 tiles.  x (R, C) bf16 -> q (R, C) e4m3, scales (ceil(R/128), C/128) f32."""
+    x = _need(x, torch.bfloat16, "x")
+    if x.dim() != 2:
+        raise ValueError("quantize_block128 takes a 2-D tensor")
+    R, Cc = x.shape
+    if Cc % TILE:
+        raise ValueError(f"C={Cc} not divisible by {TILE}")
+    q = torch.empty((R, Cc), dtype=F8, device=x.device)
+    s = torch.empty((_cdiv(R, TILE), Cc // TILE), dtype=torch.float32, device=x.device)
+    _lib.check(_lib.load().tg_quantize_block128(_ptr(x), _ptr(q), _ptr(s), R, Cc, _stream()), "tg_quantize_block128")
+    return q, s
+
+
+# ---- RMSNorm ------------------------------------------------------------------------------
+
+def rmsnorm_fwd(x, gamma, eps: float, pure: bool = False, want_rnorm: bool = False):
+    """kernels.py:44-53 (+:66), or kernels.py:30-33 when `pure`.  Returns y [, rnorm]."""
+    x = _need(x, torch.bfloat16, "x")
+    gamma = _need(gamma, torch.bfloat16, "gamma")
+    D = x.shape[-1]
+    if gamma.shape != (D,):
+        raise ValueError(f"scale shape {tuple(gamma.shape)} does not match last dim {D}")
+    rows = x.numel() // D
+    y = torch.empty_like(x)
+    rn = torch.empty(x.shape[:-1], dtype=torch.float32, device=x.device) if want_rnorm else None
+    _lib.check(_lib.load().tg_rmsnorm_fwd(_ptr(x), _ptr(gamma), float(eps), _ptr(y), _ptr(rn), rows, D,
+                                          TG_NORM_PURE if pure else TG_NORM_FUSED, _stream()), "tg_rmsnorm_fwd")
+    return (y, rn) if want_rnorm else y
+
+
+def rmsnorm_quant_fwd(x, gamma, eps: float, pure: bool = False, want_y: bool = False, want_rnorm: bool = False):
+    """Norm + 1x128 quantise in one pass.  Returns (q, scales, y or None, rnorm or None)."""
+    x = _need(x, torch.bfloat16, "x")
+    gamma = _need(gamma, torch.bfloat16, "gamma")
+    D = x.shape[-1]
+    if gamma.shape != (D,):
+        raise ValueError(f"scale shape {tuple(gamma.shape)} does not match last dim {D}")
+    if D % TILE:
+        raise ValueError(f"K={D} not divisible by block_k={TILE}")
+    rows = x.numel() // D
+    q = torch.empty(x.shape, dtype=F8, device=x.device)
+    s = torch.empty((*x.shape[:-1], D // TILE), dtype=torch.float32, device=x.device)
+    y = torch.empty_like(x) if want_y else None
+    rn = torch.empty(x.shape[:-1], dtype=torch.float32, device=x.device) if want_rnorm else None
+    _lib.check(_lib.load().tg_rmsnorm_quant_fwd(_ptr(x), _ptr(gamma), float(eps), _ptr(q), _ptr(s), _ptr(y), _ptr(rn),
+                                                rows, D, TG_NORM_PURE if pure else TG_NORM_FUSED, _stream()),
+               "tg_rmsnorm_quant_fwd")
+    return q, s, y, rn
+
+
+def rmsnorm_bwd(x, gamma, g, eps: float):
+    """kernels.py:104-118.  Returns (dx bf16 like x, dgamma bf16 (D,))."""
+    x = _need(x, torch.bfloat16, "x")
+    gamma = _need(gamma, torch.bfloat16, "gamma")
+    g = _need(g, torch.bfloat16, "g")
+    if g.shape != x.shape:
+        raise ValueError("g and x shapes differ")
+    D = x.shape[-1]
+    rows = x.numel() // D
+    lib = _lib.load()
+    dx = torch.empty_like(x)
+    dgamma = torch.empty((D,), dtype=torch.bfloat16, device=x.device)
+    nbytes = lib.tg_rmsnorm_bwd_scratch_bytes(rows, D)
+    scratch = torch.empty((max(nbytes, 16),), dtype=torch.uint8, device=x.device)
+    _lib.check(lib.tg_rmsnorm_bwd(_ptr(x), _ptr(gamma), _ptr(g), float(eps), _ptr(dx), _ptr(dgamma), _ptr(scratch),
+                                  rows, D, _stream()), "tg_rmsnorm_bwd")
+    return dx, dgamma
+
+
+# ---- GEMM ---------------------------------------------------------------------------------
+
+def new_status(device) -> torch.Tensor:
+    """A zeroed device word for the GEMM's bounded-wait status."""
+    return torch.zeros((1,), dtype=torch.int32, device=device)
+
+
+def gemm_blockscaled(a, b, sa, sb, *, M, N, K, a_major, b_major, sa_strides, sb_strides, sb_gran_n,
+                     out_dtype=torch.bfloat16, status=None, out=None):
+    """Raw call of tg_gemm_fp8_blockscaled; see include/train_gpt_b200.h for the argument
+    meaning.  a, b are 2-D e4m3 tensors as stored; strides are in elements."""
+    for t, n in ((a, "a"), (b, "b")):
+        if t.dtype != F8 or t.dim() != 2 or t.stride(1) != 1:
+            raise TypeError(f"{n} must be a 2-D e4m3 tensor with unit inner stride")
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    args = GemmArgs(
+        a=_ptr(a), b=_ptr(b), lda=a.stride(0), ldb=b.stride(0), a_major=a_major, b_major=b_major,
+        sa=_ptr(sa), sa_stride_m=sa_strides[0], sa_stride_kb=sa_strides[1],
+        sb=_ptr(sb), sb_stride_n=sb_strides[0], sb_stride_kb=sb_strides[1], sb_gran_n=sb_gran_n,
+        d=_ptr(out), ldd=out.stride(0), out_dtype=TG_OUT_F32 if out.dtype == torch.float32 else TG_OUT_BF16,
+        M=M, N=N, K=K, status=_ptr(status))
+    _lib.check(_lib.load().tg_gemm_fp8_blockscaled(C.byref(args), _stream()), "tg_gemm_fp8_blockscaled")
+    return out
+
+
+def gemm_fwd(x_q, x_s, w_q, w_s, weight_tile=(128, 1), out_dtype=torch.bfloat16, status=None):
+    """y = x W.  x_q (M,K) rowwise-quantised with x_s (M,K/128); w_q (K,N) with
+    w_s (K/128,N) [weight_tile (128,1), from quantize_colwise] or (K/128,N/128)
+    [weight_tile (128,128), from quantize_block128]."""
+    M, K = x_q.shape
+    N = w_q.shape[1]
+    nkb = x_s.shape[1]
+    if tuple(weight_tile) == (128, 1):
+        sb_str, gran = (1, N), 1
+    else:
+        sb_str, gran = (1, w_s.shape[1]), 128
+    return gemm_blockscaled(x_q, w_q, x_s, w_s, M=M, N=N, K=K, a_major=TG_MAJOR_K, b_major=TG_MAJOR_MN,
+                            sa_strides=(nkb, 1), sb_strides=sb_str, sb_gran_n=gran, out_dtype=out_dtype, status=status)
+
+
+def gemm_dgrad(g_q, g_s, w_q, w_s, weight_tile=(128, 1), out_dtype=torch.bfloat16, status=None):
+    """dx = g W^T (contracts N).  g_q (M,N) rowwise-quantised, g_s (M,N/128); w_q (K,N)
+    quantised along N: w_s (K,N/128) [tile (128,1) mode: quantize_rowwise(W)] or the shared
+    (K/128,N/128) [tile (128,128)]."""
+    M, N = g_q.shape
+    K = w_q.shape[0]
+    if tuple(weight_tile) == (128, 1):
+        sb_str, gran = (w_s.shape[1], 1), 1
+    else:
+        sb_str, gran = (w_s.shape[1], 1), 128
+    return gemm_blockscaled(g_q, w_q, g_s, w_s, M=M, N=K, K=N, a_major=TG_MAJOR_K, b_major=TG_MAJOR_K,
+                            sa_strides=(g_s.shape[1], 1), sb_strides=sb_str, sb_gran_n=gran, out_dtype=out_dtype,
+                            status=status)
+
+
+def gemm_wgrad(x_qc, x_sc, g_qc, g_sc, out_dtype=torch.bfloat16, status=None):
+    """dW = x^T g (contracts the tokens).  x_qc (T,K), g_qc (T,N) colwise-quantised (128
+    tokens x 1), scales (ceil(T/128),K) and (ceil(T/128),N)."""
+    T, K = x_qc.shape
+    N = g_qc.shape[1]
+    return gemm_blockscaled(x_qc, g_qc, x_sc, g_sc, M=K, N=N, K=T, a_major=TG_MAJOR_MN, b_major=TG_MAJOR_MN,
+                            sa_strides=(1, K), sb_strides=(1, N), sb_gran_n=1, out_dtype=out_dtype, status=status)
