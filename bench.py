@@ -1,0 +1,365 @@
+#!/usr/bin/env python
+"""Benchmark of the FP8 hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (the configuration the headline metric is quoted on): ONE GPT DECODER LAYER'S
+block-scaled FP8 linear set, forward + dgrad + wgrad -- 32768 tokens, d_model 2048,
+weights (K,N) in {QKV (2048,6144), out-proj (2048,2048), MLP-up (2048,8192), MLP-down
+(8192,2048)}; activations/gradients ~N(0,1), weights ~N(0,0.02), bf16 before
+quantisation; e4m3 with float32 amax/448 scales, 1x128 tiles for activations and
+gradients, 128x128 tiles for weights (`--weight-tile 128x1` selects the reference's own
+granularity).  A "step" is one pass over the four layers: every quantiser launch and the
+three GEMMs of each.  metric = 6*M*sum(K*N) FLOP / step time, in TFLOP/s.
+
+  value     device-resident inputs, CUDA events around K steps, max over ranks
+  e2e       the same work through the public `fp8.block_scaled_matmul` autograd call with
+            HOST (pinned) inputs and results: H2D and D2H copies inside the timed region
+  roofline  the GEMM kernel: 2*M*N*K FLOP per launch / its mean CUDA-event duration,
+            against 2 x the measured bf16 cuBLAS peak (no FP8 peak is measured on this pool)
+  cpu_baseline  the CPU port of the oracle on the host cores, bounded token sample
+
+With N > 1 (launched under torchrun) every rank runs its own replica of the layer set on
+its own GPU -- these kernels share nothing across GPUs -- so scaling is "weak" and value is
+N * per-rank FLOP / max-over-ranks time.  The data-parallel training step, which has the
+gradient all-reduce, is reported in the "train_step" object when available.
+
+`--impl reference` times the reference's path on the host cores (the CPU port of the
+oracle: JAX, which the reference needs, cannot be installed here) and prints the same JSON
+line with "impl": "reference".
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+LAYER_SHAPES = [(2048, 6144), (2048, 2048), (2048, 8192), (8192, 2048)]   # (K, N)
+TOKENS = 32768
+METRIC = "fp8_linear_fwd_bwd_tflops"
+UNIT = "TFLOP/s"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--weight-tile", default="128x128", choices=["128x128", "128x1"])
+    ap.add_argument("--tokens", type=int, default=TOKENS)
+    ap.add_argument("--cpu-sample-tokens", type=int, default=2048)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-train-step", action="store_true")
+    return ap.parse_args()
+
+
+def layer_flops(tokens: int) -> float:
+    return sum(6.0 * tokens * k * n for k, n in LAYER_SHAPES)
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d["bf16_tflops_sustained"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+# ---------------------------------------------------------------------------------------------
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 200 ms while a region runs."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.lines = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        sm, smax, power, reasons = [], [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); smax.append(float(f[2])); power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(smax), "power_w_max": max(power),
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ---------------------------------------------------------------------------------------------
+def run_reference(args):
+    """The reference arm: the reference's path on the host cores (CPU port of the oracle)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+    from oracle import cpu_baseline as cb
+    cores = torch.get_num_threads()
+    m = args.cpu_sample_tokens
+    times = []
+    for i in range(args.warmup + args.steps):
+        t, flops = cb.time_linear_set(LAYER_SHAPES, m, seed=i)
+        if i >= args.warmup:
+            times.append(t)
+    sec = sum(times) / len(times)
+    val = flops / sec / 1e12
+    sample = f"{m} of {args.tokens} tokens per step, all four layer shapes, fwd+dgrad+wgrad"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "e4m3", "data": "synthetic",
+        "config": {"workload": "gpt_decoder_layer_fp8_linear_set_fwd_dgrad_wgrad", "tokens": args.tokens,
+                   "d_model": 2048, "shapes_KN": LAYER_SHAPES, "weight_tile": "128x128",
+                   "note": "CPU port of the oracle; the reference's JAX path cannot be installed"},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+# ---------------------------------------------------------------------------------------------
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from train_gpt_b200 import fp8, ops
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path); use --impl reference for the CPU arm")
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.gpus > 1 and world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE={world})")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    tile = (128, 128) if args.weight_tile == "128x128" else (128, 1)
+    M = args.tokens
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+
+    def randn(shape, std=1.0):
+        return (torch.randn(shape, device=dev, generator=gen) * std).to(torch.bfloat16)
+
+    layers = [{"x": randn((M, K)), "w": randn((K, N), 0.02), "g": randn((M, N))} for K, N in LAYER_SHAPES]
+    status = ops.new_status(dev)
+    gemm_events = []          # (start, end, flops) per GEMM launch inside the timed region
+    record = {"on": False}
+
+    def gemm(fn, *a, flops, **kw):
+        if record["on"]:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            out = fn(*a, status=status, **kw)
+            e1.record()
+            gemm_events.append((e0, e1, flops))
+            return out
+        return fn(*a, status=status, **kw)
+
+    launches = {"n": 0}
+
+    def step():
+        n = 0
+        for L in layers:
+            x, w, g = L["x"], L["w"], L["g"]
+            K, N = w.shape
+            f = 2.0 * M * K * N
+            x_q, x_s = ops.quantize_rowwise(x)
+            w_q, w_s = fp8.quantize_weight(w, tile)
+            L["y"] = gemm(ops.gemm_fwd, x_q, x_s, w_q, w_s, tile, flops=f)
+            g_q, g_s = ops.quantize_rowwise(g)
+            if tile == (128, 1):
+                wd_q, wd_s = ops.quantize_rowwise(w)
+                n += 1
+            else:
+                wd_q, wd_s = w_q, w_s          # 128x128 tiles serve both contractions
+            L["dx"] = gemm(ops.gemm_dgrad, g_q, g_s, wd_q, wd_s, tile, flops=f)
+            x_qc, x_sc = ops.quantize_colwise(x)
+            g_qc, g_sc = ops.quantize_colwise(g)
+            L["dw"] = gemm(ops.gemm_wgrad, x_qc, x_sc, g_qc, g_sc, flops=f)
+            n += 8
+        launches["n"] = n
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    if int(status.item()) != 0:
+        raise SystemExit(f"GEMM bounded wait expired (status {int(status.item())}); results invalid")
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    record["on"] = True
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    record["on"] = False
+    clocks = sampler.stop() if rank == 0 else None
+    ms_total = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms_total], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    if int(status.item()) != 0:
+        raise SystemExit(f"GEMM bounded wait expired (status {int(status.item())}); results invalid")
+    ms_step = ms_total / args.steps
+    flops_step = layer_flops(M)
+    value = world * flops_step / (ms_step * 1e-3) / 1e12
+
+    # ---- roofline of the dominant kernel (the GEMM) from the live events --------------------
+    peaks = measured_peaks()
+    g_ms = sum(a.elapsed_time(b) for a, b, _ in gemm_events)
+    g_flops = sum(f for _, _, f in gemm_events)
+    achieved = g_flops / (g_ms * 1e-3) / 1e12
+    fp8_peak = 2.0 * peaks["bf16_tflops_sustained"]
+    roofline = {
+        "bound": "tensor", "kernel": "gemm_fp8_blockscaled_kernel", "achieved": achieved, "peak": fp8_peak,
+        "unit": "TFLOP/s", "frac": achieved / fp8_peak, "traffic": None,
+        "peak_note": f"2 x {peaks['source']} sustained bf16 cuBLAS ({peaks['bf16_tflops_sustained']} TFLOP/s); no FP8 peak is measured on this pool",
+        "frac_of_spec_4500": achieved / 4500.0,
+        "gemm_launches_timed": len(gemm_events), "gemm_share_of_step": g_ms / ms_total,
+        "mean_launch_ms": g_ms / max(len(gemm_events), 1),
+    }
+
+    # ---- end to end through the public API with host buffers --------------------------------
+    e2e = None
+    if not args.no_e2e:
+        e2e = run_e2e(args, torch, fp8, dev, tile, world, dist)
+
+    out = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "e4m3",
+        "data": "synthetic",
+        "config": {"workload": "gpt_decoder_layer_fp8_linear_set_fwd_dgrad_wgrad", "tokens": M, "d_model": 2048,
+                   "shapes_KN": LAYER_SHAPES, "weight_tile": args.weight_tile, "act_tile": "1x128",
+                   "includes": "all quantiser launches + 3 GEMMs per layer",
+                   "l2": "inputs larger than L2 (134-537 MB per operand); no flush", "parallelism": f"replicas x{world}"},
+        "roofline": roofline, "clocks": clocks, "gpu_launches": launches["n"] * args.steps,
+    }
+    if e2e is not None:
+        out["e2e"] = e2e
+    if rank == 0 and not args.no_cpu_baseline and world == 1:
+        from oracle import cpu_baseline as cb
+        m = args.cpu_sample_tokens
+        sec, fl = cb.time_linear_set(LAYER_SHAPES, m)
+        out["cpu_baseline"] = {"value": fl / sec / 1e12, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+                               "sample": f"{m} of {M} tokens, all four layer shapes, fwd+dgrad+wgrad, one pass ({sec:.1f} s)"}
+    if not args.no_train_step:
+        try:
+            from train_gpt_b200 import step as step_mod
+            out["train_step"] = step_mod.bench_train_step(world, rank, dev, dist)
+        except ImportError:
+            pass
+    if rank == 0:
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_e2e(args, torch, fp8, dev, tile, world, dist):
+    """Same layer set through `block_scaled_matmul` + autograd, inputs and results on the host."""
+    M = args.tokens
+    steps = max(2, min(args.steps, 5))
+    host = []
+    for K, N in LAYER_SHAPES:
+        host.append({
+            "x": torch.randn((M, K), dtype=torch.bfloat16).pin_memory(),
+            "w": (torch.randn((K, N)) * 0.02).to(torch.bfloat16).pin_memory(),
+            "g": torch.randn((M, N), dtype=torch.bfloat16).pin_memory(),
+            "y": torch.empty((M, N), dtype=torch.bfloat16).pin_memory(),
+            "dx": torch.empty((M, K), dtype=torch.bfloat16).pin_memory(),
+            "dw": torch.empty((K, N), dtype=torch.bfloat16).pin_memory(),
+        })
+    h2d = sum(h[k].numel() * 2 for h in host for k in ("x", "w", "g"))
+    d2h = sum(h[k].numel() * 2 for h in host for k in ("y", "dx", "dw"))
+
+    def one():
+        for h in host:
+            x = h["x"].to(dev, non_blocking=True).requires_grad_(True)
+            w = h["w"].to(dev, non_blocking=True).requires_grad_(True)
+            g = h["g"].to(dev, non_blocking=True)
+            y = fp8.block_scaled_matmul(x, w, weight_tile=tile, backward="fp8")
+            y.backward(g)
+            h["y"].copy_(y.detach(), non_blocking=True)
+            h["dx"].copy_(x.grad, non_blocking=True)
+            h["dw"].copy_(w.grad, non_blocking=True)
+
+    for _ in range(2):
+        one()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        one()
+    e1.record()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return {"value": world * layer_flops(M) / (ms / steps * 1e-3) / 1e12, "unit": UNIT, "steps": steps,
+            "ms_per_step": ms / steps, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+            "api": "train_gpt_b200.fp8.block_scaled_matmul(x, w, weight_tile=..., backward='fp8') + autograd"}
+
+
+if __name__ == "__main__":
+    main()

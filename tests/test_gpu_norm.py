@@ -6,7 +6,7 @@ implementations, so `rnorm` may differ from the oracle's in the last bits; the t
 therefore (a) bound |rnorm - oracle| by 2 ulp and (b) demand BIT-EXACT outputs against the
 oracle evaluated with the kernel's own rnorm.  The backward's two row/column sums are
 float32 reductions too: dx may differ by one bf16 ulp on a small fraction of elements
-(bound: 1 ulp, < 1 % of elements), dgamma by 2^-7 relative (one bf16 ulp) of its RMS.
+(bound: 1 ulp + 2^-14 RMS for cancelled values, < 1 % of elements), dgamma by 2^-7 relative (one bf16 ulp) of its RMS.
 """
 import numpy as np
 import pytest
@@ -98,8 +98,9 @@ def test_backward(shape):
     dx, dgamma = ops.rmsnorm_bwd(to_torch_bf16(x), to_torch_bf16(gamma), to_torch_bf16(gy), eps)
     dx_ref, dgamma_ref = no.rms_norm_bwd(x, gamma, gy, eps)
     a, b = from_torch_bf16(dx).astype(np.float32), dx_ref.astype(np.float32)
-    ulp = np.maximum(np.abs(b), 2.0 ** -126) * 2.0 ** -7
-    assert (np.abs(a - b) <= ulp).all() and (a != b).mean() < 1e-2
+    # one bf16 ulp, plus the float32 cancellation error of gs - normed*dot on near-zero results
+    tol = np.abs(b) * 2.0 ** -7 + np.sqrt(np.mean(b * b)) * 2.0 ** -14
+    assert (np.abs(a - b) <= tol).all() and (a != b).mean() < 1e-2
     dg, dg_ref = from_torch_bf16(dgamma).astype(np.float32), dgamma_ref.astype(np.float32)
     assert np.abs(dg - dg_ref).max() <= 2.0 ** -7 * np.sqrt(np.mean(dg_ref ** 2)) + 2.0 ** -7 * np.abs(dg_ref).max()
 

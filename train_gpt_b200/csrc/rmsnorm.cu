@@ -15,6 +15,26 @@ namespace tg {
 
 constexpr int kNormWarps = 8;  // warps per thread block
 
+
+// Sum of squares of the 8 bf16 values in w, as a balanced tree (keeps the rounding error of
+// a row's variance at a few 2^-24 regardless of outliers).
+__device__ __forceinline__ float sumsq8(const uint4& w) {
+  const float a0 = bf16lo(w.x), a1 = bf16hi(w.x), a2 = bf16lo(w.y), a3 = bf16hi(w.y);
+  const float a4 = bf16lo(w.z), a5 = bf16hi(w.z), a6 = bf16lo(w.w), a7 = bf16hi(w.w);
+  const float t0 = fmaf(a1, a1, a0 * a0), t1 = fmaf(a3, a3, a2 * a2);
+  const float t2 = fmaf(a5, a5, a4 * a4), t3 = fmaf(a7, a7, a6 * a6);
+  return (t0 + t1) + (t2 + t3);
+}
+
+template <int N>
+__device__ __forceinline__ float tree_sum(float (&v)[N]) {
+#pragma unroll
+  for (int stride = 1; stride < N; stride *= 2)
+#pragma unroll
+    for (int i = 0; i + stride < N; i += 2 * stride) v[i] += v[i + stride];
+  return v[0];
+}
+
 template <int WPR>
 __device__ __forceinline__ float row_sum(float v, float* s_red, int warp, int lane) {
 #pragma unroll
@@ -41,8 +61,6 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   constexpr int RPB = kNormWarps / WPR;  // rows per block per iteration
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int col_base = (warp % WPR) * NCHUNK * 256 + lane * 8;
-  const float inv_note = 0.f;
-  (void)inv_note;
 
   uint4 gm[NCHUNK];
 #pragma unroll
@@ -62,20 +80,10 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
       const int col = col_base + c * 256;
       w[c] = (row_ok && col < cols) ? ld_nc_v4(x + row * cols + col) : make_uint4(0, 0, 0, 0);
     }
-    float ss = 0.f;
+    float part[NCHUNK];
 #pragma unroll
-    for (int c = 0; c < NCHUNK; ++c) {
-      float a;
-      a = bf16lo(w[c].x); ss = fmaf(a, a, ss);
-      a = bf16hi(w[c].x); ss = fmaf(a, a, ss);
-      a = bf16lo(w[c].y); ss = fmaf(a, a, ss);
-      a = bf16hi(w[c].y); ss = fmaf(a, a, ss);
-      a = bf16lo(w[c].z); ss = fmaf(a, a, ss);
-      a = bf16hi(w[c].z); ss = fmaf(a, a, ss);
-      a = bf16lo(w[c].w); ss = fmaf(a, a, ss);
-      a = bf16hi(w[c].w); ss = fmaf(a, a, ss);
-    }
-    ss = row_sum<WPR>(ss, s_red[it & 1], warp, lane);
+    for (int c = 0; c < NCHUNK; ++c) part[c] = sumsq8(w[c]);
+    const float ss = row_sum<WPR>(tree_sum(part), s_red[it & 1], warp, lane);
     const float var = __fdiv_rn(ss, float(cols));
     const float rn = __frsqrt_rn(var + eps);
     if (row_ok && rnorm_out != nullptr && lane == 0 && (warp % WPR) == 0) rnorm_out[row] = rn;
@@ -154,23 +162,17 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
       w[c] = ok ? ld_nc_v4(x + row * cols + col) : make_uint4(0, 0, 0, 0);
       gv[c] = ok ? ld_nc_v4(g + row * cols + col) : make_uint4(0, 0, 0, 0);
     }
-    float ss = 0.f;
+    float part[NCHUNK];
 #pragma unroll
-    for (int c = 0; c < NCHUNK; ++c) {
-      const uint32_t xi[4] = {w[c].x, w[c].y, w[c].z, w[c].w};
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float a = bf16lo(xi[j]); ss = fmaf(a, a, ss);
-        a = bf16hi(xi[j]); ss = fmaf(a, a, ss);
-      }
-    }
-    ss = row_sum<WPR>(ss, s_red[(it & 1) * 2], warp, lane);
+    for (int c = 0; c < NCHUNK; ++c) part[c] = sumsq8(w[c]);
+    const float ss = row_sum<WPR>(tree_sum(part), s_red[(it & 1) * 2], warp, lane);
     const float rn = __frsqrt_rn(__fdiv_rn(ss, float(cols)) + eps);
 
     // gs*normed summed over the row; dgamma accumulation in the same sweep
-    float dsum = 0.f;
+    float dpart[NCHUNK];
 #pragma unroll
     for (int c = 0; c < NCHUNK; ++c) {
+      float dsum = 0.f;
       const int col = col_base + c * 256;
       const uint4 gm = (col < cols) ? *reinterpret_cast<const uint4*>(gamma + col) : make_uint4(0, 0, 0, 0);
       const uint32_t xi[4] = {w[c].x, w[c].y, w[c].z, w[c].w};
@@ -185,8 +187,9 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
         dsum = fmaf(__fmul_rn(g0, bf16lo(mi[j])), n0, dsum);
         dsum = fmaf(__fmul_rn(g1, bf16hi(mi[j])), n1, dsum);
       }
+      dpart[c] = dsum;
     }
-    dsum = row_sum<WPR>(dsum, s_red[(it & 1) * 2 + 1], warp, lane);
+    const float dsum = row_sum<WPR>(tree_sum(dpart), s_red[(it & 1) * 2 + 1], warp, lane);
     const float dot = __fmul_rn(dsum, inv_d);
 
 #pragma unroll
