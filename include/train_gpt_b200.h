@@ -71,6 +71,14 @@ int tg_quantize_colwise(const void* x, void* q, float* scales,
 int tg_quantize_block128(const void* x, void* q, float* scales,
                          int64_t rows, int64_t cols, void* stream);
 
+/* No counterpart in the reference.  The quantisers replace the per-element IEEE division
+ * x / scale by one reciprocal per tile and a fused correction step; this runs that
+ * shortcut against div.rn.f32 over the COMPLETE input domain (every finite bf16 amax,
+ * every bf16 |x| <= amax; 2^31 pairs) on the current device.
+ *   counts [4] uint64, device memory: [0] pairs checked, [1] bytes that differ with the
+ *   bare x*(1/s), [2] with one correction step (the shipped form -- must be 0), [3] with two. */
+int tg_selftest_quantise_division(uint64_t* counts, void* stream);
+
 /* ---- RMSNorm ---------------------------------------------------------------------- */
 
 /* mode for the norm entry points */

@@ -127,3 +127,12 @@ def test_full_size_properties():
     q_ref, s_ref = fo.quantize_to_fp8(x[rows].float().cpu().numpy())
     assert np.array_equal(f8_bytes(q[rows]), q_ref.view(np.uint8))
     assert np.array_equal(_bits(s[rows].cpu().numpy()), _bits(s_ref))
+
+
+def test_division_shortcut_is_exact_over_the_whole_domain():
+    """Every (bf16 amax, bf16 |x| <= amax) pair: the shipped reciprocal + one-correction form
+    gives the same byte as IEEE division."""
+    from train_gpt_b200 import ops
+    pairs, bare, shipped, two = ops.selftest_quantise_division()
+    assert pairs == 1065402240        # sum over finite bf16 amax of #{x : |x| <= amax}
+    assert shipped == 0 and two == 0, (pairs, bare, shipped, two)

@@ -9,7 +9,9 @@ import ctypes as C
 import os
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "libtrain_gpt_b200.so")
+# TRAIN_GPT_B200_LIB points at another build of the same library (e.g. one with -G or
+# different tile constants); it is never a different implementation.
+LIB_PATH = os.environ.get("TRAIN_GPT_B200_LIB") or os.path.join(_PKG, "libtrain_gpt_b200.so")
 
 TG_OK, TG_ERR_SHAPE, TG_ERR_ALIGN, TG_ERR_ARCH, TG_ERR_CUDA, TG_ERR_TOO_LARGE = 0, -1, -2, -3, -4, -5
 TG_NORM_FUSED, TG_NORM_PURE = 0, 1
@@ -37,6 +39,7 @@ SYMBOLS = {
     "tg_quantize_rowwise": (_i, [_p, _p, _p, _i64, _i64, _p]),
     "tg_quantize_colwise": (_i, [_p, _p, _p, _i64, _i64, _p]),
     "tg_quantize_block128": (_i, [_p, _p, _p, _i64, _i64, _p]),
+    "tg_selftest_quantise_division": (_i, [_p, _p]),
     "tg_rmsnorm_fwd": (_i, [_p, _p, _f, _p, _p, _i64, _i64, _i, _p]),
     "tg_rmsnorm_quant_fwd": (_i, [_p, _p, _f, _p, _p, _p, _p, _i64, _i64, _i, _p]),
     "tg_rmsnorm_bwd_scratch_bytes": (_i64, [_i64, _i64]),

@@ -61,13 +61,51 @@ __device__ __forceinline__ uint32_t cvt_e4m3x2(float lo, float hi) {
   return r;
 }
 
+// ---- x / scale, correctly rounded, without a per-element IEEE division -------------------
+// The quantised byte is RNE_e4m3(RN_f32(x / s)).  A per-element div.rn.f32 costs ~10
+// instructions plus a MUFU.RCP, which makes the streaming quantisers compute-bound.  The
+// tile shares one scale, so the reciprocal r = RN(1/s) is taken once and each element gets
+//     q0 = x * r;  q = fma(-fma(q0, s, -x), r, q0)
+// (one Markstein correction step).  The input domain is tiny -- x is a bf16 value and s is
+// max(amax/448, 1e-30) for a bf16 amax >= |x| -- so equality of the resulting BYTE with the
+// IEEE-division path is verified exhaustively over the whole domain by
+// tg_selftest_quantise_division (2^31 pairs), not argued.  Non-finite scales (NaN or Inf in
+// the tile) take the IEEE division so that they propagate exactly as jnp does.
+struct QuantDiv {
+  float s, r;
+  bool finite;
+  __device__ __forceinline__ explicit QuantDiv(float scale) {
+    s = scale;
+    r = __frcp_rn(scale);
+    finite = fabsf(scale) <= 3.402823466e38f;
+  }
+  template <int SCHEME = 2>
+  __device__ __forceinline__ float div(float x) const {
+    if (SCHEME == 0) return __fdiv_rn(x, s);
+    float q = __fmul_rn(x, r);
+    // residual taken as q*s - x and subtracted, so that x = -0 stays -0 (fma(+0, s, -0) is +0)
+    if (SCHEME >= 2) q = __fmaf_rn(-__fmaf_rn(q, s, -x), r, q);
+    if (SCHEME >= 3) q = __fmaf_rn(-__fmaf_rn(q, s, -x), r, q);
+    return q;
+  }
+};
+
 // Quantise the 8 bf16 values held in w (as loaded from memory, element 0 in the low half
 // of w.x) with `scale`, returning 8 e4m3 bytes in memory order.
 __device__ __forceinline__ uint2 quantize8(const uint4& w, float scale) {
-  uint32_t b0 = cvt_e4m3x2(__fdiv_rn(bf16lo(w.x), scale), __fdiv_rn(bf16hi(w.x), scale));
-  uint32_t b1 = cvt_e4m3x2(__fdiv_rn(bf16lo(w.y), scale), __fdiv_rn(bf16hi(w.y), scale));
-  uint32_t b2 = cvt_e4m3x2(__fdiv_rn(bf16lo(w.z), scale), __fdiv_rn(bf16hi(w.z), scale));
-  uint32_t b3 = cvt_e4m3x2(__fdiv_rn(bf16lo(w.w), scale), __fdiv_rn(bf16hi(w.w), scale));
+  const QuantDiv d(scale);
+  uint32_t b0, b1, b2, b3;
+  if (d.finite) {
+    b0 = cvt_e4m3x2(d.div(bf16lo(w.x)), d.div(bf16hi(w.x)));
+    b1 = cvt_e4m3x2(d.div(bf16lo(w.y)), d.div(bf16hi(w.y)));
+    b2 = cvt_e4m3x2(d.div(bf16lo(w.z)), d.div(bf16hi(w.z)));
+    b3 = cvt_e4m3x2(d.div(bf16lo(w.w)), d.div(bf16hi(w.w)));
+  } else {
+    b0 = cvt_e4m3x2(__fdiv_rn(bf16lo(w.x), scale), __fdiv_rn(bf16hi(w.x), scale));
+    b1 = cvt_e4m3x2(__fdiv_rn(bf16lo(w.y), scale), __fdiv_rn(bf16hi(w.y), scale));
+    b2 = cvt_e4m3x2(__fdiv_rn(bf16lo(w.z), scale), __fdiv_rn(bf16hi(w.z), scale));
+    b3 = cvt_e4m3x2(__fdiv_rn(bf16lo(w.w), scale), __fdiv_rn(bf16hi(w.w), scale));
+  }
   return make_uint2(b0 | (b1 << 16), b2 | (b3 << 16));
 }
 

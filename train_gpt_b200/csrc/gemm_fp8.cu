@@ -6,15 +6,21 @@
 // The scales are float32 (amax/448), not powers of two, so the tensor core's own
 // block-scale path (UE8M0 factors) cannot apply them bit-faithfully.  Instead every
 // 128-deep contraction block is issued as its own tcgen05.mma chain into a fresh TMEM
-// accumulator buffer, and four "promotion" warps pull each finished buffer out of TMEM
-// (tcgen05.ld), multiply by SA*SB and add into float32 register accumulators with packed
-// f32x2 FMAs while the tensor core fills the next buffer.  Four 128-column TMEM buffers
-// rotate (all 512 columns).
+// accumulator buffer, and sixteen "promotion" warps pull each finished buffer out of TMEM
+// (tcgen05.ld), hand it straight back to the tensor core, then multiply by SA*SB and add
+// into float32 register accumulators with packed f32x2 FMAs while the tensor core fills
+// the next buffers.  Four 128-column TMEM buffers rotate (all 512 columns).
 //
-// Warp roles in the 192-thread CTA (persistent, one CTA per SM, tiles round-robin):
-//   warp 0      one lane issues TMA loads (A and B tiles, 128 x 128 bytes, 128B swizzle)
-//   warp 1      allocates TMEM; one lane issues tcgen05.mma + tcgen05.commit
-//   warps 2..5  promotion + store of the finished 128 x 128 tile (TMEM lane quarter = warp % 4)
+// Warp roles in the 608-thread CTA (persistent, one CTA per SM, tiles round-robin):
+//   warp 0       TMA producer: A and B tiles, 128 x 128 bytes each, 128B swizzle
+//   warps 1, 2   MMA issuers, alternating contraction blocks (a single issuing thread's
+//                wait -> 4 x tcgen05.mma -> commit loop takes longer than the tensor core
+//                needs for the block; two threads keep its queue fed); warp 1 owns TMEM
+//   warps 3..18  promotion + epilogue; warp w may touch TMEM lanes 32*(w%4).. (a hardware
+//                rule) and owns accumulator columns 32*((w-3)/4)..: four warps per
+//                scheduler hide each other's TMEM-load latency
+// The finished tile goes registers -> swizzled shared memory -> one TMA store per
+// 128-byte-wide box, so the global writes are full lines whatever the row pitch.
 //
 // Operand orientation is data, not code: the TMA box is 128 bytes x 128 rows for both
 // K-major and MN-major storage (only the coordinates swap), and the shared-memory operand
@@ -23,7 +29,7 @@
 //
 // Every wait on an mbarrier is bounded: when the limit runs out the waiting role raises a
 // CTA-wide abort flag, stores a code in *status, and all roles fall through to the common
-// teardown (TMEM is always freed).
+// teardown (TMEM is always freed; the promotion warps keep their named barriers in step).
 #include <cuda.h>
 
 #include "common.cuh"
@@ -34,34 +40,43 @@ constexpr int BM = 128;          // tile rows (TMEM lanes)
 constexpr int BN = 128;          // tile columns (TMEM columns per buffer)
 constexpr int BK = 128;          // contraction block = scale granularity (fp8.py:27)
 constexpr int UMMA_K = 32;       // K of one tcgen05.mma.kind::f8f6f4
-constexpr int kStages = 6;       // shared-memory pipeline depth
 constexpr int kTmemBufs = 4;     // accumulator buffers in TMEM
 constexpr int kTmemCols = kTmemBufs * BN;  // 512
 constexpr int kTileBytes = BM * BK;        // 16384, A or B tile
-constexpr int kGemmThreads = 192;
-constexpr int kPromoThreads = 128;
+constexpr int kIssuers = 2;                      // MMA-issuing warps
+constexpr int kFirstPromoWarp = 1 + kIssuers;    // 3
+constexpr int kColGroups = 4;                    // promotion warps per TMEM lane quarter
+constexpr int kPromoWarps = 4 * kColGroups;      // 16
+constexpr int kPromoThreads = 32 * kPromoWarps;  // 512
+constexpr int kColsPerWarp = BN / kColGroups;    // 32 accumulator columns per promotion warp
+constexpr int kGemmThreads = 32 * kFirstPromoWarp + kPromoThreads;  // 608
+constexpr int kBoxBytes = 128 * 128;             // one TMA-store box: 128 rows x 128 bytes
 constexpr long long kWaitLimitCycles = 4000000000LL;  // ~2 s at 2 GHz
 
+// Shared-memory plan (offsets from the 1024-aligned base of dynamic shared memory).  The
+// output staging area is 2 boxes for bf16 and 4 for float32; the pipeline depth takes what
+// is left of the 227 KB.
+template <bool OUT_F32>
 struct SmemLayout {
-  // offsets from the 1024-aligned base of dynamic shared memory
+  static constexpr int stages = OUT_F32 ? 4 : 5;
+  static constexpr int out_boxes = OUT_F32 ? 4 : 2;
   static constexpr int a = 0;
-  static constexpr int b = kStages * kTileBytes;
-  static constexpr int sb = 2 * kStages * kTileBytes;            // float[2][BN]
-  static constexpr int bars = sb + 2 * BN * 4;                   // uint64 barriers
-  static constexpr int n_bars = 2 * kStages + 2 * kTmemBufs + 1;
+  static constexpr int b = stages * kTileBytes;
+  static constexpr int out = 2 * stages * kTileBytes;
+  static constexpr int sb = out + out_boxes * kBoxBytes;                 // float[kPromoWarps][2][kColsPerWarp]
+  static constexpr int bars = sb + kPromoWarps * 2 * kColsPerWarp * 4;   // uint64 barriers
+  static constexpr int n_bars = 2 * stages + 2 * kTmemBufs + kIssuers;
   static constexpr int tmem_ptr = bars + n_bars * 8;
   static constexpr int abort_flag = tmem_ptr + 4;
   static constexpr int total = abort_flag + 4;
+  static constexpr int bytes = total + 1024;  // slack for manual alignment
 };
-constexpr int kGemmSmemBytes = SmemLayout::total + 1024;  // slack for manual alignment
 
 struct GemmParams {
   const float* sa;
   long long sa_sm, sa_sk;
   const float* sb;
   long long sb_sn, sb_sk;
-  void* d;
-  long long ldd;
   int M, N, nkb;
   int a_mn, b_mn;       // 1 = MN-major storage
   int tiles_m, tiles_n;
@@ -72,6 +87,17 @@ struct GemmParams {
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// One lane of a converged warp (warp-uniform callers keep operands in uniform registers).
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred = 0;
+  asm volatile(
+      "{\n\t.reg .b32 rx;\n\t.reg .pred px;\n\t"
+      "elect.sync rx|px, 0xffffffff;\n\t"
+      "@px mov.s32 %0, 1;\n\t}"
+      : "+r"(pred));
+  return pred != 0;
 }
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -179,10 +205,6 @@ __device__ __forceinline__ void tmem_wait_ld(uint32_t (&v)[32]) {
       : "memory");
 }
 
-__device__ __forceinline__ void promo_bar_sync() {
-  asm volatile("bar.sync 1, %0;" ::"n"(kPromoThreads) : "memory");
-}
-
 // Shared-memory operand descriptor, 128-byte swizzle, 8-row groups 1024 bytes apart.
 //   bits  0-13 start address >> 4      bits 16-29 leading byte offset >> 4
 //   bits 32-45 stride byte offset >> 4 bits 46-47 descriptor version (1 on sm_100)
@@ -200,24 +222,42 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
   return d;
 }
 
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all committed stores have finished READING shared memory (the staging area may be reused)
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// make this thread's generic-proxy shared-memory writes visible to the async (TMA) proxy
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void promo_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kPromoThreads) : "memory"); }
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+
 // ---- kernel ----------------------------------------------------------------------------
 
 template <int SB_GRAN, bool OUT_F32>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                            const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+                            const __grid_constant__ CUtensorMap tmap_b,
+                            const __grid_constant__ CUtensorMap tmap_d, const GemmParams p) {
+  using L = SmemLayout<OUT_F32>;
+  constexpr int kStages = L::stages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t sbase = smem_u32(smem);
-  const uint32_t bar0 = sbase + SmemLayout::bars;
+  const uint32_t bar0 = sbase + L::bars;
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (kStages + s); };
   auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * kStages + b); };
   auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * kStages + kTmemBufs + b); };
-  const uint32_t drain_bar = bar0 + 8u * (2 * kStages + 2 * kTmemBufs);
-  volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem + SmemLayout::tmem_ptr);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SmemLayout::abort_flag);
-  float* s_sb = reinterpret_cast<float*>(smem + SmemLayout::sb);
+  auto drain_bar = [&](int i) { return bar0 + 8u * (2 * kStages + 2 * kTmemBufs + i); };
+  volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem + L::tmem_ptr);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::abort_flag);
+  float* s_sb = reinterpret_cast<float*>(smem + L::sb);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_tiles = p.tiles_m * p.tiles_n;
@@ -229,16 +269,17 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     for (int b = 0; b < kTmemBufs; ++b) {
       mbar_init(tfull_bar(b), 1);
-      mbar_init(tempty_bar(b), kPromoThreads);
+      mbar_init(tempty_bar(b), kPromoWarps);
     }
-    mbar_init(drain_bar, 1);
+    for (int i = 0; i < kIssuers; ++i) mbar_init(drain_bar(i), 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_a)) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_b)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_d)) : "memory");
   }
   if (warp == 1) {
-    tmem_alloc(sbase + SmemLayout::tmem_ptr, kTmemCols);
+    tmem_alloc(sbase + L::tmem_ptr, kTmemCols);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -248,57 +289,77 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   if (warp == 0) {
     // ------------------------------ TMA producer ---------------------------------------
-    if (lane == 0) {
-      uint32_t it = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
-        const int m0 = (tile / p.tiles_n) * BM, n0 = (tile % p.tiles_n) * BN;
-        for (int kb = 0; kb < p.nkb; ++kb, ++it) {
-          const int s = it % kStages;
-          if (!(ok = mbar_wait(empty_bar(s), ((it / kStages) & 1u) ^ 1u, abort_flag, p.status, 1u))) break;
+    // The whole warp walks the loop (uniform control flow); one elected lane issues.
+    uint32_t it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
+      const int m0 = (tile / p.tiles_n) * BM, n0 = (tile % p.tiles_n) * BN;
+      for (int kb = 0; kb < p.nkb; ++kb, ++it) {
+        const int s = it % kStages;
+        ok = __all_sync(0xffffffffu, mbar_wait(empty_bar(s), ((it / kStages) & 1u) ^ 1u, abort_flag, p.status, 1u));
+        if (!ok) break;
+        if (elect_one()) {
           mbar_expect_tx(full_bar(s), 2 * kTileBytes);
           const int k0 = kb * BK;
-          tma_load_2d(sbase + SmemLayout::a + s * kTileBytes, &tmap_a, full_bar(s), p.a_mn ? m0 : k0, p.a_mn ? k0 : m0);
-          tma_load_2d(sbase + SmemLayout::b + s * kTileBytes, &tmap_b, full_bar(s), p.b_mn ? n0 : k0, p.b_mn ? k0 : n0);
+          tma_load_2d(sbase + L::a + s * kTileBytes, &tmap_a, full_bar(s), p.a_mn ? m0 : k0, p.a_mn ? k0 : m0);
+          tma_load_2d(sbase + L::b + s * kTileBytes, &tmap_b, full_bar(s), p.b_mn ? n0 : k0, p.b_mn ? k0 : n0);
         }
+        __syncwarp();
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------ MMA issuer -----------------------------------------
-    if (lane == 0) {
-      // instruction descriptor: D f32 (bit 4), A/B e4m3 (0), major bits 15/16, N>>3 at 17, M>>4 at 24
-      const uint32_t idesc = (1u << 4) | (uint32_t(p.a_mn) << 15) | (uint32_t(p.b_mn) << 16) |
-                             (uint32_t(BN >> 3) << 17) | (uint32_t(BM >> 4) << 24);
-      // descriptor start-address step per UMMA_K: 32 bytes along a K-major row, 32 rows of 128 B otherwise
-      const uint32_t a_step = p.a_mn ? (UMMA_K * 128) >> 4 : UMMA_K >> 4;
-      const uint32_t b_step = p.b_mn ? (UMMA_K * 128) >> 4 : UMMA_K >> 4;
-      uint32_t it = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
-        for (int kb = 0; kb < p.nkb; ++kb, ++it) {
-          const int s = it % kStages, buf = it % kTmemBufs;
-          if (!(ok = mbar_wait(tempty_bar(buf), ((it / kTmemBufs) & 1u) ^ 1u, abort_flag, p.status, 2u))) break;
-          if (!(ok = mbar_wait(full_bar(s), (it / kStages) & 1u, abort_flag, p.status, 3u))) break;
-          tc_fence_after();
-          const uint64_t a_desc = make_smem_desc(sbase + SmemLayout::a + s * kTileBytes);
-          const uint64_t b_desc = make_smem_desc(sbase + SmemLayout::b + s * kTileBytes);
-          const uint32_t d_tmem = tmem_base + uint32_t(buf * BN);
+  } else if (warp < kFirstPromoWarp) {
+    // ------------------------------ MMA issuers ----------------------------------------
+    // Issuer i takes the contraction blocks with (global block counter) % kIssuers == i.
+    // Blocks are independent: each has its own TMEM buffer and shared-memory stage.
+    const int issuer = warp - 1;
+    // instruction descriptor: D f32 (bit 4), A/B e4m3 (0), major bits 15/16, N>>3 at 17, M>>4 at 24
+    const uint32_t idesc = (1u << 4) | (uint32_t(p.a_mn) << 15) | (uint32_t(p.b_mn) << 16) |
+                           (uint32_t(BN >> 3) << 17) | (uint32_t(BM >> 4) << 24);
+    // descriptor start-address step per UMMA_K: 32 bytes along a K-major row, 32 rows of 128 B otherwise
+    const uint32_t a_step = p.a_mn ? (UMMA_K * 128) >> 4 : UMMA_K >> 4;
+    const uint32_t b_step = p.b_mn ? (UMMA_K * 128) >> 4 : UMMA_K >> 4;
+    const uint64_t a_desc0 = make_smem_desc(sbase + L::a);
+    const uint64_t b_desc0 = make_smem_desc(sbase + L::b);
+    int my_tiles = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) ++my_tiles;
+    const uint32_t total = uint32_t(my_tiles) * uint32_t(p.nkb);
+    bool ok = true;
+    for (uint32_t it = issuer; ok && it < total; it += kIssuers) {
+      const int s = it % kStages, buf = it % kTmemBufs;
+      ok = __all_sync(0xffffffffu, mbar_wait(tempty_bar(buf), ((it / kTmemBufs) & 1u) ^ 1u, abort_flag, p.status, 2u) &&
+                                       mbar_wait(full_bar(s), (it / kStages) & 1u, abort_flag, p.status, 3u));
+      if (!ok) break;
+      tc_fence_after();
+      if (elect_one()) {
+        const uint64_t a_desc = a_desc0 + uint64_t((s * kTileBytes) >> 4);
+        const uint64_t b_desc = b_desc0 + uint64_t((s * kTileBytes) >> 4);
+        const uint32_t d_tmem = tmem_base + uint32_t(buf * BN);
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k)
-            umma_f8(d_tmem, a_desc + uint64_t(k * a_step), b_desc + uint64_t(k * b_step), idesc, k > 0 ? 1u : 0u);
-          umma_commit(empty_bar(s));    // shared-memory stage free once these MMAs retire
-          umma_commit(tfull_bar(buf));  // accumulator buffer ready for promotion
-        }
+        for (int k = 0; k < BK / UMMA_K; ++k)
+          umma_f8(d_tmem, a_desc + uint64_t(k * a_step), b_desc + uint64_t(k * b_step), idesc, k > 0 ? 1u : 0u);
+        // ONE commit per block: the promotion warps see the accumulator buffer ready, and the
+        // first of them frees the shared-memory stage on this thread's behalf.
+        umma_commit(tfull_bar(buf));
       }
-      // make sure nothing issued here is still running when TMEM is freed
-      umma_commit(drain_bar);
-      mbar_wait(drain_bar, 0u, abort_flag, p.status, 4u);
+      __syncwarp();
     }
+    // make sure nothing issued here is still running when TMEM is freed
+    if (elect_one()) {
+      umma_commit(drain_bar(issuer));
+      mbar_wait(drain_bar(issuer), 0u, abort_flag, p.status, 4u);
+    }
+    __syncwarp();
   } else {
-    // ------------------------------ promotion + store ----------------------------------
+    // ------------------------------ promotion + epilogue --------------------------------
+    const int pw = warp - kFirstPromoWarp;     // 0..kPromoWarps-1
     const int quarter = warp & 3;              // TMEM lanes this warp may touch
+    const int cg = pw >> 2;                    // column group: columns [cg*32, cg*32+32) of the tile
     const int r = quarter * 32 + lane;         // row inside the tile
-    const int pt = threadIdx.x - 64;           // 0..127 among promotion threads
+    const int c0 = cg * kColsPerWarp;
+    float* sb_stage = s_sb + pw * (2 * kColsPerWarp);   // warp-private, double-buffered
+    const bool store_thread = (pw == 0 && lane == 0);
+    // this thread's 16-byte chunks in the swizzled staging area (row r of box(es))
+    const uint32_t out_row = sbase + L::out + uint32_t(r) * 128u;
     uint32_t it = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
@@ -309,14 +370,14 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const float* sb_ptr;
       bool sb_ok = true;
       if (SB_GRAN == 1) {
-        sb_ok = (n0 + pt) < p.N;
-        sb_ptr = p.sb + (long long)(sb_ok ? n0 + pt : 0) * p.sb_sn;
+        sb_ok = (n0 + c0 + lane) < p.N;        // lane j stages the scale of column c0 + j
+        sb_ptr = p.sb + (long long)(sb_ok ? n0 + c0 + lane : 0) * p.sb_sn;
       } else {
         sb_ptr = p.sb + (long long)(n0 / 128) * p.sb_sn;
       }
-      float2 acc[BN / 2];
+      float2 acc[kColsPerWarp / 2];
 #pragma unroll
-      for (int j = 0; j < BN / 2; ++j) acc[j] = make_float2(0.f, 0.f);
+      for (int j = 0; j < kColsPerWarp / 2; ++j) acc[j] = make_float2(0.f, 0.f);
 
       float sa_next = m_ok ? __ldg(sa_ptr) : 0.f;
       float sb_next = sb_ok ? __ldg(sb_ptr) : 0.f;
@@ -327,68 +388,80 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
           sa_next = m_ok ? __ldg(sa_ptr + (long long)(kb + 1) * p.sa_sk) : 0.f;
           sb_next = sb_ok ? __ldg(sb_ptr + (long long)(kb + 1) * p.sb_sk) : 0.f;
         }
-        float* sb_stage = s_sb + (it & 1u) * BN;
+        float* stage = sb_stage + (it & 1u) * kColsPerWarp;
         if (SB_GRAN == 1) {
-          sb_stage[pt] = sb_v;
-          promo_bar_sync();
+          stage[lane] = sb_v;
+          __syncwarp();
         }
-        // After an abort the remaining iterations only keep the named barrier above in
-        // step (no thread may leave while others still wait on it); TMEM is not touched.
+        // After an abort the remaining iterations only keep loop counters and barriers in step.
         if (ok) ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar(buf), (it / kTmemBufs) & 1u, abort_flag, p.status, 5u));
         if (!ok) continue;
+        // the block's MMAs have retired: its shared-memory stage can be refilled
+        if (store_thread) mbar_arrive(empty_bar(it % kStages));
         tc_fence_after();
-        const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(buf * BN);
-        const float2 sa2 = make_float2(sa_v, sa_v);
-        const float s_scalar = sa_v * sb_v;
-        const float2 s2 = make_float2(s_scalar, s_scalar);
-        uint32_t v[2][32];
-        tmem_ld32(taddr, v[0]);
-#pragma unroll
-        for (int c = 0; c < BN / 32; ++c) {
-          tmem_wait_ld(v[c & 1]);
-          if (c + 1 < BN / 32) tmem_ld32(taddr + uint32_t((c + 1) * 32), v[(c + 1) & 1]);
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const float2 pv = make_float2(__uint_as_float(v[c & 1][2 * j]), __uint_as_float(v[c & 1][2 * j + 1]));
-            if (SB_GRAN == 1) {
-              const float2 sbv = *reinterpret_cast<const float2*>(sb_stage + c * 32 + 2 * j);
-              acc[c * 16 + j] = __ffma2_rn(__fmul2_rn(pv, sbv), sa2, acc[c * 16 + j]);
-            } else {
-              acc[c * 16 + j] = __ffma2_rn(pv, s2, acc[c * 16 + j]);
-            }
-          }
-        }
-        // all of this thread's reads of the buffer have completed (wait::ld above)
+        uint32_t v[32];
+        tmem_ld32(tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(buf * BN + c0), v);
+        tmem_wait_ld(v);
+        // the partial sums are in registers: hand the buffer back to the tensor core at once
         tc_fence_before();
-        mbar_arrive(tempty_bar(buf));
-      }
-      if (!ok) continue;
-      // ---- store the finished tile row: 128 columns, contiguous per thread -------------
-      if (m_ok) {
-        if (OUT_F32) {
-          float* drow = static_cast<float*>(p.d) + (long long)m * p.ldd + n0;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar(buf));
+        if (SB_GRAN == 1) {
+          const float2 sa2 = make_float2(sa_v, sa_v);
 #pragma unroll
-          for (int j = 0; j < BN / 4; ++j) {
-            if (n0 + j * 4 < p.N)
-              *reinterpret_cast<float4*>(drow + j * 4) =
-                  make_float4(acc[2 * j].x, acc[2 * j].y, acc[2 * j + 1].x, acc[2 * j + 1].y);
+          for (int j = 0; j < kColsPerWarp / 4; ++j) {
+            const float4 sb4 = *reinterpret_cast<const float4*>(stage + 4 * j);
+            const float2 p0 = make_float2(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]));
+            const float2 p1 = make_float2(__uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+            acc[2 * j] = __ffma2_rn(__fmul2_rn(p0, make_float2(sb4.x, sb4.y)), sa2, acc[2 * j]);
+            acc[2 * j + 1] = __ffma2_rn(__fmul2_rn(p1, make_float2(sb4.z, sb4.w)), sa2, acc[2 * j + 1]);
           }
         } else {
-          __nv_bfloat16* drow = static_cast<__nv_bfloat16*>(p.d) + (long long)m * p.ldd + n0;
+          const float s_scalar = sa_v * sb_v;
+          const float2 s2 = make_float2(s_scalar, s_scalar);
 #pragma unroll
-          for (int j = 0; j < BN / 8; ++j) {
-            if (n0 + j * 8 < p.N) {
-              uint4 o;
-              o.x = pack_bf16x2(acc[4 * j].x, acc[4 * j].y);
-              o.y = pack_bf16x2(acc[4 * j + 1].x, acc[4 * j + 1].y);
-              o.z = pack_bf16x2(acc[4 * j + 2].x, acc[4 * j + 2].y);
-              o.w = pack_bf16x2(acc[4 * j + 3].x, acc[4 * j + 3].y);
-              *reinterpret_cast<uint4*>(drow + j * 8) = o;
-            }
+          for (int j = 0; j < kColsPerWarp / 2; ++j) {
+            const float2 pv = make_float2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+            acc[j] = __ffma2_rn(pv, s2, acc[j]);
           }
         }
       }
+      // ---- epilogue: registers -> swizzled staging -> TMA store --------------------------
+      // Every promotion thread takes both named barriers for every tile, aborting or not.
+      if (store_thread) tma_store_wait_read();  // the previous tile's stores have let go of the staging area
+      promo_bar_sync();
+      if (ok) {
+        if (OUT_F32) {
+          // 32 columns x 4 B = one 128-byte box row; box index = column group
+          const uint32_t base = out_row + uint32_t(cg) * kBoxBytes;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            st_shared_v4(base + (uint32_t(j ^ (r & 7)) << 4), __float_as_uint(acc[2 * j].x), __float_as_uint(acc[2 * j].y),
+                         __float_as_uint(acc[2 * j + 1].x), __float_as_uint(acc[2 * j + 1].y));
+        } else {
+          // 32 columns x 2 B = half a box row; two column groups share a box
+          const uint32_t base = out_row + uint32_t(cg >> 1) * kBoxBytes;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int chunk = (cg & 1) * 4 + j;
+            st_shared_v4(base + (uint32_t(chunk ^ (r & 7)) << 4), pack_bf16x2(acc[4 * j].x, acc[4 * j].y),
+                         pack_bf16x2(acc[4 * j + 1].x, acc[4 * j + 1].y), pack_bf16x2(acc[4 * j + 2].x, acc[4 * j + 2].y),
+                         pack_bf16x2(acc[4 * j + 3].x, acc[4 * j + 3].y));
+          }
+        }
+        fence_proxy_async_smem();
+      }
+      promo_bar_sync();
+      if (store_thread && ok) {
+        constexpr int kBoxCols = OUT_F32 ? 32 : 64;  // elements per 128-byte box row
+#pragma unroll
+        for (int b = 0; b < L::out_boxes; ++b)
+          if (n0 + b * kBoxCols < p.N)
+            tma_store_2d(&tmap_d, sbase + L::out + b * kBoxBytes, n0 + b * kBoxCols, m0);
+        tma_store_commit();
+      }
     }
+    if (store_thread) tma_store_wait_read();
   }
 
   // ------------------------------ teardown ----------------------------------------------
@@ -421,34 +494,38 @@ static int get_encode_fn(EncodeTiledFn* out) {
   return TG_OK;
 }
 
-// 2-D byte tensor [outer][inner], row pitch `pitch` bytes, box 128 x 128, 128-byte swizzle.
-static int make_tmap(CUtensorMap* map, const void* base, int64_t inner, int64_t outer, int64_t pitch) {
+// 2-D tensor [outer][inner] of `esize`-byte elements, row pitch `pitch_bytes`; box = 128 bytes
+// of the inner dimension x 128 rows, 128-byte swizzle.
+static int make_tmap(CUtensorMap* map, CUtensorMapDataType dt, int esize, const void* base, int64_t inner,
+                     int64_t outer, int64_t pitch_bytes) {
   EncodeTiledFn enc;
   if (int rc = get_encode_fn(&enc)) return rc;
   cuuint64_t dims[2] = {cuuint64_t(inner), cuuint64_t(outer)};
-  cuuint64_t strides[1] = {cuuint64_t(pitch)};
-  cuuint32_t box[2] = {128, 128};
+  cuuint64_t strides[1] = {cuuint64_t(pitch_bytes)};
+  cuuint32_t box[2] = {cuuint32_t(128 / esize), 128};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = enc(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return record_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
   return TG_OK;
 }
 
 template <int SB_GRAN, bool OUT_F32>
-static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t st) {
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, const GemmParams& p,
+                       int grid, cudaStream_t st) {
   auto kern = gemm_fp8_blockscaled_kernel<SB_GRAN, OUT_F32>;
-  static bool attr_set = false;  // per instantiation; set once per process (per-device attribute: set each time on a new device)
-  static int attr_dev = -1;
+  constexpr int smem = SmemLayout<OUT_F32>::bytes;
+  static_assert(smem <= 227 * 1024, "shared-memory plan exceeds the 227 KB a CTA may use");
+  // the attribute is per device: set it once for each device this instantiation runs on
+  static bool attr_set[64] = {};
   int dev = 0;
   TG_CUDA_CHECK(cudaGetDevice(&dev));
-  if (!attr_set || attr_dev != dev) {
-    TG_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes));
-    attr_set = true;
-    attr_dev = dev;
+  if (dev < 0 || dev >= 64) return TG_ERR_SHAPE;
+  if (!attr_set[dev]) {
+    TG_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    attr_set[dev] = true;
   }
-  kern<<<grid, kGemmThreads, kGemmSmemBytes, st>>>(ta, tb, p);
+  kern<<<grid, kGemmThreads, smem, st>>>(ta, tb, td, p);
   TG_CUDA_CHECK(cudaGetLastError());
   return TG_OK;
 }
@@ -474,27 +551,29 @@ extern "C" int tg_gemm_fp8_blockscaled(const tg_gemm_args* a, void* stream) {
   if (!aligned16(a->a) || !aligned16(a->b) || !aligned16(a->d)) return TG_ERR_ALIGN;
   if (int rc = check_arch()) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool f32 = a->out_dtype == TG_OUT_F32;
+  const int esz = f32 ? 4 : 2;
   if (a->K == 0) {
-    const size_t esz = a->out_dtype == TG_OUT_F32 ? 4 : 2;
     TG_CUDA_CHECK(cudaMemset2DAsync(a->d, size_t(a->ldd) * esz, 0, size_t(a->N) * esz, size_t(a->M), st));
     return TG_OK;
   }
-  CUtensorMap ta, tb;
-  if (int rc = make_tmap(&ta, a->a, a_inner, a_outer, a->lda)) return rc;
-  if (int rc = make_tmap(&tb, a->b, b_inner, b_outer, a->ldb)) return rc;
+  CUtensorMap ta, tb, td;
+  if (int rc = make_tmap(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a->a, a_inner, a_outer, a->lda)) return rc;
+  if (int rc = make_tmap(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a->b, b_inner, b_outer, a->ldb)) return rc;
+  if (int rc = make_tmap(&td, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, esz, a->d, a->N,
+                         a->M, a->ldd * esz))
+    return rc;
   GemmParams p;
   p.sa = a->sa; p.sa_sm = a->sa_stride_m; p.sa_sk = a->sa_stride_kb;
   p.sb = a->sb; p.sb_sn = a->sb_stride_n; p.sb_sk = a->sb_stride_kb;
-  p.d = a->d; p.ldd = a->ldd;
   p.M = int(a->M); p.N = int(a->N); p.nkb = int((a->K + BK - 1) / BK);
   p.a_mn = a->a_major == TG_MAJOR_MN; p.b_mn = a->b_major == TG_MAJOR_MN;
   p.tiles_m = int((a->M + BM - 1) / BM); p.tiles_n = int((a->N + BN - 1) / BN);
   p.status = a->status;
   const int64_t n_tiles = int64_t(p.tiles_m) * p.tiles_n;
-  if (n_tiles > INT32_MAX) return TG_ERR_TOO_LARGE;
+  if (n_tiles > INT32_MAX || n_tiles * p.nkb > INT32_MAX) return TG_ERR_TOO_LARGE;
   const int sms = sm_count();
   const int grid = int(n_tiles < sms ? n_tiles : sms);
-  const bool f32 = a->out_dtype == TG_OUT_F32;
-  if (a->sb_gran_n == 1) return f32 ? launch_gemm<1, true>(ta, tb, p, grid, st) : launch_gemm<1, false>(ta, tb, p, grid, st);
-  return f32 ? launch_gemm<128, true>(ta, tb, p, grid, st) : launch_gemm<128, false>(ta, tb, p, grid, st);
+  if (a->sb_gran_n == 1) return f32 ? launch_gemm<1, true>(ta, tb, td, p, grid, st) : launch_gemm<1, false>(ta, tb, td, p, grid, st);
+  return f32 ? launch_gemm<128, true>(ta, tb, td, p, grid, st) : launch_gemm<128, false>(ta, tb, td, p, grid, st);
 }

@@ -44,35 +44,38 @@ quantize_rowwise_kernel(const uint4* __restrict__ x, uint2* __restrict__ q,
 
 // ---------------------------------------------------------------------------------------
 // 128 x 1 tiles (a scale per column per block of 128 rows).  A thread block owns a
-// 128-row x 256-column panel: 32 lanes x 8 columns across, 8 warps x 16 rows down.  Each
-// thread holds its 16 x 8 values in registers, column maxima are combined across the 8
-// warps through shared memory, then the same registers are divided and stored.
+// 128-row x 128-column panel: a half-warp spans the 128 columns (16 lanes x 8 columns), so
+// each of the 16 half-warps owns every 16th row (8 rows per thread, kept in registers).
+// Column maxima are combined across the half-warps through shared memory, then the same
+// registers are divided and stored.  ~90 registers: two blocks per SM, so one block's loads
+// overlap the other's arithmetic.
 // ---------------------------------------------------------------------------------------
-constexpr int kColPanelCols = 256;
-constexpr int kColWarps = 8;
-constexpr int kColRowsPerWarp = kTile / kColWarps;  // 16
+constexpr int kColPanelCols = 128;
+constexpr int kColThreads = 256;
+constexpr int kColHalfWarps = kColThreads / 16;           // 16
+constexpr int kColRowsPerThread = kTile / kColHalfWarps;  // 8
 
-__global__ void __launch_bounds__(kColWarps * 32)
+__global__ void __launch_bounds__(kColThreads, 2)
 quantize_colwise_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
                         float* __restrict__ scales, int64_t rows, int64_t cols) {
-  __shared__ float s_max[kColWarps][kColPanelCols];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int64_t col0 = int64_t(blockIdx.x) * kColPanelCols + lane * 8;
+  __shared__ float s_max[kColHalfWarps][kColPanelCols];
+  const int cx = threadIdx.x & 15, hw = threadIdx.x >> 4;
+  const int64_t col0 = int64_t(blockIdx.x) * kColPanelCols + cx * 8;
   const int64_t row_blk = blockIdx.y;
-  const int64_t row0 = row_blk * kTile + warp * kColRowsPerWarp;
-  const bool col_ok = col0 < cols;  // cols % 8 == 0
+  const int64_t row0 = row_blk * kTile + hw;  // this thread's rows: row0 + 16 r
+  const bool col_ok = col0 < cols;            // cols % 8 == 0
 
-  uint4 w[kColRowsPerWarp];
+  uint4 w[kColRowsPerThread];
 #pragma unroll
-  for (int r = 0; r < kColRowsPerWarp; ++r) {
-    const int64_t row = row0 + r;
+  for (int r = 0; r < kColRowsPerThread; ++r) {
+    const int64_t row = row0 + r * kColHalfWarps;
     w[r] = (col_ok && row < rows) ? ld_nc_v4(x + row * cols + col0) : make_uint4(0, 0, 0, 0);
   }
   float m[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) m[j] = 0.f;
 #pragma unroll
-  for (int r = 0; r < kColRowsPerWarp; ++r) {
+  for (int r = 0; r < kColRowsPerThread; ++r) {
     m[0] = max_nan(m[0], fabsf(bf16lo(w[r].x)));
     m[1] = max_nan(m[1], fabsf(bf16hi(w[r].x)));
     m[2] = max_nan(m[2], fabsf(bf16lo(w[r].y)));
@@ -82,33 +85,51 @@ quantize_colwise_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict
     m[6] = max_nan(m[6], fabsf(bf16lo(w[r].w)));
     m[7] = max_nan(m[7], fabsf(bf16hi(w[r].w)));
   }
-  float4* dst = reinterpret_cast<float4*>(&s_max[warp][lane * 8]);
+  float4* dst = reinterpret_cast<float4*>(&s_max[hw][cx * 8]);
   dst[0] = make_float4(m[0], m[1], m[2], m[3]);
   dst[1] = make_float4(m[4], m[5], m[6], m[7]);
   __syncthreads();
   float s[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
-    float v = s_max[0][lane * 8 + j];
+    float v = s_max[0][cx * 8 + j];
 #pragma unroll
-    for (int wv = 1; wv < kColWarps; ++wv) v = max_nan(v, s_max[wv][lane * 8 + j]);
+    for (int h = 1; h < kColHalfWarps; ++h) v = max_nan(v, s_max[h][cx * 8 + j]);
     s[j] = scale_from_amax(v);
   }
   if (!col_ok) return;
-  if (warp == 0) {
+  if (hw == 0) {
     float4* sp = reinterpret_cast<float4*>(scales + row_blk * cols + col0);
     sp[0] = make_float4(s[0], s[1], s[2], s[3]);
     sp[1] = make_float4(s[4], s[5], s[6], s[7]);
   }
+  bool all_finite = true;
+  float rc[8];
 #pragma unroll
-  for (int r = 0; r < kColRowsPerWarp; ++r) {
-    const int64_t row = row0 + r;
+  for (int j = 0; j < 8; ++j) {
+    rc[j] = __frcp_rn(s[j]);
+    all_finite = all_finite && (fabsf(s[j]) <= 3.402823466e38f);
+  }
+#pragma unroll
+  for (int r = 0; r < kColRowsPerThread; ++r) {
+    const int64_t row = row0 + r * kColHalfWarps;
     if (row >= rows) break;
     const uint4 v = w[r];
-    uint32_t b0 = cvt_e4m3x2(__fdiv_rn(bf16lo(v.x), s[0]), __fdiv_rn(bf16hi(v.x), s[1]));
-    uint32_t b1 = cvt_e4m3x2(__fdiv_rn(bf16lo(v.y), s[2]), __fdiv_rn(bf16hi(v.y), s[3]));
-    uint32_t b2 = cvt_e4m3x2(__fdiv_rn(bf16lo(v.z), s[4]), __fdiv_rn(bf16hi(v.z), s[5]));
-    uint32_t b3 = cvt_e4m3x2(__fdiv_rn(bf16lo(v.w), s[6]), __fdiv_rn(bf16hi(v.w), s[7]));
+    const float xs[8] = {bf16lo(v.x), bf16hi(v.x), bf16lo(v.y), bf16hi(v.y),
+                         bf16lo(v.z), bf16hi(v.z), bf16lo(v.w), bf16hi(v.w)};
+    float qv[8];
+    if (all_finite) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {  // x/s as q0 = x*r, q = fma(-fma(q0,s,-x), r, q0): see QuantDiv
+        const float q0 = __fmul_rn(xs[j], rc[j]);
+        qv[j] = __fmaf_rn(-__fmaf_rn(q0, s[j], -xs[j]), rc[j], q0);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) qv[j] = __fdiv_rn(xs[j], s[j]);
+    }
+    const uint32_t b0 = cvt_e4m3x2(qv[0], qv[1]), b1 = cvt_e4m3x2(qv[2], qv[3]);
+    const uint32_t b2 = cvt_e4m3x2(qv[4], qv[5]), b3 = cvt_e4m3x2(qv[6], qv[7]);
     *reinterpret_cast<uint2*>(q + row * cols + col0) = make_uint2(b0 | (b1 << 16), b2 | (b3 << 16));
   }
 }
@@ -178,7 +199,7 @@ extern "C" int tg_quantize_colwise(const void* x, void* q, float* scales, int64_
   if (int rc = check_arch()) return rc;
   const int64_t gx = (cols + kColPanelCols - 1) / kColPanelCols, gy = (rows + kTile - 1) / kTile;
   if (gy > 65535) return TG_ERR_TOO_LARGE;
-  quantize_colwise_kernel<<<dim3(unsigned(gx), unsigned(gy)), kColWarps * 32, 0,
+  quantize_colwise_kernel<<<dim3(unsigned(gx), unsigned(gy)), kColThreads, 0,
                             static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(q), scales, rows, cols);
   TG_CUDA_CHECK(cudaGetLastError());

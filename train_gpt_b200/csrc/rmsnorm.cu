@@ -52,7 +52,7 @@ __device__ __forceinline__ float row_sum(float v, float* s_red, int warp, int la
 }
 
 template <int NCHUNK, int WPR, bool QUANT>
-__global__ void __launch_bounds__(kNormWarps * 32)
+__global__ void __launch_bounds__(kNormWarps * 32, 2)
 rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma,
                    float eps, uint8_t* __restrict__ q, float* __restrict__ scales,
                    __nv_bfloat16* __restrict__ y, float* __restrict__ rnorm_out, int64_t rows,
@@ -62,12 +62,10 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int col_base = (warp % WPR) * NCHUNK * 256 + lane * 8;
 
-  uint4 gm[NCHUNK];
-#pragma unroll
-  for (int c = 0; c < NCHUNK; ++c) {
-    const int col = col_base + c * 256;
-    gm[c] = (col < cols) ? *reinterpret_cast<const uint4*>(gamma + col) : make_uint4(0, 0, 0, 0);
-  }
+  // gamma lives in shared memory (not registers) so that two blocks fit on an SM
+  extern __shared__ uint4 s_gamma[];
+  for (int i = threadIdx.x; i < cols / 8; i += blockDim.x) s_gamma[i] = reinterpret_cast<const uint4*>(gamma)[i];
+  __syncthreads();
 
   int it = 0;
   for (int64_t row_base = int64_t(blockIdx.x) * RPB; row_base < rows;
@@ -93,7 +91,8 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     for (int c = 0; c < NCHUNK; ++c) {
       const int col = col_base + c * 256;
       const uint32_t xi[4] = {w[c].x, w[c].y, w[c].z, w[c].w};
-      const uint32_t gi[4] = {gm[c].x, gm[c].y, gm[c].z, gm[c].w};
+      const uint4 gm = (col < cols) ? s_gamma[col >> 3] : make_uint4(0, 0, 0, 0);
+      const uint32_t gi[4] = {gm.x, gm.y, gm.z, gm.w};
       uint4 yo;
       uint32_t* yp = &yo.x;
 #pragma unroll
@@ -285,7 +284,7 @@ static int launch_fwd(const void* x, const void* gamma, float eps, void* q, floa
   const int blocks = norm_blocks(rows, g.wpr, 16);
 #define TG_FWD_CASE(NC, W)                                                                          \
   if (g.nchunk == NC && g.wpr == W) {                                                               \
-    rmsnorm_fwd_kernel<NC, W, QUANT><<<blocks, kNormWarps * 32, 0, st>>>(                           \
+    rmsnorm_fwd_kernel<NC, W, QUANT><<<blocks, kNormWarps * 32, size_t(cols) * 2, st>>>(                           \
         static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(gamma), eps,        \
         static_cast<uint8_t*>(q), scales, static_cast<__nv_bfloat16*>(y), rnorm, rows, int(cols),   \
         mode);                                                                                      \

@@ -1,0 +1,165 @@
+"""Per-kernel microbenchmarks on one GPU (the counterpart of train-gpt's bench_fp8.py GEMM
+table and debug_bf16_norm.py `bench_norm`): achieved GB/s for the streaming kernels,
+TFLOP/s for the GEMMs, against the algorithmic bytes / FLOPs of each.
+
+    python -m train_gpt_b200.microbench quant  [--rows 32768 --cols 2048]
+    python -m train_gpt_b200.microbench norm   [--rows 32768 --cols 2048]
+    python -m train_gpt_b200.microbench gemm   [--m 32768 --n 6144 --k 2048 --mode fwd|dgrad|wgrad --tile 128x128|128x1]
+    python -m train_gpt_b200.microbench sweep  (square and skinny GEMM shapes)
+
+Timing: CUDA events on the launching stream, `--warmup` untimed launches, then `--iters`
+samples (ten back-to-back launches each for the streaming kernels, one for a GEMM); operands rotate through enough distinct buffers to exceed the
+126 MB L2 between reuses (streaming kernels) or are larger than L2 themselves.  Prints one
+JSON object per kernel.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+
+import torch
+
+from . import fp8, ops
+
+L2_BYTES = 126e6
+
+
+def _time(fn, n_variants, warmup, iters, batch=1):
+    """Median and best time of one launch.  `batch` launches go between each pair of events
+    (rotating through the input variants) so that host launch gaps do not count against
+    kernels that run for tens of microseconds."""
+    for i in range(warmup):
+        fn(i % n_variants)
+    torch.cuda.synchronize()
+    ts = []
+    k = 0
+    for _ in range(iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(batch):
+            fn(k % n_variants)
+            k += 1
+        e1.record()
+        e1.synchronize()
+        ts.append(e0.elapsed_time(e1) / batch)
+    return statistics.median(ts), min(ts)
+
+
+def _outlier_input(rows, cols, n, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    xs = []
+    for _ in range(n):
+        x = torch.randn(rows, cols, device="cuda", generator=g)
+        x = torch.where(torch.rand(rows, cols, device="cuda", generator=g) < 1e-3, x * 50, x)
+        xs.append(x.to(torch.bfloat16))
+    return xs
+
+
+def _report(name, ms_med, ms_min, bytes_=None, flops=None, **extra):
+    out = {"kernel": name, "ms_median": round(ms_med, 5), "ms_min": round(ms_min, 5)}
+    if bytes_ is not None:
+        out["algorithmic_MB"] = round(bytes_ / 1e6, 3)
+        out["GBps_median"] = round(bytes_ / ms_med / 1e6, 1)
+        out["GBps_best"] = round(bytes_ / ms_min / 1e6, 1)
+    if flops is not None:
+        out["GFLOP"] = round(flops / 1e9, 2)
+        out["TFLOPs_median"] = round(flops / ms_med / 1e9, 1)
+        out["TFLOPs_best"] = round(flops / ms_min / 1e9, 1)
+    out.update(extra)
+    print(json.dumps(out), flush=True)
+    return out
+
+
+def bench_quant(rows, cols, warmup, iters):
+    E = rows * cols
+    n = max(2, int(L2_BYTES * 2 // (E * 2)) + 1)
+    xs = _outlier_input(rows, cols, n)
+    m, b = _time(lambda i: ops.quantize_rowwise(xs[i]), n, warmup, iters, batch=10)
+    _report("quantize_rowwise", m, b, bytes_=3.03125 * E, shape=[rows, cols])
+    m, b = _time(lambda i: ops.quantize_colwise(xs[i]), n, warmup, iters, batch=10)
+    _report("quantize_colwise", m, b, bytes_=3.03125 * E, shape=[rows, cols])
+    m, b = _time(lambda i: ops.quantize_block128(xs[i]), n, warmup, iters, batch=10)
+    _report("quantize_block128", m, b, bytes_=(3.0 + 4.0 / 16384) * E, shape=[rows, cols])
+
+
+def bench_norm(rows, cols, warmup, iters):
+    E = rows * cols
+    n = max(2, int(L2_BYTES * 2 // (E * 2)) + 1)
+    xs = _outlier_input(rows, cols, n)
+    gs = [torch.randn(rows, cols, device="cuda").to(torch.bfloat16) for _ in range(n)]
+    gamma = (1 + 0.1 * torch.randn(cols, device="cuda")).to(torch.bfloat16)
+    eps = 1e-6
+    m, b = _time(lambda i: ops.rmsnorm_quant_fwd(xs[i], gamma, eps), n, warmup, iters, batch=10)
+    _report("rmsnorm_quant_fwd", m, b, bytes_=3.03125 * E + 2 * cols, shape=[rows, cols])
+    m, b = _time(lambda i: ops.rmsnorm_fwd(xs[i], gamma, eps), n, warmup, iters, batch=10)
+    _report("rmsnorm_fwd", m, b, bytes_=4.0 * E + 2 * cols, shape=[rows, cols])
+    m, b = _time(lambda i: ops.rmsnorm_bwd(xs[i], gamma, gs[i], eps), n, warmup, iters, batch=10)
+    _report("rmsnorm_bwd", m, b, bytes_=6.0 * E + 4 * cols, shape=[rows, cols])
+
+
+def _gemm_case(M, N, K, mode, tile, warmup, iters, student_t=False):
+    """M tokens, linear layer (K -> N).  mode picks which of the layer's three GEMMs runs."""
+    g = torch.Generator(device="cuda").manual_seed(0)
+    if student_t:
+        # Student-t(3) = N(0,1) / sqrt(chi2(3)/3), drawn on the device
+        chi = sum(torch.randn(M, K, device="cuda", generator=g) ** 2 for _ in range(3)) / 3.0
+        x = (torch.randn(M, K, device="cuda", generator=g) / chi.sqrt()).to(torch.bfloat16)
+        del chi
+    else:
+        x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    w = (0.02 * torch.randn(K, N, device="cuda", generator=g)).to(torch.bfloat16)
+    gr = torch.randn(M, N, device="cuda", generator=g).to(torch.bfloat16)
+    st = ops.new_status("cuda")
+    if mode == "fwd":
+        a_q, a_s = ops.quantize_rowwise(x)
+        w_q, w_s = fp8.quantize_weight(w, tile)
+        fn = lambda i: ops.gemm_fwd(a_q, a_s, w_q, w_s, tile, status=st)
+    elif mode == "dgrad":
+        g_q, g_s = ops.quantize_rowwise(gr)
+        w_q, w_s = ops.quantize_rowwise(w) if tile == (128, 1) else ops.quantize_block128(w)
+        fn = lambda i: ops.gemm_dgrad(g_q, g_s, w_q, w_s, tile, status=st)
+    else:
+        x_q, x_s = ops.quantize_colwise(x)
+        g_q, g_s = ops.quantize_colwise(gr)
+        fn = lambda i: ops.gemm_wgrad(x_q, x_s, g_q, g_s, status=st)
+    m, b = _time(fn, 1, warmup, iters)
+    if int(st.item()) != 0:
+        raise RuntimeError(f"GEMM bounded wait expired, status {int(st.item())}")
+    return _report(f"gemm_{mode}", m, b, flops=2.0 * M * N * K, tokens=M, K=K, N=N,
+                   weight_tile=f"{tile[0]}x{tile[1]}", pct_of_4500=round(2.0 * M * N * K / m / 1e9 / 45.0, 1))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["quant", "norm", "gemm", "sweep"])
+    ap.add_argument("--rows", type=int, default=32768)
+    ap.add_argument("--cols", type=int, default=2048)
+    ap.add_argument("--m", type=int, default=32768)
+    ap.add_argument("--n", type=int, default=6144)
+    ap.add_argument("--k", type=int, default=2048)
+    ap.add_argument("--mode", default="fwd", choices=["fwd", "dgrad", "wgrad", "all"])
+    ap.add_argument("--tile", default="128x128", choices=["128x128", "128x1"])
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--iters", type=int, default=30)
+    a = ap.parse_args()
+    tile = (128, 128) if a.tile == "128x128" else (128, 1)
+    if a.what == "quant":
+        bench_quant(a.rows, a.cols, a.warmup, a.iters)
+    elif a.what == "norm":
+        bench_norm(a.rows, a.cols, a.warmup, a.iters)
+    elif a.what == "gemm":
+        for mode in (["fwd", "dgrad", "wgrad"] if a.mode == "all" else [a.mode]):
+            _gemm_case(a.m, a.n, a.k, mode, tile, a.warmup, a.iters)
+    else:
+        # the shape sweep of the benchmark configurations: squares, then skinny M with K=N=8192
+        for n in (1024, 2048, 4096, 8192, 16384):
+            for mode in ("fwd", "dgrad", "wgrad"):
+                _gemm_case(n, n, n, mode, tile, a.warmup, max(5, a.iters // 3), student_t=True)
+        for m in (16, 64, 256):
+            for mode in ("fwd", "dgrad", "wgrad"):
+                _gemm_case(m, 8192, 8192, mode, tile, a.warmup, a.iters, student_t=True)
+
+
+if __name__ == "__main__":
+    main()

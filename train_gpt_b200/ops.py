@@ -80,6 +80,14 @@ def quantize_block128(x: torch.Tensor):
     return q, s
 
 
+def selftest_quantise_division(device="cuda"):
+    """Exhaustive check of the quantisers' division shortcut on the device.  Returns
+    (pairs checked, mismatches of x*(1/s), of the shipped one-step form, of two steps)."""
+    counts = torch.zeros(4, dtype=torch.int64, device=device)
+    _lib.check(_lib.load().tg_selftest_quantise_division(_ptr(counts), _stream()), "tg_selftest_quantise_division")
+    return tuple(int(v) for v in counts.cpu())
+
+
 # ---- RMSNorm ------------------------------------------------------------------------------
 
 def rmsnorm_fwd(x, gamma, eps: float, pure: bool = False, want_rnorm: bool = False):
