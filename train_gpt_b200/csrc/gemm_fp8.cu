@@ -7,20 +7,24 @@
 // block-scale path (UE8M0 factors) cannot apply them bit-faithfully.  Instead every
 // 128-deep contraction block is issued as its own tcgen05.mma chain into a fresh TMEM
 // accumulator buffer, and sixteen "promotion" warps pull each finished buffer out of TMEM
-// (tcgen05.ld), hand it straight back to the tensor core, then multiply by SA*SB and add
-// into float32 register accumulators with packed f32x2 FMAs while the tensor core fills
-// the next buffers.  Four 128-column TMEM buffers rotate (all 512 columns).
+// (tcgen05.ld), hand it back to the tensor core, multiply by SA*SB and add into float32
+// register accumulators with packed f32x2 FMAs while the tensor core fills the next buffer.
 //
-// Warp roles in the 608-thread CTA (persistent, one CTA per SM, tiles round-robin):
-//   warp 0       TMA producer: A and B tiles, 128 x 128 bytes each, 128B swizzle
-//   warps 1, 2   MMA issuers, alternating contraction blocks (a single issuing thread's
-//                wait -> 4 x tcgen05.mma -> commit loop takes longer than the tensor core
-//                needs for the block; two threads keep its queue fed); warp 1 owns TMEM
-//   warps 3..18  promotion + epilogue; warp w may touch TMEM lanes 32*(w%4).. (a hardware
-//                rule) and owns accumulator columns 32*((w-3)/4)..: four warps per
-//                scheduler hide each other's TMEM-load latency
-// The finished tile goes registers -> swizzled shared memory -> one TMA store per
-// 128-byte-wide box, so the global writes are full lines whatever the row pitch.
+// Tile: 128 rows x BN columns, BN = 256 (two 256-column TMEM buffers) or 128 (four).  The
+// wide tile halves the shared-memory and L2 traffic per FLOP and doubles the tensor-core
+// time per issued instruction, which is what keeps the single-thread issue loop and the
+// barrier round trips off the critical path.
+//
+// Warp roles in the 576-thread CTA (persistent, one CTA per SM, tiles round-robin):
+//   warp 0       TMA producer: A (one 128 x 128-byte box) and B (BN/128 boxes), 128B swizzle
+//   warp 1       MMA issuer (owns the TMEM allocation).  Its barrier polls for block k+1 are
+//                issued before the tcgen05.mma of block k, so their latency hides under the
+//                ~300-cycle issue of four MMAs and a commit
+//   warps 2..17  promotion + epilogue; warp w may touch TMEM lanes 32*(w%4).. (a hardware
+//                rule) and owns accumulator columns (BN/4)*((w-2)/4)..; four warps per
+//                scheduler hide each other's TMEM-load latency.  Each warp stores its own
+//                32 x BN/4 piece of the tile: registers -> its private swizzled staging
+//                area -> TMA store, with no cross-warp barrier.
 //
 // Operand orientation is data, not code: the TMA box is 128 bytes x 128 rows for both
 // K-major and MN-major storage (only the coordinates swap), and the shared-memory operand
@@ -29,7 +33,7 @@
 //
 // Every wait on an mbarrier is bounded: when the limit runs out the waiting role raises a
 // CTA-wide abort flag, stores a code in *status, and all roles fall through to the common
-// teardown (TMEM is always freed; the promotion warps keep their named barriers in step).
+// teardown (TMEM is always freed).
 #include <cuda.h>
 
 #include "common.cuh"
@@ -37,39 +41,50 @@
 namespace tg {
 
 constexpr int BM = 128;          // tile rows (TMEM lanes)
-constexpr int BN = 128;          // tile columns (TMEM columns per buffer)
 constexpr int BK = 128;          // contraction block = scale granularity (fp8.py:27)
 constexpr int UMMA_K = 32;       // K of one tcgen05.mma.kind::f8f6f4
-constexpr int kTmemBufs = 4;     // accumulator buffers in TMEM
-constexpr int kTmemCols = kTmemBufs * BN;  // 512
-constexpr int kTileBytes = BM * BK;        // 16384, A or B tile
-constexpr int kIssuers = 2;                      // MMA-issuing warps
-constexpr int kFirstPromoWarp = 1 + kIssuers;    // 3
-constexpr int kColGroups = 4;                    // promotion warps per TMEM lane quarter
-constexpr int kPromoWarps = 4 * kColGroups;      // 16
-constexpr int kPromoThreads = 32 * kPromoWarps;  // 512
-constexpr int kColsPerWarp = BN / kColGroups;    // 32 accumulator columns per promotion warp
-constexpr int kGemmThreads = 32 * kFirstPromoWarp + kPromoThreads;  // 608
-constexpr int kBoxBytes = 128 * 128;             // one TMA-store box: 128 rows x 128 bytes
+constexpr int kTmemCols = 512;
+constexpr int kTileBytes = 128 * 128;            // one operand TMA box: 128 rows x 128 bytes
+constexpr int kIssuers = 1;                      // MMA-issuing warps
+constexpr int kFirstPromoWarp = 1 + kIssuers;    // 2
+constexpr int kPromoWarps = 16;
+constexpr int kGemmThreads = 32 * (kFirstPromoWarp + kPromoWarps);  // 576: 112 registers per thread
+constexpr int kSmemLimit = 227 * 1024;
 constexpr long long kWaitLimitCycles = 4000000000LL;  // ~2 s at 2 GHz
 
-// Shared-memory plan (offsets from the 1024-aligned base of dynamic shared memory).  The
-// output staging area is 2 boxes for bf16 and 4 for float32; the pipeline depth takes what
-// is left of the 227 KB.
-template <bool OUT_F32>
-struct SmemLayout {
-  static constexpr int stages = OUT_F32 ? 4 : 5;
-  static constexpr int out_boxes = OUT_F32 ? 4 : 2;
-  static constexpr int a = 0;
-  static constexpr int b = stages * kTileBytes;
-  static constexpr int out = 2 * stages * kTileBytes;
-  static constexpr int sb = out + out_boxes * kBoxBytes;                 // float[kPromoWarps][2][kColsPerWarp]
-  static constexpr int bars = sb + kPromoWarps * 2 * kColsPerWarp * 4;   // uint64 barriers
-  static constexpr int n_bars = 2 * stages + 2 * kTmemBufs + kIssuers;
-  static constexpr int tmem_ptr = bars + n_bars * 8;
-  static constexpr int abort_flag = tmem_ptr + 4;
-  static constexpr int total = abort_flag + 4;
-  static constexpr int bytes = total + 1024;  // slack for manual alignment
+// Compile-time plan of one kernel variant.
+template <int BN_, int SB_GRAN, bool OUT_F32>
+struct Cfg {
+  static constexpr int BN = BN_;
+  static constexpr int tmem_bufs = kTmemCols / BN;            // 2 or 4
+  static constexpr int cols_per_warp = BN / 4;                // 64 or 32
+  static constexpr int b_boxes = BN / 128;
+  static constexpr int stage_bytes = kTileBytes * (1 + b_boxes);
+  static constexpr int esize = OUT_F32 ? 4 : 2;
+  // epilogue: a warp stages its 32 rows x `phase_cols` columns at a time (rows of <= 128
+  // bytes; a fourth pipeline stage bought with narrower staging rows measured no faster)
+  static constexpr int row_bytes = cols_per_warp * esize;     // 64, 128 or 256
+  static constexpr int phase_cap = 128;
+  static constexpr int phase_row_bytes = row_bytes < phase_cap ? row_bytes : phase_cap;
+  static constexpr int phases = row_bytes / phase_row_bytes;
+  static constexpr int phase_cols = phase_row_bytes / esize;
+  static constexpr int warp_out_bytes = 32 * phase_row_bytes;
+  static constexpr int out_bytes = kPromoWarps * warp_out_bytes;
+  static constexpr int sb_bytes = SB_GRAN == 1 ? kPromoWarps * 2 * cols_per_warp * 4 : 0;  // float[warps][2][cols_per_warp]
+  static constexpr int misc_bytes = 512;                      // barriers, TMEM pointer, abort flag
+  static constexpr int stages_fit = (kSmemLimit - 1024 - out_bytes - sb_bytes - misc_bytes) / stage_bytes;
+  static constexpr int stages = stages_fit > 6 ? 6 : stages_fit;
+  // offsets from the 1024-aligned base of dynamic shared memory
+  static constexpr int off_out = stages * stage_bytes;
+  static constexpr int off_sb = off_out + out_bytes;
+  static constexpr int off_bars = off_sb + sb_bytes;
+  static constexpr int n_bars = 2 * stages + 2 * tmem_bufs + kIssuers;
+  static constexpr int off_tmem_ptr = off_bars + n_bars * 8;
+  static constexpr int off_abort = off_tmem_ptr + 4;
+  static constexpr int smem_bytes = off_bars + misc_bytes + 1024;  // + slack for manual alignment
+  static_assert(n_bars * 8 + 8 <= misc_bytes, "misc area too small");
+  static_assert(stages >= 3, "pipeline too shallow");
+  static_assert(smem_bytes <= kSmemLimit, "shared-memory plan exceeds the 227 KB a CTA may use");
 };
 
 struct GemmParams {
@@ -117,6 +132,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Non-blocking probe of a barrier phase.
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(bar), "r"(parity)
@@ -205,6 +233,25 @@ __device__ __forceinline__ void tmem_wait_ld(uint32_t (&v)[32]) {
       : "memory");
 }
 
+// 16-column variants (fewer live registers: used by the 64-columns-per-warp tile)
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld16(uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.wait::ld.sync.aligned;"
+      : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]),
+        "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15])
+      :
+      : "memory");
+}
+
 // Shared-memory operand descriptor, 128-byte swizzle, 8-row groups 1024 bytes apart.
 //   bits  0-13 start address >> 4      bits 16-29 leading byte offset >> 4
 //   bits 32-45 stride byte offset >> 4 bits 46-47 descriptor version (1 on sm_100)
@@ -232,32 +279,54 @@ __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 // make this thread's generic-proxy shared-memory writes visible to the async (TMA) proxy
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void promo_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kPromoThreads) : "memory"); }
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
 }
 
 // ---- kernel ----------------------------------------------------------------------------
 
-template <int SB_GRAN, bool OUT_F32>
+// acc[j] += scale * v[2j..2j+1] for NC TMEM columns; SB_GRAN == 1 multiplies by the per-column
+// scales staged in shared memory first.
+template <int SB_GRAN, int NC>
+__device__ __forceinline__ void promote(float2* acc, const uint32_t (&v)[NC], const float* stage, float sa_v, float s_scalar) {
+  if (SB_GRAN == 1) {
+    const float2 sa2 = make_float2(sa_v, sa_v);
+#pragma unroll
+    for (int j = 0; j < NC / 4; ++j) {
+      const float4 sb4 = *reinterpret_cast<const float4*>(stage + 4 * j);
+      const float2 p0 = make_float2(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]));
+      const float2 p1 = make_float2(__uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+      acc[2 * j] = __ffma2_rn(__fmul2_rn(p0, make_float2(sb4.x, sb4.y)), sa2, acc[2 * j]);
+      acc[2 * j + 1] = __ffma2_rn(__fmul2_rn(p1, make_float2(sb4.z, sb4.w)), sa2, acc[2 * j + 1]);
+    }
+  } else {
+    const float2 s2 = make_float2(s_scalar, s_scalar);
+#pragma unroll
+    for (int j = 0; j < NC / 2; ++j) {
+      const float2 pv = make_float2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+      acc[j] = __ffma2_rn(pv, s2, acc[j]);
+    }
+  }
+}
+
+template <int BN_, int SB_GRAN, bool OUT_F32>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
                             const __grid_constant__ CUtensorMap tmap_b,
                             const __grid_constant__ CUtensorMap tmap_d, const GemmParams p) {
-  using L = SmemLayout<OUT_F32>;
-  constexpr int kStages = L::stages;
+  using C = Cfg<BN_, SB_GRAN, OUT_F32>;
+  constexpr int BN = C::BN, kStages = C::stages, kTmemBufs = C::tmem_bufs, kCols = C::cols_per_warp;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t sbase = smem_u32(smem);
-  const uint32_t bar0 = sbase + L::bars;
+  const uint32_t bar0 = sbase + C::off_bars;
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (kStages + s); };
   auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * kStages + b); };
   auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * kStages + kTmemBufs + b); };
   auto drain_bar = [&](int i) { return bar0 + 8u * (2 * kStages + 2 * kTmemBufs + i); };
-  volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem + L::tmem_ptr);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::abort_flag);
-  float* s_sb = reinterpret_cast<float*>(smem + L::sb);
+  volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem + C::off_tmem_ptr);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::off_abort);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_tiles = p.tiles_m * p.tiles_n;
@@ -279,7 +348,7 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_d)) : "memory");
   }
   if (warp == 1) {
-    tmem_alloc(sbase + L::tmem_ptr, kTmemCols);
+    tmem_alloc(sbase + C::off_tmem_ptr, kTmemCols);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -287,181 +356,220 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_smem;
 
-  if (warp == 0) {
-    // ------------------------------ TMA producer ---------------------------------------
-    // The whole warp walks the loop (uniform control flow); one elected lane issues.
-    uint32_t it = 0;
-    bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
-      const int m0 = (tile / p.tiles_n) * BM, n0 = (tile % p.tiles_n) * BN;
-      for (int kb = 0; kb < p.nkb; ++kb, ++it) {
-        const int s = it % kStages;
-        ok = __all_sync(0xffffffffu, mbar_wait(empty_bar(s), ((it / kStages) & 1u) ^ 1u, abort_flag, p.status, 1u));
-        if (!ok) break;
+  if (warp < kFirstPromoWarp) {
+    if (warp == 0) {
+      // ------------------------------ TMA producer -------------------------------------
+      // The whole warp walks the loop (uniform control flow); one elected lane issues.
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
+        const int m0 = (tile / p.tiles_n) * BM, n0 = (tile % p.tiles_n) * BN;
+        for (int kb = 0; kb < p.nkb; ++kb, ++it) {
+          const int s = it % kStages;
+          ok = __all_sync(0xffffffffu, mbar_wait(empty_bar(s), ((it / kStages) & 1u) ^ 1u, abort_flag, p.status, 1u));
+          if (!ok) break;
+          if (elect_one()) {
+            mbar_expect_tx(full_bar(s), C::stage_bytes);
+            const int k0 = kb * BK;
+            const uint32_t dst = sbase + s * C::stage_bytes;
+            tma_load_2d(dst, &tmap_a, full_bar(s), p.a_mn ? m0 : k0, p.a_mn ? k0 : m0);
+#pragma unroll
+            for (int b = 0; b < C::b_boxes; ++b) {
+              const int nb = n0 + b * 128;  // a box wholly past N is still loaded: it arrives as zeros
+              tma_load_2d(dst + (1 + b) * kTileBytes, &tmap_b, full_bar(s), p.b_mn ? nb : k0, p.b_mn ? k0 : nb);
+            }
+          }
+          __syncwarp();
+        }
+      }
+    } else if (warp <= kIssuers) {
+      // ------------------------------ MMA issuers --------------------------------------
+      // Issuer i takes the contraction blocks with (global block counter) % kIssuers == i.
+      // Blocks are independent: each has its own TMEM buffer and shared-memory stage.
+      const int issuer = warp - 1;
+      // instruction descriptor: D f32 (bit 4), A/B e4m3 (0), major bits 15/16, N>>3 at 17, M>>4 at 24
+      const uint32_t idesc = (1u << 4) | (uint32_t(p.a_mn) << 15) | (uint32_t(p.b_mn) << 16) |
+                             (uint32_t(BN >> 3) << 17) | (uint32_t(BM >> 4) << 24);
+      // descriptor start-address step per UMMA_K: 32 bytes along a K-major row, 32 rows of 128 B otherwise
+      const uint32_t a_step = p.a_mn ? (UMMA_K * 128) >> 4 : UMMA_K >> 4;
+      const uint32_t b_step = p.b_mn ? (UMMA_K * 128) >> 4 : UMMA_K >> 4;
+      const uint64_t a_desc0 = make_smem_desc(sbase);
+      const uint64_t b_desc0 = make_smem_desc(sbase + kTileBytes);
+      int my_tiles = 0;
+      for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) ++my_tiles;
+      const uint32_t total = uint32_t(my_tiles) * uint32_t(p.nkb);
+      bool ok = true;
+      bool ready = false;  // barriers of block `it` already seen complete by an early probe
+      for (uint32_t it = issuer; ok && it < total; it += kIssuers) {
+        const int s = it % kStages, buf = it % kTmemBufs;
+        if (!ready) {
+          ok = __all_sync(0xffffffffu, mbar_wait(tempty_bar(buf), ((it / kTmemBufs) & 1u) ^ 1u, abort_flag, p.status, 2u) &&
+                                           mbar_wait(full_bar(s), (it / kStages) & 1u, abort_flag, p.status, 3u));
+          if (!ok) break;
+        }
+        tc_fence_after();
+        // probe the next block's barriers now; the answers are read after this block is issued
+        const uint32_t nx = it + kIssuers;
+        bool nx_ready = false;
+        if (nx < total)
+          nx_ready = mbar_test(tempty_bar(nx % kTmemBufs), ((nx / kTmemBufs) & 1u) ^ 1u) &
+                     mbar_test(full_bar(nx % kStages), (nx / kStages) & 1u);
         if (elect_one()) {
-          mbar_expect_tx(full_bar(s), 2 * kTileBytes);
-          const int k0 = kb * BK;
-          tma_load_2d(sbase + L::a + s * kTileBytes, &tmap_a, full_bar(s), p.a_mn ? m0 : k0, p.a_mn ? k0 : m0);
-          tma_load_2d(sbase + L::b + s * kTileBytes, &tmap_b, full_bar(s), p.b_mn ? n0 : k0, p.b_mn ? k0 : n0);
+          const uint64_t a_desc = a_desc0 + uint64_t((s * C::stage_bytes) >> 4);
+          const uint64_t b_desc = b_desc0 + uint64_t((s * C::stage_bytes) >> 4);
+          const uint32_t d_tmem = tmem_base + uint32_t(buf * BN);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_f8(d_tmem, a_desc + uint64_t(k * a_step), b_desc + uint64_t(k * b_step), idesc, k > 0 ? 1u : 0u);
+          umma_commit(empty_bar(s));    // shared-memory stage free once these MMAs retire
+          umma_commit(tfull_bar(buf));  // accumulator buffer ready for promotion
         }
         __syncwarp();
+        ready = __all_sync(0xffffffffu, nx_ready);
       }
-    }
-  } else if (warp < kFirstPromoWarp) {
-    // ------------------------------ MMA issuers ----------------------------------------
-    // Issuer i takes the contraction blocks with (global block counter) % kIssuers == i.
-    // Blocks are independent: each has its own TMEM buffer and shared-memory stage.
-    const int issuer = warp - 1;
-    // instruction descriptor: D f32 (bit 4), A/B e4m3 (0), major bits 15/16, N>>3 at 17, M>>4 at 24
-    const uint32_t idesc = (1u << 4) | (uint32_t(p.a_mn) << 15) | (uint32_t(p.b_mn) << 16) |
-                           (uint32_t(BN >> 3) << 17) | (uint32_t(BM >> 4) << 24);
-    // descriptor start-address step per UMMA_K: 32 bytes along a K-major row, 32 rows of 128 B otherwise
-    const uint32_t a_step = p.a_mn ? (UMMA_K * 128) >> 4 : UMMA_K >> 4;
-    const uint32_t b_step = p.b_mn ? (UMMA_K * 128) >> 4 : UMMA_K >> 4;
-    const uint64_t a_desc0 = make_smem_desc(sbase + L::a);
-    const uint64_t b_desc0 = make_smem_desc(sbase + L::b);
-    int my_tiles = 0;
-    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) ++my_tiles;
-    const uint32_t total = uint32_t(my_tiles) * uint32_t(p.nkb);
-    bool ok = true;
-    for (uint32_t it = issuer; ok && it < total; it += kIssuers) {
-      const int s = it % kStages, buf = it % kTmemBufs;
-      ok = __all_sync(0xffffffffu, mbar_wait(tempty_bar(buf), ((it / kTmemBufs) & 1u) ^ 1u, abort_flag, p.status, 2u) &&
-                                       mbar_wait(full_bar(s), (it / kStages) & 1u, abort_flag, p.status, 3u));
-      if (!ok) break;
-      tc_fence_after();
+      // make sure nothing issued here is still running when TMEM is freed
       if (elect_one()) {
-        const uint64_t a_desc = a_desc0 + uint64_t((s * kTileBytes) >> 4);
-        const uint64_t b_desc = b_desc0 + uint64_t((s * kTileBytes) >> 4);
-        const uint32_t d_tmem = tmem_base + uint32_t(buf * BN);
-#pragma unroll
-        for (int k = 0; k < BK / UMMA_K; ++k)
-          umma_f8(d_tmem, a_desc + uint64_t(k * a_step), b_desc + uint64_t(k * b_step), idesc, k > 0 ? 1u : 0u);
-        // ONE commit per block: the promotion warps see the accumulator buffer ready, and the
-        // first of them frees the shared-memory stage on this thread's behalf.
-        umma_commit(tfull_bar(buf));
+        umma_commit(drain_bar(issuer));
+        mbar_wait(drain_bar(issuer), 0u, abort_flag, p.status, 4u);
       }
       __syncwarp();
     }
-    // make sure nothing issued here is still running when TMEM is freed
-    if (elect_one()) {
-      umma_commit(drain_bar(issuer));
-      mbar_wait(drain_bar(issuer), 0u, abort_flag, p.status, 4u);
-    }
-    __syncwarp();
   } else {
     // ------------------------------ promotion + epilogue --------------------------------
     const int pw = warp - kFirstPromoWarp;     // 0..kPromoWarps-1
     const int quarter = warp & 3;              // TMEM lanes this warp may touch
-    const int cg = pw >> 2;                    // column group: columns [cg*32, cg*32+32) of the tile
+    const int cg = pw >> 2;                    // column group
     const int r = quarter * 32 + lane;         // row inside the tile
-    const int c0 = cg * kColsPerWarp;
-    float* sb_stage = s_sb + pw * (2 * kColsPerWarp);   // warp-private, double-buffered
-    const bool store_thread = (pw == 0 && lane == 0);
-    // this thread's 16-byte chunks in the swizzled staging area (row r of box(es))
-    const uint32_t out_row = sbase + L::out + uint32_t(r) * 128u;
+    const int c0 = cg * kCols;                 // first column inside the tile
+    float* sb_stage = reinterpret_cast<float*>(smem + C::off_sb) + pw * (2 * kCols);  // warp-private, double-buffered
+    const uint32_t out_base = sbase + C::off_out + uint32_t(pw) * C::warp_out_bytes + uint32_t(lane) * C::phase_row_bytes;
+    // TMA swizzle of this row: 16-byte chunk index XOR address bits 7.. (128B: 3 bits, 64B: 2, 32B: 1)
+    const int swz = C::phase_row_bytes == 128 ? (lane & 7) : C::phase_row_bytes == 64 ? ((lane >> 1) & 3) : ((lane >> 2) & 1);
     uint32_t it = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-      const int m0 = (tile / p.tiles_n) * BM, n0 = (tile % p.tiles_n) * BN;
-      const int m = m0 + r;
-      const bool m_ok = m < p.M;
-      const float* sa_ptr = p.sa + (long long)(m_ok ? m : 0) * p.sa_sm;
-      const float* sb_ptr;
-      bool sb_ok = true;
-      if (SB_GRAN == 1) {
-        sb_ok = (n0 + c0 + lane) < p.N;        // lane j stages the scale of column c0 + j
-        sb_ptr = p.sb + (long long)(sb_ok ? n0 + c0 + lane : 0) * p.sb_sn;
-      } else {
-        sb_ptr = p.sb + (long long)(n0 / 128) * p.sb_sn;
-      }
-      float2 acc[kColsPerWarp / 2];
-#pragma unroll
-      for (int j = 0; j < kColsPerWarp / 2; ++j) acc[j] = make_float2(0.f, 0.f);
 
-      float sa_next = m_ok ? __ldg(sa_ptr) : 0.f;
-      float sb_next = sb_ok ? __ldg(sb_ptr) : 0.f;
+    // per-tile state, computed one tile ahead so that the first scale loads are in flight
+    // during the previous tile's epilogue
+    int m0 = 0, n0 = 0;
+    bool m_ok = false, sb_ok0 = false, sb_ok1 = false;
+    const float* sa_ptr = p.sa;
+    const float* sb_ptr0 = p.sb;
+    const float* sb_ptr1 = p.sb;
+    float sa_next = 0.f, sb_next0 = 0.f, sb_next1 = 0.f;
+    auto open_tile = [&](int tile) {
+      m0 = (tile / p.tiles_n) * BM;
+      n0 = (tile % p.tiles_n) * BN;
+      const int m = m0 + r;
+      m_ok = m < p.M;
+      sa_ptr = p.sa + (long long)(m_ok ? m : 0) * p.sa_sm;
+      if (SB_GRAN == 1) {                      // lane j stages the scales of columns c0 + j (and c0 + 32 + j)
+        sb_ok0 = (n0 + c0 + lane) < p.N;
+        sb_ok1 = kCols > 32 && (n0 + c0 + 32 + lane) < p.N;
+        sb_ptr0 = p.sb + (long long)(sb_ok0 ? n0 + c0 + lane : 0) * p.sb_sn;
+        sb_ptr1 = p.sb + (long long)(sb_ok1 ? n0 + c0 + 32 + lane : 0) * p.sb_sn;
+      } else {                                 // one scale per 128 columns
+        sb_ok0 = true;
+        sb_ok1 = false;
+        const int nblk = (n0 + c0) / 128;
+        sb_ptr0 = p.sb + (long long)((nblk * 128 < p.N) ? nblk : 0) * p.sb_sn;
+        sb_ptr1 = sb_ptr0;
+      }
+      sa_next = m_ok ? __ldg(sa_ptr) : 0.f;
+      sb_next0 = sb_ok0 ? __ldg(sb_ptr0) : 0.f;
+      sb_next1 = sb_ok1 ? __ldg(sb_ptr1) : 0.f;
+    };
+
+    if (blockIdx.x < n_tiles) open_tile(blockIdx.x);
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+      const int tile_m0 = m0, tile_n0 = n0;
+      float2 acc[kCols / 2];
+#pragma unroll
+      for (int j = 0; j < kCols / 2; ++j) acc[j] = make_float2(0.f, 0.f);
+
       for (int kb = 0; kb < p.nkb; ++kb, ++it) {
         const int buf = it % kTmemBufs;
-        const float sa_v = sa_next, sb_v = sb_next;
+        const float sa_v = sa_next, sb_v0 = sb_next0, sb_v1 = sb_next1;
         if (kb + 1 < p.nkb) {
           sa_next = m_ok ? __ldg(sa_ptr + (long long)(kb + 1) * p.sa_sk) : 0.f;
-          sb_next = sb_ok ? __ldg(sb_ptr + (long long)(kb + 1) * p.sb_sk) : 0.f;
+          sb_next0 = sb_ok0 ? __ldg(sb_ptr0 + (long long)(kb + 1) * p.sb_sk) : 0.f;
+          sb_next1 = sb_ok1 ? __ldg(sb_ptr1 + (long long)(kb + 1) * p.sb_sk) : 0.f;
         }
-        float* stage = sb_stage + (it & 1u) * kColsPerWarp;
+        float* stage = sb_stage + (it & 1u) * kCols;
         if (SB_GRAN == 1) {
-          stage[lane] = sb_v;
+          stage[lane] = sb_v0;
+          if (kCols > 32) stage[32 + lane] = sb_v1;
           __syncwarp();
         }
-        // After an abort the remaining iterations only keep loop counters and barriers in step.
+        // After an abort the remaining iterations only keep the loop counters in step.
         if (ok) ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar(buf), (it / kTmemBufs) & 1u, abort_flag, p.status, 5u));
         if (!ok) continue;
-        // the block's MMAs have retired: its shared-memory stage can be refilled
-        if (store_thread) mbar_arrive(empty_bar(it % kStages));
         tc_fence_after();
-        uint32_t v[32];
-        tmem_ld32(tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(buf * BN + c0), v);
-        tmem_wait_ld(v);
-        // the partial sums are in registers: hand the buffer back to the tensor core at once
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(tempty_bar(buf));
-        if (SB_GRAN == 1) {
-          const float2 sa2 = make_float2(sa_v, sa_v);
+        const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(buf * BN + c0);
+        const float s_scalar = sa_v * sb_v0;
+        if (kCols > 32) {
+          // 64 columns in four 16-column pieces; the buffer goes back after the last load lands
+          uint32_t v[16];
 #pragma unroll
-          for (int j = 0; j < kColsPerWarp / 4; ++j) {
-            const float4 sb4 = *reinterpret_cast<const float4*>(stage + 4 * j);
-            const float2 p0 = make_float2(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]));
-            const float2 p1 = make_float2(__uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
-            acc[2 * j] = __ffma2_rn(__fmul2_rn(p0, make_float2(sb4.x, sb4.y)), sa2, acc[2 * j]);
-            acc[2 * j + 1] = __ffma2_rn(__fmul2_rn(p1, make_float2(sb4.z, sb4.w)), sa2, acc[2 * j + 1]);
+          for (int q = 0; q < 3; ++q) {
+            tmem_ld16(taddr + 16 * q, v);
+            tmem_wait_ld16(v);
+            promote<SB_GRAN, 16>(acc + 8 * q, v, stage + 16 * q, sa_v, s_scalar);
           }
+          tmem_ld16(taddr + 48, v);
+          tmem_wait_ld16(v);
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(tempty_bar(buf));
+          promote<SB_GRAN, 16>(acc + 24, v, stage + 48, sa_v, s_scalar);
         } else {
-          const float s_scalar = sa_v * sb_v;
-          const float2 s2 = make_float2(s_scalar, s_scalar);
-#pragma unroll
-          for (int j = 0; j < kColsPerWarp / 2; ++j) {
-            const float2 pv = make_float2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
-            acc[j] = __ffma2_rn(pv, s2, acc[j]);
-          }
+          uint32_t v[32];
+          tmem_ld32(taddr, v);
+          tmem_wait_ld(v);
+          // every partial sum of the buffer is in registers: hand it back to the tensor core
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(tempty_bar(buf));
+          promote<SB_GRAN, 32>(acc, v, stage, sa_v, s_scalar);
         }
       }
-      // ---- epilogue: registers -> swizzled staging -> TMA store --------------------------
-      // Every promotion thread takes both named barriers for every tile, aborting or not.
-      if (store_thread) tma_store_wait_read();  // the previous tile's stores have let go of the staging area
-      promo_bar_sync();
-      if (ok) {
+
+      // start the next tile's first scale loads before the stores of this one
+      if (tile + int(gridDim.x) < n_tiles) open_tile(tile + gridDim.x);
+
+      // ---- epilogue: registers -> this warp's swizzled staging rows -> TMA store ----------
+      if (!ok) continue;
+      const int row0 = tile_m0 + quarter * 32;
+#pragma unroll
+      for (int ph = 0; ph < C::phases; ++ph) {
+        if (lane == 0) tma_store_wait_read();  // this warp's earlier stores have let go of the staging rows
+        __syncwarp();
         if (OUT_F32) {
-          // 32 columns x 4 B = one 128-byte box row; box index = column group
-          const uint32_t base = out_row + uint32_t(cg) * kBoxBytes;
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
-            st_shared_v4(base + (uint32_t(j ^ (r & 7)) << 4), __float_as_uint(acc[2 * j].x), __float_as_uint(acc[2 * j].y),
-                         __float_as_uint(acc[2 * j + 1].x), __float_as_uint(acc[2 * j + 1].y));
+          for (int c = 0; c < C::phase_row_bytes / 16; ++c) {   // 4 floats per 16-byte chunk
+            const int j = ph * (C::phase_cols / 2) + 2 * c;
+            st_shared_v4(out_base + (uint32_t(c ^ swz) << 4), __float_as_uint(acc[j].x), __float_as_uint(acc[j].y),
+                         __float_as_uint(acc[j + 1].x), __float_as_uint(acc[j + 1].y));
+          }
         } else {
-          // 32 columns x 2 B = half a box row; two column groups share a box
-          const uint32_t base = out_row + uint32_t(cg >> 1) * kBoxBytes;
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int chunk = (cg & 1) * 4 + j;
-            st_shared_v4(base + (uint32_t(chunk ^ (r & 7)) << 4), pack_bf16x2(acc[4 * j].x, acc[4 * j].y),
-                         pack_bf16x2(acc[4 * j + 1].x, acc[4 * j + 1].y), pack_bf16x2(acc[4 * j + 2].x, acc[4 * j + 2].y),
-                         pack_bf16x2(acc[4 * j + 3].x, acc[4 * j + 3].y));
+          for (int c = 0; c < C::phase_row_bytes / 16; ++c) {   // 8 bf16 per 16-byte chunk
+            const int j = ph * (C::phase_cols / 2) + 4 * c;
+            st_shared_v4(out_base + (uint32_t(c ^ swz) << 4), pack_bf16x2(acc[j].x, acc[j].y),
+                         pack_bf16x2(acc[j + 1].x, acc[j + 1].y), pack_bf16x2(acc[j + 2].x, acc[j + 2].y),
+                         pack_bf16x2(acc[j + 3].x, acc[j + 3].y));
           }
         }
         fence_proxy_async_smem();
-      }
-      promo_bar_sync();
-      if (store_thread && ok) {
-        constexpr int kBoxCols = OUT_F32 ? 32 : 64;  // elements per 128-byte box row
-#pragma unroll
-        for (int b = 0; b < L::out_boxes; ++b)
-          if (n0 + b * kBoxCols < p.N)
-            tma_store_2d(&tmap_d, sbase + L::out + b * kBoxBytes, n0 + b * kBoxCols, m0);
-        tma_store_commit();
+        __syncwarp();
+        const int col = tile_n0 + c0 + ph * C::phase_cols;
+        if (lane == 0 && col < p.N && row0 < p.M) {
+          tma_store_2d(&tmap_d, sbase + C::off_out + uint32_t(pw) * C::warp_out_bytes, col, row0);
+          tma_store_commit();
+        }
       }
     }
-    if (store_thread) tma_store_wait_read();
+    if (lane == 0) tma_store_wait_read();
+    __syncwarp();
   }
 
   // ------------------------------ teardown ----------------------------------------------
@@ -494,38 +602,52 @@ static int get_encode_fn(EncodeTiledFn* out) {
   return TG_OK;
 }
 
-// 2-D tensor [outer][inner] of `esize`-byte elements, row pitch `pitch_bytes`; box = 128 bytes
-// of the inner dimension x 128 rows, 128-byte swizzle.
+// 2-D tensor [outer][inner] of `esize`-byte elements, row pitch `pitch_bytes`; box of
+// `box_inner_bytes` (32, 64 or 128, = the swizzle span) x `box_rows`.
 static int make_tmap(CUtensorMap* map, CUtensorMapDataType dt, int esize, const void* base, int64_t inner,
-                     int64_t outer, int64_t pitch_bytes) {
+                     int64_t outer, int64_t pitch_bytes, int box_inner_bytes, int box_rows) {
   EncodeTiledFn enc;
   if (int rc = get_encode_fn(&enc)) return rc;
   cuuint64_t dims[2] = {cuuint64_t(inner), cuuint64_t(outer)};
   cuuint64_t strides[1] = {cuuint64_t(pitch_bytes)};
-  cuuint32_t box[2] = {cuuint32_t(128 / esize), 128};
+  cuuint32_t box[2] = {cuuint32_t(box_inner_bytes / esize), cuuint32_t(box_rows)};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                   box_inner_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                   : box_inner_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return record_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
   return TG_OK;
 }
 
-template <int SB_GRAN, bool OUT_F32>
-static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, const GemmParams& p,
-                       int grid, cudaStream_t st) {
-  auto kern = gemm_fp8_blockscaled_kernel<SB_GRAN, OUT_F32>;
-  constexpr int smem = SmemLayout<OUT_F32>::bytes;
-  static_assert(smem <= 227 * 1024, "shared-memory plan exceeds the 227 KB a CTA may use");
+template <int BN_, int SB_GRAN, bool OUT_F32>
+static int launch_gemm(const tg_gemm_args* a, GemmParams p, cudaStream_t st) {
+  using C = Cfg<BN_, SB_GRAN, OUT_F32>;
+  auto kern = gemm_fp8_blockscaled_kernel<BN_, SB_GRAN, OUT_F32>;
+  CUtensorMap ta, tb, td;
+  const int64_t a_inner = p.a_mn ? a->M : a->K, a_outer = p.a_mn ? a->K : a->M;
+  const int64_t b_inner = p.b_mn ? a->N : a->K, b_outer = p.b_mn ? a->K : a->N;
+  if (int rc = make_tmap(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a->a, a_inner, a_outer, a->lda, 128, 128)) return rc;
+  if (int rc = make_tmap(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a->b, b_inner, b_outer, a->ldb, 128, 128)) return rc;
+  if (int rc = make_tmap(&td, OUT_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, C::esize, a->d,
+                         a->N, a->M, a->ldd * C::esize, C::phase_row_bytes, 32))
+    return rc;
+  p.tiles_m = int((a->M + BM - 1) / BM);
+  p.tiles_n = int((a->N + BN_ - 1) / BN_);
+  const int64_t n_tiles = int64_t(p.tiles_m) * p.tiles_n;
+  if (n_tiles > INT32_MAX || n_tiles * p.nkb > INT32_MAX) return TG_ERR_TOO_LARGE;
+  const int sms = sm_count();
+  const int grid = int(n_tiles < sms ? n_tiles : sms);
   // the attribute is per device: set it once for each device this instantiation runs on
   static bool attr_set[64] = {};
   int dev = 0;
   TG_CUDA_CHECK(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return TG_ERR_SHAPE;
   if (!attr_set[dev]) {
-    TG_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    TG_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::smem_bytes));
     attr_set[dev] = true;
   }
-  kern<<<grid, kGemmThreads, smem, st>>>(ta, tb, td, p);
+  kern<<<grid, kGemmThreads, C::smem_bytes, st>>>(ta, tb, td, p);
   TG_CUDA_CHECK(cudaGetLastError());
   return TG_OK;
 }
@@ -545,35 +667,31 @@ extern "C" int tg_gemm_fp8_blockscaled(const tg_gemm_args* a, void* stream) {
   if (a->out_dtype != TG_OUT_BF16 && a->out_dtype != TG_OUT_F32) return TG_ERR_SHAPE;
   if (a->N % 8 != 0 || a->ldd % 8 != 0 || a->ldd < a->N) return TG_ERR_SHAPE;
   if (a->lda % 16 != 0 || a->ldb % 16 != 0) return TG_ERR_SHAPE;
-  const int64_t a_inner = a->a_major == TG_MAJOR_K ? a->K : a->M, a_outer = a->a_major == TG_MAJOR_K ? a->M : a->K;
-  const int64_t b_inner = a->b_major == TG_MAJOR_K ? a->K : a->N, b_outer = a->b_major == TG_MAJOR_K ? a->N : a->K;
+  const int64_t a_inner = a->a_major == TG_MAJOR_K ? a->K : a->M;
+  const int64_t b_inner = a->b_major == TG_MAJOR_K ? a->K : a->N;
   if (a->lda < a_inner || a->ldb < b_inner) return TG_ERR_SHAPE;
   if (!aligned16(a->a) || !aligned16(a->b) || !aligned16(a->d)) return TG_ERR_ALIGN;
   if (int rc = check_arch()) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool f32 = a->out_dtype == TG_OUT_F32;
-  const int esz = f32 ? 4 : 2;
   if (a->K == 0) {
+    const size_t esz = f32 ? 4 : 2;
     TG_CUDA_CHECK(cudaMemset2DAsync(a->d, size_t(a->ldd) * esz, 0, size_t(a->N) * esz, size_t(a->M), st));
     return TG_OK;
   }
-  CUtensorMap ta, tb, td;
-  if (int rc = make_tmap(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a->a, a_inner, a_outer, a->lda)) return rc;
-  if (int rc = make_tmap(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a->b, b_inner, b_outer, a->ldb)) return rc;
-  if (int rc = make_tmap(&td, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, esz, a->d, a->N,
-                         a->M, a->ldd * esz))
-    return rc;
   GemmParams p;
   p.sa = a->sa; p.sa_sm = a->sa_stride_m; p.sa_sk = a->sa_stride_kb;
   p.sb = a->sb; p.sb_sn = a->sb_stride_n; p.sb_sk = a->sb_stride_kb;
   p.M = int(a->M); p.N = int(a->N); p.nkb = int((a->K + BK - 1) / BK);
   p.a_mn = a->a_major == TG_MAJOR_MN; p.b_mn = a->b_major == TG_MAJOR_MN;
-  p.tiles_m = int((a->M + BM - 1) / BM); p.tiles_n = int((a->N + BN - 1) / BN);
+  p.tiles_m = p.tiles_n = 0;
   p.status = a->status;
-  const int64_t n_tiles = int64_t(p.tiles_m) * p.tiles_n;
-  if (n_tiles > INT32_MAX || n_tiles * p.nkb > INT32_MAX) return TG_ERR_TOO_LARGE;
-  const int sms = sm_count();
-  const int grid = int(n_tiles < sms ? n_tiles : sms);
-  if (a->sb_gran_n == 1) return f32 ? launch_gemm<1, true>(ta, tb, td, p, grid, st) : launch_gemm<1, false>(ta, tb, td, p, grid, st);
-  return f32 ? launch_gemm<128, true>(ta, tb, td, p, grid, st) : launch_gemm<128, false>(ta, tb, td, p, grid, st);
+  const bool g1 = a->sb_gran_n == 1;
+  // 128 x 256 tiles when one scale covers 128 columns; per-column scales cost the promotion
+  // warps twice the arithmetic and 64 columns of them per warp do not fit the register
+  // budget, so that case keeps 128 x 128 tiles.
+  const bool wide = a->N > 128 && !g1;
+  if (wide) return f32 ? launch_gemm<256, 128, true>(a, p, st) : launch_gemm<256, 128, false>(a, p, st);
+  if (g1) return f32 ? launch_gemm<128, 1, true>(a, p, st) : launch_gemm<128, 1, false>(a, p, st);
+  return f32 ? launch_gemm<128, 128, true>(a, p, st) : launch_gemm<128, 128, false>(a, p, st);
 }
