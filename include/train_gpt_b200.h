@@ -117,6 +117,27 @@ int64_t tg_rmsnorm_bwd_scratch_bytes(int64_t rows, int64_t cols);
 int tg_rmsnorm_bwd(const void* x, const void* gamma, const void* g, float eps, void* dx,
                    void* dgamma, void* scratch, int64_t rows, int64_t cols, void* stream);
 
+/* No counterpart in the reference.  The same backward as tg_rmsnorm_bwd for hosts that
+ * cannot hand over a scratch buffer because they cannot allocate one: a custom-call
+ * handler inside a compiled XLA program gets only the buffers XLA planned, and XLA has
+ * usually claimed most of the device already (the reference's launchers give it 90 %),
+ * so cudaMalloc there can fail or stall.  The partial column sums go to a 4 MiB array
+ * built into the library image (held by every GPU that loads the library, until exit).
+ *   - Problems whose tg_rmsnorm_bwd_scratch_bytes(rows, cols) exceeds
+ *     tg_rmsnorm_bwd_static_max_scratch_bytes() are refused with TG_ERR_TOO_LARGE and a
+ *     message in tg_last_cuda_error(); nothing is launched.  (cols = 2048 fits for any
+ *     row count; cols = 4096 does not once rows exceed a few hundred.)
+ *   - The first call on each device looks up the array's device address (no allocation);
+ *     make that first call outside any stream capture.
+ *   - All calls on a device share the one array.  The kernels overwrite what they read,
+ *     so nothing needs clearing between calls, but two calls whose kernels can overlap on
+ *     the GPU (different streams, no dependency between them) race on it: keep them on
+ *     one stream or order them with events.
+ *   - Calls no cudaMalloc / cudaFree and no allocating library routine.                  */
+int64_t tg_rmsnorm_bwd_static_max_scratch_bytes(void);
+int tg_rmsnorm_bwd_static(const void* x, const void* gamma, const void* g, float eps, void* dx,
+                          void* dgamma, int64_t rows, int64_t cols, void* stream);
+
 /* ---- block-scaled FP8 GEMM -------------------------------------------------------- */
 
 /* Operand storage, seen from the GEMM  D[m,n] = sum_k A[m,k] * B[n,k]. */

@@ -359,3 +359,46 @@ extern "C" int tg_rmsnorm_bwd(const void* x, const void* gamma, const void* g, f
   TG_CUDA_CHECK(cudaGetLastError());
   return TG_OK;
 }
+
+// ---------------------------------------------------------------------------------------
+// Norm backward for callers that may not allocate device memory.
+//
+// tg_rmsnorm_bwd wants a scratch buffer from its caller.  Some hosts of this library have
+// nowhere to get one: an XLA custom-call handler receives only the buffers the compiler
+// planned for it, and the reference's launchers hand XLA 90 % of the device up front
+// (XLA_PYTHON_CLIENT_MEM_FRACTION=0.9, train-gpt bench_fp8_norm.py:64), so a cudaMalloc
+// from inside the handler can fail outright or stall the stream it synchronises with.
+// For them the partial column sums live in a fixed array inside the library image.  Every
+// GPU that loads the library carries these 4 MiB until the process exits.
+// ---------------------------------------------------------------------------------------
+namespace tg {
+constexpr int64_t kStaticBwdScratchBytes = 4ll << 20;
+static __device__ __align__(256) unsigned char g_bwd_scratch[kStaticBwdScratchBytes];
+}  // namespace tg
+
+extern "C" int64_t tg_rmsnorm_bwd_static_max_scratch_bytes(void) { return tg::kStaticBwdScratchBytes; }
+
+extern "C" int tg_rmsnorm_bwd_static(const void* x, const void* gamma, const void* g, float eps,
+                                     void* dx, void* dgamma, int64_t rows, int64_t cols, void* stream) {
+  // In host code `g_bwd_scratch` is only a handle for the runtime, not an address a kernel
+  // can use; the device address is looked up once per device, with that device current.
+  static void* dev_ptr[64] = {};
+  if (rows < 0 || cols <= 0 || cols % 8 != 0) return TG_ERR_SHAPE;
+  const int64_t need = tg_rmsnorm_bwd_scratch_bytes(rows, cols);
+  if (need > tg::kStaticBwdScratchBytes) {
+    // message for tg_last_cuda_error(): the size limit is the caller's to handle
+    tg::record_cuda_error(cudaErrorInvalidValue,
+                          "tg_rmsnorm_bwd_static: rows x cols needs more than the 4 MiB built-in scratch; "
+                          "use tg_rmsnorm_bwd with a caller-owned buffer");
+    return TG_ERR_TOO_LARGE;
+  }
+  int dev = 0;
+  TG_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return TG_ERR_SHAPE;
+  void* scratch = dev_ptr[dev];
+  if (scratch == nullptr) {
+    TG_CUDA_CHECK(cudaGetSymbolAddress(&scratch, tg::g_bwd_scratch));
+    dev_ptr[dev] = scratch;  // racing first calls on one device store the same value
+  }
+  return tg_rmsnorm_bwd(x, gamma, g, eps, dx, dgamma, scratch, rows, cols, stream);
+}
