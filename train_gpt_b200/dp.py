@@ -1,0 +1,94 @@
+"""Data-parallel gradient exchange for the training step: the one collective the hot path
+has.  train-gpt itself is single-device (train.py:1); the exchange belongs between
+`value_and_grad` (train.py:129) and `global_norm` (train.py:132).
+
+Gradients of one bucket (one decoder layer, or the embedding / head group) live in ONE flat
+buffer; every parameter's `.grad` is a view into it.  When the last gradient of a bucket has
+been accumulated during backward, the bucket's all-reduce is launched asynchronously, so the
+exchange of layer l overlaps the backward of layers l-1 .. 0.  NCCL (NVLink/NVSwitch) on GPUs,
+gloo on CPU -- the class only uses `torch.distributed`.
+"""
+from __future__ import annotations
+
+from typing import List, Sequence
+
+import torch
+import torch.distributed as dist
+
+
+class GradBuckets:
+    """Flat gradient buckets with overlap of all-reduce and backward.
+
+    buckets: list of lists of parameters, in the order their gradients become ready LAST to
+    FIRST does not matter -- each bucket fires when its own parameters are all done.
+    """
+
+    def __init__(self, buckets: Sequence[Sequence[torch.nn.Parameter]], world_size: int, average: bool = True,
+                 group=None):
+        self.world_size = world_size
+        self.average = average
+        self.group = group
+        self.flat: List[torch.Tensor] = []
+        self._pending: List[int] = []
+        self._sizes: List[int] = []
+        self._handles = []
+        self._hooks = []
+        for bi, params in enumerate(buckets):
+            params = [p for p in params if p.requires_grad]
+            if not params:
+                self.flat.append(torch.empty(0))
+                self._sizes.append(0)
+                self._pending.append(0)
+                continue
+            dtype, device = params[0].dtype, params[0].device
+            n = sum(p.numel() for p in params)
+            flat = torch.zeros(n, dtype=dtype, device=device)
+            off = 0
+            for p in params:
+                if p.dtype != dtype:
+                    raise TypeError("all parameters of a bucket must share a dtype")
+                p.grad = flat[off:off + p.numel()].view_as(p)
+                off += p.numel()
+                self._hooks.append(p.register_post_accumulate_grad_hook(self._make_hook(bi)))
+            self.flat.append(flat)
+            self._sizes.append(len(params))
+            self._pending.append(len(params))
+
+    def _make_hook(self, bi: int):
+        def hook(_param):
+            self._pending[bi] -= 1
+            if self._pending[bi] == 0:
+                self._launch(bi)
+        return hook
+
+    def _launch(self, bi: int):
+        if self.world_size > 1:
+            self._handles.append(dist.all_reduce(self.flat[bi], op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+
+    def finish(self):
+        """Wait for every bucket's exchange, turn sums into means, re-arm for the next step."""
+        for bi, left in enumerate(self._pending):
+            if left != 0 and self._sizes[bi] != 0:
+                # a parameter that got no gradient this step: exchange what there is
+                self._launch(bi)
+        for h in self._handles:
+            h.wait()
+        self._handles.clear()
+        if self.world_size > 1 and self.average:
+            for f in self.flat:
+                if f.numel():
+                    f.mul_(1.0 / self.world_size)
+        self._pending = list(self._sizes)
+
+    def zero(self):
+        for f in self.flat:
+            if f.numel():
+                f.zero_()
+
+    def global_norm(self) -> torch.Tensor:
+        """optax.global_norm (train.py:132) over all buckets, in float32."""
+        sq = [f.float().pow(2).sum() for f in self.flat if f.numel()]
+        return torch.stack(sq).sum().sqrt()
+
+    def bytes(self) -> int:
+        return sum(f.numel() * f.element_size() for f in self.flat)

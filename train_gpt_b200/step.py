@@ -1,0 +1,250 @@
+"""The caller of the hot path: one GPT pre-training step with the FP8 linears and the fused
+norm, data-parallel over the GPUs of a node.
+
+This is the restatement of train-gpt's step that the benchmark needs (model.py:57-98 as
+re-built by bench_fp8_norm.py:81-128, losses.py:8-12, train.py:114-137), not a model zoo:
+attention (torch SDPA), embedding, loss and AdamW are torch glue; the six projections per
+layer and the norms run on this package's kernels through the reference's `mm` / `norm` seam.
+
+    mm   "fp8"      block_scaled_matmul, 128x128 weight tiles, FP8 dgrad + wgrad
+         "fp8_ref"  block_scaled_matmul exactly as the reference calls it (128x1 tiles, bf16 STE backward)
+         "bf16"     a @ b (bench_fp8_norm.py:130)
+    norm "fused"    rms_norm_quant feeding q/k/v (and up) from ONE quantised activation (FP8 mm only)
+         "kernel"   kernels.rms_norm;  "pure": kernels._rms_norm_pure
+         "torch_reference"  kernels.py:30-33 written with torch ops: the comparator the loss-curve
+                    parity test and the CPU (gloo) tests of the gradient exchange run against
+
+Differences from model.py that BASELINE.json's configuration 3 asks for are switches: GELU
+(default there) or the reference's squared ReLU (model.py:72); learned positions, separate
+q/k/v, untied head, tanh logit cap 15 and the 0.02 / 0.02/sqrt(2L) init follow model.py.
+No per-block rematerialisation (the reference's `use_remat` trades compute for memory; 180 GB
+does not need it at these sizes).
+"""
+from __future__ import annotations
+
+import math
+import time
+from dataclasses import dataclass
+
+import torch
+import torch.nn.functional as F
+
+from . import fp8, kernels, ops
+from .dp import GradBuckets
+
+
+@dataclass(frozen=True)
+class StepConfig:
+    vocab_size: int = 50304
+    seq_len: int = 1024
+    d_model: int = 1024
+    n_layers: int = 24
+    n_heads: int = 16
+    head_dim: int = 64
+    d_ff: int = 4096
+    init_std: float = 0.02          # config.py:16
+    rms_eps: float = 1e-5           # config.py:17
+    logit_cap: float = 15.0         # config.py:19
+    activation: str = "gelu"        # "gelu" (BASELINE configuration 3) or "relu2" (model.py:72)
+    mm: str = "fp8"
+    norm: str = "fused"
+    lr: float = 3e-4
+    weight_decay: float = 0.1       # train.py make_optimizer default use
+    clip_norm: float = 1.0
+
+
+SMALL = dict(vocab_size=256, seq_len=128, d_model=128, n_layers=2, n_heads=4, head_dim=32, d_ff=512)  # config.py:32-40
+
+
+class _NormQuant(torch.autograd.Function):
+    """rms_norm whose forward also emits the 1x128-quantised form of its output; the bf16
+    output carries the gradient, the quantised pair rides along for the GEMMs."""
+
+    @staticmethod
+    def forward(ctx, x, gamma, eps):
+        q, s, y, _ = ops.rmsnorm_quant_fwd(x, gamma, eps, want_y=True)
+        ctx.save_for_backward(x, gamma)
+        ctx.eps = eps
+        ctx.mark_non_differentiable(q, s)
+        return y, q, s
+
+    @staticmethod
+    def backward(ctx, gy, _gq, _gs):
+        x, gamma = ctx.saved_tensors
+        dx, dgamma = ops.rmsnorm_bwd(x, gamma, gy.contiguous(), ctx.eps)
+        return dx, dgamma, None
+
+
+class GPT:
+    """Parameters (bf16, model.py:19-54) and forward pass."""
+
+    def __init__(self, cfg: StepConfig, device, seed: int = 0):
+        self.cfg = cfg
+        g = torch.Generator(device=device).manual_seed(seed)
+        std, proj_std = cfg.init_std, cfg.init_std / math.sqrt(2.0 * cfg.n_layers)   # model.py:21-22
+        d, h, ff = cfg.d_model, cfg.n_heads * cfg.head_dim, cfg.d_ff
+
+        def normal(shape, s=std):
+            return torch.nn.Parameter((torch.randn(shape, device=device, generator=g) * s).to(torch.bfloat16))
+
+        def ones(n):
+            return torch.nn.Parameter(torch.ones(n, device=device, dtype=torch.bfloat16))
+
+        self.embed = normal((cfg.vocab_size, d))
+        self.pos = normal((cfg.seq_len, d))
+        self.layers = []
+        for _ in range(cfg.n_layers):
+            self.layers.append({
+                "norm1": ones(d), "wq": normal((d, h)), "wk": normal((d, h)), "wv": normal((d, h)),
+                "wo": normal((h, d), proj_std), "norm2": ones(d), "w_up": normal((d, ff)),
+                "w_down": normal((ff, d), proj_std)})
+        self.final_norm = ones(d)
+        self.unembed = normal((d, cfg.vocab_size))
+
+    def buckets(self):
+        """Gradient buckets in the order backward finishes them: head group, layers L-1..0, embeddings."""
+        out = [[self.unembed, self.final_norm]]
+        for lp in reversed(self.layers):
+            out.append(list(lp.values()))
+        out.append([self.embed, self.pos])
+        return out
+
+    def parameters(self):
+        return [p for b in self.buckets() for p in b]
+
+    # ---- the mm / norm seam (bench_fp8_norm.py:81-86) -------------------------------------
+    def _mm(self, a, w, aq=None):
+        m = self.cfg.mm
+        if m == "bf16":
+            return a @ w
+        if m == "fp8":
+            return fp8.block_scaled_matmul(a, w, weight_tile=(128, 128), backward="fp8", a_quantized=aq)
+        if m == "fp8_ref":
+            return fp8.block_scaled_matmul(a, w, a_quantized=aq)
+        raise ValueError(f"unknown mm {m!r}")
+
+    def _norm(self, x, w):
+        """Returns (y, quantised pair or None)."""
+        c = self.cfg
+        if c.norm == "fused" and c.mm != "bf16":
+            y, q, s = _NormQuant.apply(x, w, c.rms_eps)
+            return y, (q, s)
+        if c.norm == "pure":
+            return kernels._rms_norm_pure(x, w, c.rms_eps), None
+        if c.norm == "torch_reference":
+            var = x.float().pow(2).mean(-1, keepdim=True)                           # kernels.py:31
+            return x * torch.rsqrt(var + c.rms_eps).to(x.dtype) * w, None           # kernels.py:32-33
+        return kernels.rms_norm(x, w, c.rms_eps), None
+
+    def _act(self, u):
+        return F.gelu(u) if self.cfg.activation == "gelu" else F.relu(u) ** 2      # model.py:72
+
+    def forward(self, ids):
+        c = self.cfg
+        B, T = ids.shape
+        x = self.embed[ids] + self.pos[:T]                                          # model.py:83
+        for lp in self.layers:
+            h, hq = self._norm(x, lp["norm1"])                                      # model.py:76
+            q = self._mm(h, lp["wq"], hq).view(B, T, c.n_heads, c.head_dim)         # model.py:63-65
+            k = self._mm(h, lp["wk"], hq).view(B, T, c.n_heads, c.head_dim)
+            v = self._mm(h, lp["wv"], hq).view(B, T, c.n_heads, c.head_dim)
+            o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True)
+            x = x + self._mm(o.transpose(1, 2).reshape(B, T, -1), lp["wo"])         # model.py:68
+            h, hq = self._norm(x, lp["norm2"])                                      # model.py:77
+            x = x + self._mm(self._act(self._mm(h, lp["w_up"], hq)), lp["w_down"])
+        x, _ = self._norm(x, self.final_norm)                                       # model.py:93
+        logits = x @ self.unembed                                                   # stays bf16 (bench_fp8_norm.py:86)
+        return c.logit_cap * torch.tanh(logits / c.logit_cap)                       # model.py:97
+
+    def loss(self, ids, targets):
+        logits = self.forward(ids).float()                                          # losses.py:9
+        return F.cross_entropy(logits.view(-1, logits.shape[-1]), targets.view(-1))  # losses.py:10-12
+
+
+class Trainer:
+    """train.py:126-137 with the gradient exchange inserted: loss + backward (bucketed
+    all-reduce overlapping it), global norm, clip, AdamW."""
+
+    def __init__(self, cfg: StepConfig, device, world_size: int = 1, seed: int = 0):
+        self.cfg, self.device, self.world = cfg, device, world_size
+        self.model = GPT(cfg, device, seed)                     # same seed on every rank: replicated weights
+        self.buckets = GradBuckets(self.model.buckets(), world_size)
+        use_fused = torch.device(device).type == "cuda"
+        self.opt = torch.optim.AdamW(self.model.parameters(), lr=cfg.lr, weight_decay=cfg.weight_decay,
+                                     betas=(0.9, 0.999), eps=1e-8, fused=use_fused)
+
+    def step(self, ids, targets):
+        self.buckets.zero()
+        loss = self.model.loss(ids, targets)
+        loss.backward()
+        self.buckets.finish()
+        gnorm = self.buckets.global_norm()                                           # train.py:132
+        scale = torch.clamp(self.cfg.clip_norm / (gnorm + 1e-6), max=1.0)            # optax.clip_by_global_norm
+        for f in self.buckets.flat:
+            if f.numel():
+                f.mul_(scale.to(f.dtype))
+        self.opt.step()
+        return loss.detach(), gnorm
+
+
+def synthetic_batch(cfg: StepConfig, batch: int, device, seed: int, learnable: bool = False):
+    """Seeded tokens uniform over the vocabulary (data.py:10-11's random windows stand-in).
+    `learnable` draws sequences from a fixed random bigram map instead, so that a short run
+    has a falling loss curve to compare."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    if not learnable:
+        ids = torch.randint(0, cfg.vocab_size, (batch, cfg.seq_len + 1), generator=g)
+    else:
+        table = torch.randint(0, cfg.vocab_size, (cfg.vocab_size,), generator=torch.Generator().manual_seed(1234))
+        ids = torch.empty((batch, cfg.seq_len + 1), dtype=torch.long)
+        ids[:, 0] = torch.randint(0, cfg.vocab_size, (batch,), generator=g)
+        noise = torch.rand((batch, cfg.seq_len), generator=g) < 0.1
+        rnd = torch.randint(0, cfg.vocab_size, (batch, cfg.seq_len), generator=g)
+        for t in range(cfg.seq_len):
+            ids[:, t + 1] = torch.where(noise[:, t], rnd[:, t], table[ids[:, t]])
+    ids = ids.to(device)
+    return ids[:, :-1].contiguous(), ids[:, 1:].contiguous()
+
+
+def step_flops(cfg: StepConfig, tokens: int) -> float:
+    """The reference's estimator 6 * L * layer_params * tokens (bench.py:96-102)."""
+    d, h, ff = cfg.d_model, cfg.n_heads * cfg.head_dim, cfg.d_ff
+    layer_params = 3 * d * h + h * d + 2 * d * ff
+    return 6.0 * cfg.n_layers * layer_params * tokens
+
+
+def bench_train_step(world: int, rank: int, device, dist, steps: int = 5, warmup: int = 3, batch_per_gpu: int = 32,
+                     cfg: StepConfig = StepConfig()):
+    """Tokens/s of the data-parallel step (BASELINE configuration 3): batch sharded by rank,
+    weights replicated, gradients all-reduced per layer bucket over NCCL."""
+    tr = Trainer(cfg, device, world_size=world)
+    batches = [synthetic_batch(cfg, batch_per_gpu, device, seed=1000 * rank + i) for i in range(2)]
+    for i in range(warmup):
+        loss, _ = tr.step(*batches[i % 2])
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        loss, gnorm = tr.step(*batches[i % 2])
+    e1.record()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    tokens = world * batch_per_gpu * cfg.seq_len
+    sec = ms / steps * 1e-3
+    return {
+        "metric": "train_tokens_per_s", "value": tokens / sec, "unit": "tokens/s", "ms_per_step": ms / steps,
+        "steps": steps, "warmup": warmup, "loss": float(loss), "grad_norm": float(gnorm),
+        "mfu_flops_per_s": step_flops(cfg, tokens) / sec,
+        "config": {"layers": cfg.n_layers, "d_model": cfg.d_model, "heads": cfg.n_heads, "d_ff": cfg.d_ff,
+                   "vocab": cfg.vocab_size, "seq": cfg.seq_len, "batch_per_gpu": batch_per_gpu, "activation": cfg.activation,
+                   "mm": cfg.mm, "norm": cfg.norm, "optimizer": "AdamW lr 3e-4", "parallelism": f"dp{world}",
+                   "grad_bytes_allreduced": tr.buckets.bytes(), "data": "tokens uniform over the vocabulary (seeded)"},
+    }
