@@ -451,32 +451,39 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // per-tile state, computed one tile ahead so that the first scale loads are in flight
     // during the previous tile's epilogue
     int m0 = 0, n0 = 0;
-    bool m_ok = false, sb_ok0 = false, sb_ok1 = false;
+    bool m_ok = false, sb_ok = false;
     const float* sa_ptr = p.sa;
-    const float* sb_ptr0 = p.sb;
-    const float* sb_ptr1 = p.sb;
-    float sa_next = 0.f, sb_next0 = 0.f, sb_next1 = 0.f;
+    const float* sb_ptr = p.sb;
+    float sa_next = 0.f;
+    float2 sb_next = make_float2(0.f, 0.f);
+    // per-column scales: lane j stages column c0 + j (32-column warps) or the pair c0 + 2j, c0 + 2j + 1
+    constexpr int kPerLane = kCols / 32;
+    auto load_sb = [&](long long kb) {
+      float2 v = make_float2(0.f, 0.f);
+      if (sb_ok) {
+        const float* q = sb_ptr + kb * p.sb_sk;
+        v.x = __ldg(q);
+        if (SB_GRAN == 1 && kPerLane == 2) v.y = __ldg(q + p.sb_sn);
+      }
+      return v;
+    };
     auto open_tile = [&](int tile) {
       m0 = (tile / p.tiles_n) * BM;
       n0 = (tile % p.tiles_n) * BN;
       const int m = m0 + r;
       m_ok = m < p.M;
       sa_ptr = p.sa + (long long)(m_ok ? m : 0) * p.sa_sm;
-      if (SB_GRAN == 1) {                      // lane j stages the scales of columns c0 + j (and c0 + 32 + j)
-        sb_ok0 = (n0 + c0 + lane) < p.N;
-        sb_ok1 = kCols > 32 && (n0 + c0 + 32 + lane) < p.N;
-        sb_ptr0 = p.sb + (long long)(sb_ok0 ? n0 + c0 + lane : 0) * p.sb_sn;
-        sb_ptr1 = p.sb + (long long)(sb_ok1 ? n0 + c0 + 32 + lane : 0) * p.sb_sn;
-      } else {                                 // one scale per 128 columns
-        sb_ok0 = true;
-        sb_ok1 = false;
+      if (SB_GRAN == 1) {
+        const int col = n0 + c0 + kPerLane * lane;   // N % 8 == 0, so a pair is in or out together
+        sb_ok = col < p.N;
+        sb_ptr = p.sb + (long long)(sb_ok ? col : 0) * p.sb_sn;
+      } else {                                       // one scale per 128 columns
         const int nblk = (n0 + c0) / 128;
-        sb_ptr0 = p.sb + (long long)((nblk * 128 < p.N) ? nblk : 0) * p.sb_sn;
-        sb_ptr1 = sb_ptr0;
+        sb_ok = true;
+        sb_ptr = p.sb + (long long)((nblk * 128 < p.N) ? nblk : 0) * p.sb_sn;
       }
       sa_next = m_ok ? __ldg(sa_ptr) : 0.f;
-      sb_next0 = sb_ok0 ? __ldg(sb_ptr0) : 0.f;
-      sb_next1 = sb_ok1 ? __ldg(sb_ptr1) : 0.f;
+      sb_next = load_sb(0);
     };
 
     if (blockIdx.x < n_tiles) open_tile(blockIdx.x);
@@ -488,16 +495,16 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
       for (int kb = 0; kb < p.nkb; ++kb, ++it) {
         const int buf = it % kTmemBufs;
-        const float sa_v = sa_next, sb_v0 = sb_next0, sb_v1 = sb_next1;
+        const float sa_v = sa_next;
+        const float2 sb_v = sb_next;
         if (kb + 1 < p.nkb) {
           sa_next = m_ok ? __ldg(sa_ptr + (long long)(kb + 1) * p.sa_sk) : 0.f;
-          sb_next0 = sb_ok0 ? __ldg(sb_ptr0 + (long long)(kb + 1) * p.sb_sk) : 0.f;
-          sb_next1 = sb_ok1 ? __ldg(sb_ptr1 + (long long)(kb + 1) * p.sb_sk) : 0.f;
+          sb_next = load_sb(kb + 1);
         }
         float* stage = sb_stage + (it & 1u) * kCols;
         if (SB_GRAN == 1) {
-          stage[lane] = sb_v0;
-          if (kCols > 32) stage[32 + lane] = sb_v1;
+          if (kPerLane == 2) *reinterpret_cast<float2*>(stage + 2 * lane) = sb_v;
+          else stage[lane] = sb_v.x;
           __syncwarp();
         }
         // After an abort the remaining iterations only keep the loop counters in step.
@@ -505,7 +512,7 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (!ok) continue;
         tc_fence_after();
         const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(buf * BN + c0);
-        const float s_scalar = sa_v * sb_v0;
+        const float s_scalar = sa_v * sb_v.x;
         if (kCols > 32) {
           // 64 columns in four 16-column pieces; the buffer goes back after the last load lands
           uint32_t v[16];
@@ -687,9 +694,10 @@ extern "C" int tg_gemm_fp8_blockscaled(const tg_gemm_args* a, void* stream) {
   p.tiles_m = p.tiles_n = 0;
   p.status = a->status;
   const bool g1 = a->sb_gran_n == 1;
-  // 128 x 256 tiles when one scale covers 128 columns; per-column scales cost the promotion
-  // warps twice the arithmetic and 64 columns of them per warp do not fit the register
-  // budget, so that case keeps 128 x 128 tiles.
+  // 128 x 256 tiles when one scale covers 128 columns.  Per-column scales double the
+  // promotion arithmetic and 64 accumulator columns per thread plus their staging do not
+  // fit the 96 registers an 18-warp CTA gets (measured: 2x slower with the spills), so that
+  // case keeps 128 x 128 tiles.
   const bool wide = a->N > 128 && !g1;
   if (wide) return f32 ? launch_gemm<256, 128, true>(a, p, st) : launch_gemm<256, 128, false>(a, p, st);
   if (g1) return f32 ? launch_gemm<128, 1, true>(a, p, st) : launch_gemm<128, 1, false>(a, p, st);

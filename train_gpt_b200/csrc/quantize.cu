@@ -46,8 +46,8 @@ quantize_rowwise_kernel(const uint4* __restrict__ x, uint2* __restrict__ q,
 // 128 x 1 tiles (a scale per column per block of 128 rows).  A thread block owns a
 // 128-row x 128-column panel: a half-warp spans the 128 columns (16 lanes x 8 columns), so
 // each of the 16 half-warps owns every 16th row (8 rows per thread, kept in registers).
-// Column maxima are combined across the half-warps through shared memory, then the same
-// registers are divided and stored.  ~90 registers: two blocks per SM, so one block's loads
+// Column maxima are combined across the warps through shared memory (one thread per column
+// finishes the reduction and the reciprocal), then the same registers are divided and stored.  ~90 registers: two blocks per SM, so one block's loads
 // overlap the other's arithmetic.
 // ---------------------------------------------------------------------------------------
 constexpr int kColPanelCols = 128;
@@ -58,7 +58,8 @@ constexpr int kColRowsPerThread = kTile / kColHalfWarps;  // 8
 __global__ void __launch_bounds__(kColThreads, 2)
 quantize_colwise_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
                         float* __restrict__ scales, int64_t rows, int64_t cols) {
-  __shared__ float s_max[kColHalfWarps][kColPanelCols];
+  __shared__ float s_max[kColThreads / 32][kColPanelCols];
+  __shared__ __align__(16) float s_scale[kColPanelCols], s_rcp[kColPanelCols];
   const int cx = threadIdx.x & 15, hw = threadIdx.x >> 4;
   const int64_t col0 = int64_t(blockIdx.x) * kColPanelCols + cx * 8;
   const int64_t row_blk = blockIdx.y;
@@ -71,45 +72,50 @@ quantize_colwise_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict
     const int64_t row = row0 + r * kColHalfWarps;
     w[r] = (col_ok && row < rows) ? ld_nc_v4(x + row * cols + col0) : make_uint4(0, 0, 0, 0);
   }
-  float m[8];
-#pragma unroll
-  for (int j = 0; j < 8; ++j) m[j] = 0.f;
+  uint32_t m2[4] = {0u, 0u, 0u, 0u};  // packed |.|-maxima of column pairs (0,1) (2,3) (4,5) (6,7)
 #pragma unroll
   for (int r = 0; r < kColRowsPerThread; ++r) {
-    m[0] = max_nan(m[0], fabsf(bf16lo(w[r].x)));
-    m[1] = max_nan(m[1], fabsf(bf16hi(w[r].x)));
-    m[2] = max_nan(m[2], fabsf(bf16lo(w[r].y)));
-    m[3] = max_nan(m[3], fabsf(bf16hi(w[r].y)));
-    m[4] = max_nan(m[4], fabsf(bf16lo(w[r].z)));
-    m[5] = max_nan(m[5], fabsf(bf16hi(w[r].z)));
-    m[6] = max_nan(m[6], fabsf(bf16lo(w[r].w)));
-    m[7] = max_nan(m[7], fabsf(bf16hi(w[r].w)));
+    m2[0] = absmax2(m2[0], w[r].x);
+    m2[1] = absmax2(m2[1], w[r].y);
+    m2[2] = absmax2(m2[2], w[r].z);
+    m2[3] = absmax2(m2[3], w[r].w);
   }
-  float4* dst = reinterpret_cast<float4*>(&s_max[hw][cx * 8]);
-  dst[0] = make_float4(m[0], m[1], m[2], m[3]);
-  dst[1] = make_float4(m[4], m[5], m[6], m[7]);
+  // the two half-warps of a warp hold the same columns: combine them in registers first
+#pragma unroll
+  for (int j = 0; j < 4; ++j) m2[j] = __vmaxu2(m2[j], __shfl_xor_sync(0xffffffffu, m2[j], 16));
+  const int wp = threadIdx.x >> 5;
+  if ((threadIdx.x & 16) == 0) {
+    float4* dst = reinterpret_cast<float4*>(&s_max[wp][cx * 8]);
+    dst[0] = make_float4(__uint_as_float(m2[0] << 16), __uint_as_float(m2[0] & 0xffff0000u),
+                         __uint_as_float(m2[1] << 16), __uint_as_float(m2[1] & 0xffff0000u));
+    dst[1] = make_float4(__uint_as_float(m2[2] << 16), __uint_as_float(m2[2] & 0xffff0000u),
+                         __uint_as_float(m2[3] << 16), __uint_as_float(m2[3] & 0xffff0000u));
+  }
   __syncthreads();
-  float s[8];
+  // one thread per column finishes the maximum, derives scale and reciprocal once, and
+  // publishes both (conflict-free: consecutive threads, consecutive words)
+  if (threadIdx.x < kColPanelCols) {
+    float v = s_max[0][threadIdx.x];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    float v = s_max[0][cx * 8 + j];
-#pragma unroll
-    for (int h = 1; h < kColHalfWarps; ++h) v = max_nan(v, s_max[h][cx * 8 + j]);
-    s[j] = scale_from_amax(v);
+    for (int h = 1; h < kColThreads / 32; ++h) v = max_nan(v, s_max[h][threadIdx.x]);
+    const float sc = scale_from_amax(v);
+    s_scale[threadIdx.x] = sc;
+    s_rcp[threadIdx.x] = __frcp_rn(sc);
+    const int64_t col = int64_t(blockIdx.x) * kColPanelCols + threadIdx.x;
+    if (col < cols) scales[row_blk * cols + col] = sc;
   }
+  __syncthreads();
   if (!col_ok) return;
-  if (hw == 0) {
-    float4* sp = reinterpret_cast<float4*>(scales + row_blk * cols + col0);
-    sp[0] = make_float4(s[0], s[1], s[2], s[3]);
-    sp[1] = make_float4(s[4], s[5], s[6], s[7]);
+  float s[8], rc[8];
+  {
+    const float4 a0 = *reinterpret_cast<const float4*>(&s_scale[cx * 8]), a1 = *reinterpret_cast<const float4*>(&s_scale[cx * 8 + 4]);
+    const float4 b0 = *reinterpret_cast<const float4*>(&s_rcp[cx * 8]), b1 = *reinterpret_cast<const float4*>(&s_rcp[cx * 8 + 4]);
+    s[0] = a0.x; s[1] = a0.y; s[2] = a0.z; s[3] = a0.w; s[4] = a1.x; s[5] = a1.y; s[6] = a1.z; s[7] = a1.w;
+    rc[0] = b0.x; rc[1] = b0.y; rc[2] = b0.z; rc[3] = b0.w; rc[4] = b1.x; rc[5] = b1.y; rc[6] = b1.z; rc[7] = b1.w;
   }
   bool all_finite = true;
-  float rc[8];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    rc[j] = __frcp_rn(s[j]);
-    all_finite = all_finite && (fabsf(s[j]) <= 3.402823466e38f);
-  }
+  for (int j = 0; j < 8; ++j) all_finite = all_finite && (fabsf(s[j]) <= 3.402823466e38f);
 #pragma unroll
   for (int r = 0; r < kColRowsPerThread; ++r) {
     const int64_t row = row0 + r * kColHalfWarps;
@@ -146,16 +152,17 @@ quantize_block128_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restric
   const int64_t col0 = int64_t(blockIdx.x) * kTile + cx * 8;
   const int64_t row0 = int64_t(blockIdx.y) * kTile + ry * 8;
   uint4 w[8];
-  float m = 0.f;
 #pragma unroll
   for (int r = 0; r < 8; ++r) {
     const int64_t row = row0 + r;
     w[r] = (row < rows) ? ld_nc_v4(x + row * cols + col0) : make_uint4(0, 0, 0, 0);
   }
+  uint32_t mb = 0u;
 #pragma unroll
-  for (int r = 0; r < 8; ++r) m = amax8(w[r], m);
+  for (int r = 0; r < 8; ++r) mb = absmax8(w[r], mb);
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) m = max_nan(m, __shfl_xor_sync(0xffffffffu, m, o));
+  for (int o = 16; o > 0; o >>= 1) mb = __vmaxu2(mb, __shfl_xor_sync(0xffffffffu, mb, o));
+  float m = absmax_to_float(mb);
   if ((threadIdx.x & 31) == 0) s_max[threadIdx.x >> 5] = m;
   __syncthreads();
   m = s_max[0];
