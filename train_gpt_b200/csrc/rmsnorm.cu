@@ -51,20 +51,25 @@ __device__ __forceinline__ float row_sum(float v, float* s_red, int warp, int la
   return v;
 }
 
-template <int NCHUNK, int WPR, bool QUANT>
-__global__ void __launch_bounds__(kNormWarps * 32, 2)
+template <int NCHUNK, int WPR, bool QUANT, bool PURE>
+__global__ void __launch_bounds__(kNormWarps * 32, 3)
 rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma,
                    float eps, uint8_t* __restrict__ q, float* __restrict__ scales,
                    __nv_bfloat16* __restrict__ y, float* __restrict__ rnorm_out, int64_t rows,
-                   int cols, int mode) {
+                   int cols) {
   __shared__ float s_red[2][kNormWarps];
   constexpr int RPB = kNormWarps / WPR;  // rows per block per iteration
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int col_base = (warp % WPR) * NCHUNK * 256 + lane * 8;
 
-  // gamma lives in shared memory (not registers) so that two blocks fit on an SM
-  extern __shared__ uint4 s_gamma[];
-  for (int i = threadIdx.x; i < cols / 8; i += blockDim.x) s_gamma[i] = reinterpret_cast<const uint4*>(gamma)[i];
+  // gamma lives in shared memory, already widened to float (one conversion per block
+  // instead of one per row), not in registers, so that more blocks fit on an SM
+  extern __shared__ float4 s_gamma[];
+  for (int i = threadIdx.x; i < cols / 8; i += blockDim.x) {
+    const uint4 gq = reinterpret_cast<const uint4*>(gamma)[i];
+    s_gamma[2 * i] = make_float4(bf16lo(gq.x), bf16hi(gq.x), bf16lo(gq.y), bf16hi(gq.y));
+    s_gamma[2 * i + 1] = make_float4(bf16lo(gq.z), bf16hi(gq.z), bf16lo(gq.w), bf16hi(gq.w));
+  }
   __syncthreads();
 
   int it = 0;
@@ -91,20 +96,23 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     for (int c = 0; c < NCHUNK; ++c) {
       const int col = col_base + c * 256;
       const uint32_t xi[4] = {w[c].x, w[c].y, w[c].z, w[c].w};
-      const uint4 gm = (col < cols) ? s_gamma[col >> 3] : make_uint4(0, 0, 0, 0);
-      const uint32_t gi[4] = {gm.x, gm.y, gm.z, gm.w};
+      float4 g0 = make_float4(0.f, 0.f, 0.f, 0.f), g1 = g0;
+      if (col < cols) {
+        g0 = s_gamma[col >> 2];
+        g1 = s_gamma[(col >> 2) + 1];
+      }
+      const float gf[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
       uint4 yo;
       uint32_t* yp = &yo.x;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        float lo, hi;
-        if (mode == TG_NORM_FUSED) {
-          lo = __fmul_rn(__fmul_rn(bf16lo(xi[j]), rn), bf16lo(gi[j]));
-          hi = __fmul_rn(__fmul_rn(bf16hi(xi[j]), rn), bf16hi(gi[j]));
+        if (!PURE) {
+          const float lo = __fmul_rn(__fmul_rn(bf16lo(xi[j]), rn), gf[2 * j]);
+          const float hi = __fmul_rn(__fmul_rn(bf16hi(xi[j]), rn), gf[2 * j + 1]);
           yp[j] = pack_bf16x2(lo, hi);
         } else {
           const uint32_t t = pack_bf16x2(__fmul_rn(bf16lo(xi[j]), rn_b), __fmul_rn(bf16hi(xi[j]), rn_b));
-          yp[j] = pack_bf16x2(__fmul_rn(bf16lo(t), bf16lo(gi[j])), __fmul_rn(bf16hi(t), bf16hi(gi[j])));
+          yp[j] = pack_bf16x2(__fmul_rn(bf16lo(t), gf[2 * j]), __fmul_rn(bf16hi(t), gf[2 * j + 1]));
         }
       }
       const bool ok = row_ok && col < cols;
@@ -282,12 +290,14 @@ static int launch_fwd(const void* x, const void* gamma, float eps, void* q, floa
   NormGeom g;
   if (!norm_geom(cols, &g)) return cols > 8192 ? TG_ERR_TOO_LARGE : TG_ERR_SHAPE;
   const int blocks = norm_blocks(rows, g.wpr, 16);
-#define TG_FWD_CASE(NC, W)                                                                          \
-  if (g.nchunk == NC && g.wpr == W) {                                                               \
-    rmsnorm_fwd_kernel<NC, W, QUANT><<<blocks, kNormWarps * 32, size_t(cols) * 2, st>>>(                           \
-        static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(gamma), eps,        \
-        static_cast<uint8_t*>(q), scales, static_cast<__nv_bfloat16*>(y), rnorm, rows, int(cols),   \
-        mode);                                                                                      \
+#define TG_FWD_CASE(NC, W)                                                                      \
+  if (g.nchunk == NC && g.wpr == W) {                                                           \
+    auto kern = mode == TG_NORM_PURE ? rmsnorm_fwd_kernel<NC, W, QUANT, true>                   \
+                                     : rmsnorm_fwd_kernel<NC, W, QUANT, false>;                 \
+    kern<<<blocks, kNormWarps * 32, size_t(cols) * 4, st>>>(                                    \
+        static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(gamma), eps,    \
+        static_cast<uint8_t*>(q), scales, static_cast<__nv_bfloat16*>(y), rnorm, rows,          \
+        int(cols));                                                                             \
   } else
   TG_FWD_CASE(1, 1) TG_FWD_CASE(2, 1) TG_FWD_CASE(4, 1) TG_FWD_CASE(8, 1) TG_FWD_CASE(8, 2)
   TG_FWD_CASE(8, 4) { return TG_ERR_SHAPE; }
