@@ -133,6 +133,8 @@ def run_reference(args):
         return
     import torch
     from oracle import cpu_baseline as cb
+    # torchrun pins OMP_NUM_THREADS=1 per rank; this arm is one process meant to use every host core
+    torch.set_num_threads(os.cpu_count() or 1)
     cores = torch.get_num_threads()
     m = args.cpu_sample_tokens
     times = []
@@ -177,6 +179,9 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        # keep stdout to the one JSON line: NCCL prints its version banner there at VERSION/INFO
+        if os.environ.get("NCCL_DEBUG", "VERSION").upper() in ("VERSION", ""):
+            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=dev)
 
     tile = (128, 128) if args.weight_tile == "128x128" else (128, 1)
@@ -294,6 +299,7 @@ def main():
         out["e2e"] = e2e
     if rank == 0 and not args.no_cpu_baseline and world == 1:
         from oracle import cpu_baseline as cb
+        torch.set_num_threads(os.cpu_count() or 1)
         m = args.cpu_sample_tokens
         sec, fl = cb.time_linear_set(LAYER_SHAPES, m)
         out["cpu_baseline"] = {"value": fl / sec / 1e12, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
