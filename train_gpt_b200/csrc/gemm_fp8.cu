@@ -24,7 +24,9 @@
 //                rule) and owns accumulator columns (BN/4)*((w-2)/4)..; four warps per
 //                scheduler hide each other's TMEM-load latency.  Each warp stores its own
 //                32 x BN/4 piece of the tile: registers -> its private swizzled staging
-//                area -> TMA store, with no cross-warp barrier.
+//                rows -> 16-byte global stores that cover whole 128-byte lines; no cross-warp
+//                barrier, no asynchronous-proxy fence or wait (a TMA-store epilogue measured
+//                ~2300 cycles per tile, most of it in those waits).
 //
 // Operand orientation is data, not code: the TMA box is 128 bytes x 128 rows for both
 // K-major and MN-major storage (only the coordinates swap), and the shared-memory operand
@@ -92,6 +94,8 @@ struct GemmParams {
   long long sa_sm, sa_sk;
   const float* sb;
   long long sb_sn, sb_sk;
+  void* d;              // output, row pitch ldd elements
+  long long ldd;
   int M, N, nkb;
   int a_mn, b_mn;       // 1 = MN-major storage
   int tiles_m, tiles_n;
@@ -269,16 +273,6 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
   return d;
 }
 
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
-               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(x), "r"(y)
-               : "memory");
-}
-__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-// all committed stores have finished READING shared memory (the staging area may be reused)
-__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-// make this thread's generic-proxy shared-memory writes visible to the async (TMA) proxy
-__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
 }
@@ -312,8 +306,7 @@ __device__ __forceinline__ void promote(float2* acc, const uint32_t (&v)[NC], co
 template <int BN_, int SB_GRAN, bool OUT_F32>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                            const __grid_constant__ CUtensorMap tmap_b,
-                            const __grid_constant__ CUtensorMap tmap_d, const GemmParams p) {
+                            const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
   using C = Cfg<BN_, SB_GRAN, OUT_F32>;
   constexpr int BN = C::BN, kStages = C::stages, kTmemBufs = C::tmem_bufs, kCols = C::cols_per_warp;
   extern __shared__ uint8_t smem_raw[];
@@ -345,7 +338,6 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_a)) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_b)) : "memory");
-    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_d)) : "memory");
   }
   if (warp == 1) {
     tmem_alloc(sbase + C::off_tmem_ptr, kTmemCols);
@@ -543,40 +535,48 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
       // start the next tile's first scale loads before the stores of this one
       if (tile + int(gridDim.x) < n_tiles) open_tile(tile + gridDim.x);
 
-      // ---- epilogue: registers -> this warp's swizzled staging rows -> TMA store ----------
+      // ---- epilogue: registers -> this warp's swizzled staging rows -> coalesced stores ------
+      // Each thread holds one row; a warp-private transpose through shared memory lets every
+      // store instruction write whole 128-byte lines (4 or 8 rows x one staging row each).  No
+      // asynchronous proxy is involved, so there is nothing to fence or wait for: the warp's
+      // own program order (plus __syncwarp) protects the staging rows.
       if (!ok) continue;
-      const int row0 = tile_m0 + quarter * 32;
+      const int row_base = tile_m0 + quarter * 32;
+      constexpr int PRB = C::phase_row_bytes, LPR = PRB / 16, RPI = 32 / LPR;
+      uint8_t* warp_out = smem + C::off_out + pw * C::warp_out_bytes;
+      const int my_chunk = lane % LPR;
 #pragma unroll
       for (int ph = 0; ph < C::phases; ++ph) {
-        if (lane == 0) tma_store_wait_read();  // this warp's earlier stores have let go of the staging rows
-        __syncwarp();
+        __syncwarp();  // the previous read-back of these staging rows is complete
         if (OUT_F32) {
 #pragma unroll
-          for (int c = 0; c < C::phase_row_bytes / 16; ++c) {   // 4 floats per 16-byte chunk
+          for (int c = 0; c < PRB / 16; ++c) {   // 4 floats per 16-byte chunk
             const int j = ph * (C::phase_cols / 2) + 2 * c;
             st_shared_v4(out_base + (uint32_t(c ^ swz) << 4), __float_as_uint(acc[j].x), __float_as_uint(acc[j].y),
                          __float_as_uint(acc[j + 1].x), __float_as_uint(acc[j + 1].y));
           }
         } else {
 #pragma unroll
-          for (int c = 0; c < C::phase_row_bytes / 16; ++c) {   // 8 bf16 per 16-byte chunk
+          for (int c = 0; c < PRB / 16; ++c) {   // 8 bf16 per 16-byte chunk
             const int j = ph * (C::phase_cols / 2) + 4 * c;
             st_shared_v4(out_base + (uint32_t(c ^ swz) << 4), pack_bf16x2(acc[j].x, acc[j].y),
                          pack_bf16x2(acc[j + 1].x, acc[j + 1].y), pack_bf16x2(acc[j + 2].x, acc[j + 2].y),
                          pack_bf16x2(acc[j + 3].x, acc[j + 3].y));
           }
         }
-        fence_proxy_async_smem();
         __syncwarp();
-        const int col = tile_n0 + c0 + ph * C::phase_cols;
-        if (lane == 0 && col < p.N && row0 < p.M) {
-          tma_store_2d(&tmap_d, sbase + C::off_out + uint32_t(pw) * C::warp_out_bytes, col, row0);
-          tma_store_commit();
+        const int col = tile_n0 + c0 + ph * C::phase_cols + my_chunk * (16 / C::esize);
+        uint8_t* dcol = static_cast<uint8_t*>(p.d) + (long long)col * C::esize;
+#pragma unroll
+        for (int i = 0; i < 32 / RPI; ++i) {
+          const int rr = i * RPI + lane / LPR;
+          const int sw = PRB == 128 ? (rr & 7) : ((rr >> 1) & 3);
+          const uint4 val = *reinterpret_cast<const uint4*>(warp_out + rr * PRB + ((my_chunk ^ sw) << 4));
+          if (row_base + rr < p.M && col < p.N)
+            *reinterpret_cast<uint4*>(dcol + (long long)(row_base + rr) * p.ldd * C::esize) = val;
         }
       }
     }
-    if (lane == 0) tma_store_wait_read();
-    __syncwarp();
   }
 
   // ------------------------------ teardown ----------------------------------------------
@@ -631,14 +631,11 @@ template <int BN_, int SB_GRAN, bool OUT_F32>
 static int launch_gemm(const tg_gemm_args* a, GemmParams p, cudaStream_t st) {
   using C = Cfg<BN_, SB_GRAN, OUT_F32>;
   auto kern = gemm_fp8_blockscaled_kernel<BN_, SB_GRAN, OUT_F32>;
-  CUtensorMap ta, tb, td;
+  CUtensorMap ta, tb;
   const int64_t a_inner = p.a_mn ? a->M : a->K, a_outer = p.a_mn ? a->K : a->M;
   const int64_t b_inner = p.b_mn ? a->N : a->K, b_outer = p.b_mn ? a->K : a->N;
   if (int rc = make_tmap(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a->a, a_inner, a_outer, a->lda, 128, 128)) return rc;
   if (int rc = make_tmap(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a->b, b_inner, b_outer, a->ldb, 128, 128)) return rc;
-  if (int rc = make_tmap(&td, OUT_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, C::esize, a->d,
-                         a->N, a->M, a->ldd * C::esize, C::phase_row_bytes, 32))
-    return rc;
   p.tiles_m = int((a->M + BM - 1) / BM);
   p.tiles_n = int((a->N + BN_ - 1) / BN_);
   const int64_t n_tiles = int64_t(p.tiles_m) * p.tiles_n;
@@ -654,7 +651,7 @@ static int launch_gemm(const tg_gemm_args* a, GemmParams p, cudaStream_t st) {
     TG_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::smem_bytes));
     attr_set[dev] = true;
   }
-  kern<<<grid, kGemmThreads, C::smem_bytes, st>>>(ta, tb, td, p);
+  kern<<<grid, kGemmThreads, C::smem_bytes, st>>>(ta, tb, p);
   TG_CUDA_CHECK(cudaGetLastError());
   return TG_OK;
 }
@@ -689,6 +686,7 @@ extern "C" int tg_gemm_fp8_blockscaled(const tg_gemm_args* a, void* stream) {
   GemmParams p;
   p.sa = a->sa; p.sa_sm = a->sa_stride_m; p.sa_sk = a->sa_stride_kb;
   p.sb = a->sb; p.sb_sn = a->sb_stride_n; p.sb_sk = a->sb_stride_kb;
+  p.d = a->d; p.ldd = a->ldd;
   p.M = int(a->M); p.N = int(a->N); p.nkb = int((a->K + BK - 1) / BK);
   p.a_mn = a->a_major == TG_MAJOR_MN; p.b_mn = a->b_major == TG_MAJOR_MN;
   p.tiles_m = p.tiles_n = 0;
