@@ -37,6 +37,7 @@
 // CTA-wide abort flag, stores a code in *status, and all roles fall through to the common
 // teardown (TMEM is always freed).
 #include <cuda.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 
@@ -55,12 +56,12 @@ constexpr int kSmemLimit = 227 * 1024;
 constexpr long long kWaitLimitCycles = 4000000000LL;  // ~2 s at 2 GHz
 
 // Compile-time plan of one kernel variant.
-template <int BN_, int SB_GRAN, bool OUT_F32>
+template <int BN_, int SB_GRAN, bool OUT_F32, bool CTA2>
 struct Cfg {
   static constexpr int BN = BN_;
   static constexpr int tmem_bufs = kTmemCols / BN;            // 2 or 4
   static constexpr int cols_per_warp = BN / 4;                // 64 or 32
-  static constexpr int b_boxes = BN / 128;
+  static constexpr int b_boxes = CTA2 ? 1 : BN / 128;         // a CTA of a pair loads half of B
   static constexpr int stage_bytes = kTileBytes * (1 + b_boxes);
   static constexpr int esize = OUT_F32 ? 4 : 2;
   // epilogue: a warp stages its 32 rows x `phase_cols` columns at a time (rows of <= 128
@@ -80,7 +81,12 @@ struct Cfg {
   static constexpr int off_out = stages * stage_bytes;
   static constexpr int off_sb = off_out + out_bytes;
   static constexpr int off_bars = off_sb + sb_bytes;
-  static constexpr int n_bars = 2 * stages + 2 * tmem_bufs + kIssuers;
+  // (handing the wide accumulator over in two 128-column halves, each with its own barriers
+  // and N=128 MMAs, was tried: 7 % slower -- A is read twice and twice as many MMAs issue)
+  static constexpr int halves = 1;
+  static constexpr int n_tbars = tmem_bufs * halves;
+  static constexpr int n_bars = 2 * stages + 2 * n_tbars + kIssuers;
+  static_assert(!CTA2 || BN == 256, "the 2-CTA variant is built for 256-column tiles");
   static constexpr int off_tmem_ptr = off_bars + n_bars * 8;
   static constexpr int off_abort = off_tmem_ptr + 4;
   static constexpr int smem_bytes = off_bars + misc_bytes + 1024;  // + slack for manual alignment
@@ -256,6 +262,60 @@ __device__ __forceinline__ void tmem_wait_ld16(uint32_t (&v)[16]) {
       : "memory");
 }
 
+// ---- CTA-pair (cta_group::2) variants ---------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// address of the same shared-memory offset in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t mapa(uint32_t local_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t cluster_addr, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_addr), "r"(bytes) : "memory");
+}
+// TMA load into THIS CTA's shared memory whose completion is counted on a barrier that may
+// live in the pair's other CTA (no multicast: each CTA fetches its own boxes)
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+// arrive (when the issuing thread's MMAs retire) on the barrier at this offset in BOTH CTAs
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"(uint16_t(3)) : "memory");
+}
+__device__ __forceinline__ void umma_f8_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // Shared-memory operand descriptor, 128-byte swizzle, 8-row groups 1024 bytes apart.
 //   bits  0-13 start address >> 4      bits 16-29 leading byte offset >> 4
 //   bits 32-45 stride byte offset >> 4 bits 46-47 descriptor version (1 on sm_100)
@@ -303,11 +363,11 @@ __device__ __forceinline__ void promote(float2* acc, const uint32_t (&v)[NC], co
   }
 }
 
-template <int BN_, int SB_GRAN, bool OUT_F32>
+template <int BN_, int SB_GRAN, bool OUT_F32, bool CTA2>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
                             const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
-  using C = Cfg<BN_, SB_GRAN, OUT_F32>;
+  using C = Cfg<BN_, SB_GRAN, OUT_F32, CTA2>;
   constexpr int BN = C::BN, kStages = C::stages, kTmemBufs = C::tmem_bufs, kCols = C::cols_per_warp;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -316,22 +376,31 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (kStages + s); };
   auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * kStages + b); };
-  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * kStages + kTmemBufs + b); };
-  auto drain_bar = [&](int i) { return bar0 + 8u * (2 * kStages + 2 * kTmemBufs + i); };
+  constexpr int kHalves = C::halves, kTBars = C::n_tbars;
+  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * kStages + kTBars + b); };
+  auto drain_bar = [&](int i) { return bar0 + 8u * (2 * kStages + 2 * kTBars + i); };
   volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem + C::off_tmem_ptr);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::off_abort);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_tiles = p.tiles_m * p.tiles_n;
+  // A pair (cluster of two CTAs) shares one 256 x 256 tile: CTA r of the pair owns rows
+  // r*128.. of it (its A tile, its TMEM, its output rows) and fetches B rows r*128.. for both.
+  const uint32_t crank = CTA2 ? cluster_ctarank() : 0u;
+  const bool leader = crank == 0;
+  const int first_tile = CTA2 ? int(blockIdx.x >> 1) : int(blockIdx.x);
+  const int tile_step = CTA2 ? int(gridDim.x >> 1) : int(gridDim.x);
+  const int row_off = int(crank) * BM;         // this CTA's rows inside the (pair) tile
+  constexpr int TM = CTA2 ? 2 * BM : BM;       // rows of a tile
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(full_bar(s), 1);
+      mbar_init(full_bar(s), CTA2 ? 2 : 1);   // one expect_tx arrival per CTA of the pair
       mbar_init(empty_bar(s), 1);
     }
-    for (int b = 0; b < kTmemBufs; ++b) {
+    for (int b = 0; b < kTBars; ++b) {
       mbar_init(tfull_bar(b), 1);
-      mbar_init(tempty_bar(b), kPromoWarps);
+      mbar_init(tempty_bar(b), CTA2 ? 2 * kPromoWarps : kPromoWarps / kHalves);
     }
     for (int i = 0; i < kIssuers; ++i) mbar_init(drain_bar(i), 1);
     *abort_flag = 0;
@@ -340,11 +409,17 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_b)) : "memory");
   }
   if (warp == 1) {
-    tmem_alloc(sbase + C::off_tmem_ptr, kTmemCols);
-    tmem_relinquish();
+    if (CTA2) {
+      tmem_alloc_pair(sbase + C::off_tmem_ptr, kTmemCols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(sbase + C::off_tmem_ptr, kTmemCols);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (CTA2) cluster_sync_all();   // both CTAs' barriers exist before anyone signals across
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_smem;
 
@@ -354,48 +429,58 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
       // The whole warp walks the loop (uniform control flow); one elected lane issues.
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
-        const int m0 = (tile / p.tiles_n) * BM, n0 = (tile % p.tiles_n) * BN;
+      for (int tile = first_tile; ok && tile < n_tiles; tile += tile_step) {
+        const int m0 = (tile / p.tiles_n) * TM + row_off, n0 = (tile % p.tiles_n) * BN;
         for (int kb = 0; kb < p.nkb; ++kb, ++it) {
           const int s = it % kStages;
           ok = __all_sync(0xffffffffu, mbar_wait(empty_bar(s), ((it / kStages) & 1u) ^ 1u, abort_flag, p.status, 1u));
           if (!ok) break;
           if (elect_one()) {
-            mbar_expect_tx(full_bar(s), C::stage_bytes);
             const int k0 = kb * BK;
             const uint32_t dst = sbase + s * C::stage_bytes;
-            tma_load_2d(dst, &tmap_a, full_bar(s), p.a_mn ? m0 : k0, p.a_mn ? k0 : m0);
+            if (CTA2) {
+              // both CTAs count their bytes on the LEADER's barrier: its MMA thread consumes both halves
+              const uint32_t bar = mapa(full_bar(s), 0u);
+              mbar_expect_tx_cluster(bar, C::stage_bytes);
+              const int nb = n0 + int(crank) * 128;
+              tma_load_2d_pair(dst, &tmap_a, bar, p.a_mn ? m0 : k0, p.a_mn ? k0 : m0);
+              tma_load_2d_pair(dst + kTileBytes, &tmap_b, bar, p.b_mn ? nb : k0, p.b_mn ? k0 : nb);
+            } else {
+              mbar_expect_tx(full_bar(s), C::stage_bytes);
+              tma_load_2d(dst, &tmap_a, full_bar(s), p.a_mn ? m0 : k0, p.a_mn ? k0 : m0);
 #pragma unroll
-            for (int b = 0; b < C::b_boxes; ++b) {
-              const int nb = n0 + b * 128;  // a box wholly past N is still loaded: it arrives as zeros
-              tma_load_2d(dst + (1 + b) * kTileBytes, &tmap_b, full_bar(s), p.b_mn ? nb : k0, p.b_mn ? k0 : nb);
+              for (int b = 0; b < C::b_boxes; ++b) {
+                const int nb = n0 + b * 128;  // a box wholly past N is still loaded: it arrives as zeros
+                tma_load_2d(dst + (1 + b) * kTileBytes, &tmap_b, full_bar(s), p.b_mn ? nb : k0, p.b_mn ? k0 : nb);
+              }
             }
           }
           __syncwarp();
         }
       }
-    } else if (warp <= kIssuers) {
+    } else if (warp <= kIssuers && leader) {
       // ------------------------------ MMA issuers --------------------------------------
       // Issuer i takes the contraction blocks with (global block counter) % kIssuers == i.
       // Blocks are independent: each has its own TMEM buffer and shared-memory stage.
       const int issuer = warp - 1;
       // instruction descriptor: D f32 (bit 4), A/B e4m3 (0), major bits 15/16, N>>3 at 17, M>>4 at 24
       const uint32_t idesc = (1u << 4) | (uint32_t(p.a_mn) << 15) | (uint32_t(p.b_mn) << 16) |
-                             (uint32_t(BN >> 3) << 17) | (uint32_t(BM >> 4) << 24);
+                             (uint32_t((BN / C::halves) >> 3) << 17) | (uint32_t(TM >> 4) << 24);
       // descriptor start-address step per UMMA_K: 32 bytes along a K-major row, 32 rows of 128 B otherwise
       const uint32_t a_step = p.a_mn ? (UMMA_K * 128) >> 4 : UMMA_K >> 4;
       const uint32_t b_step = p.b_mn ? (UMMA_K * 128) >> 4 : UMMA_K >> 4;
       const uint64_t a_desc0 = make_smem_desc(sbase);
       const uint64_t b_desc0 = make_smem_desc(sbase + kTileBytes);
       int my_tiles = 0;
-      for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) ++my_tiles;
+      for (int tile = first_tile; tile < n_tiles; tile += tile_step) ++my_tiles;
       const uint32_t total = uint32_t(my_tiles) * uint32_t(p.nkb);
       bool ok = true;
       bool ready = false;  // barriers of block `it` already seen complete by an early probe
       for (uint32_t it = issuer; ok && it < total; it += kIssuers) {
         const int s = it % kStages, buf = it % kTmemBufs;
+        const uint32_t tpar = ((it / kTmemBufs) & 1u) ^ 1u;
         if (!ready) {
-          ok = __all_sync(0xffffffffu, mbar_wait(tempty_bar(buf), ((it / kTmemBufs) & 1u) ^ 1u, abort_flag, p.status, 2u) &&
+          ok = __all_sync(0xffffffffu, mbar_wait(tempty_bar(buf * kHalves), tpar, abort_flag, p.status, 2u) &&
                                            mbar_wait(full_bar(s), (it / kStages) & 1u, abort_flag, p.status, 3u));
           if (!ok) break;
         }
@@ -404,24 +489,35 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const uint32_t nx = it + kIssuers;
         bool nx_ready = false;
         if (nx < total)
-          nx_ready = mbar_test(tempty_bar(nx % kTmemBufs), ((nx / kTmemBufs) & 1u) ^ 1u) &
+          nx_ready = mbar_test(tempty_bar((nx % kTmemBufs) * kHalves), ((nx / kTmemBufs) & 1u) ^ 1u) &
                      mbar_test(full_bar(nx % kStages), (nx / kStages) & 1u);
-        if (elect_one()) {
-          const uint64_t a_desc = a_desc0 + uint64_t((s * C::stage_bytes) >> 4);
-          const uint64_t b_desc = b_desc0 + uint64_t((s * C::stage_bytes) >> 4);
-          const uint32_t d_tmem = tmem_base + uint32_t(buf * BN);
+        const uint64_t a_desc = a_desc0 + uint64_t((s * C::stage_bytes) >> 4);
+        const uint64_t b_desc = b_desc0 + uint64_t((s * C::stage_bytes) >> 4);
+        const uint32_t d_tmem = tmem_base + uint32_t(buf * BN);
+        if (CTA2) {
+          if (elect_one()) {
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k)
-            umma_f8(d_tmem, a_desc + uint64_t(k * a_step), b_desc + uint64_t(k * b_step), idesc, k > 0 ? 1u : 0u);
-          umma_commit(empty_bar(s));    // shared-memory stage free once these MMAs retire
-          umma_commit(tfull_bar(buf));  // accumulator buffer ready for promotion
+            for (int k = 0; k < BK / UMMA_K; ++k)
+              umma_f8_pair(d_tmem, a_desc + uint64_t(k * a_step), b_desc + uint64_t(k * b_step), idesc, k > 0 ? 1u : 0u);
+            umma_commit_pair(empty_bar(s));    // frees the stage in both CTAs
+            umma_commit_pair(tfull_bar(buf));  // both CTAs' promotion warps may read their half
+          }
+        } else {
+          if (elect_one()) {
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k)
+              umma_f8(d_tmem, a_desc + uint64_t(k * a_step), b_desc + uint64_t(k * b_step), idesc, k > 0 ? 1u : 0u);
+            umma_commit(empty_bar(s));    // shared-memory stage free once these MMAs retire
+            umma_commit(tfull_bar(buf));  // accumulator buffer ready for promotion
+          }
         }
         __syncwarp();
         ready = __all_sync(0xffffffffu, nx_ready);
       }
       // make sure nothing issued here is still running when TMEM is freed
       if (elect_one()) {
-        umma_commit(drain_bar(issuer));
+        if (CTA2) asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(drain_bar(issuer)) : "memory");
+        else umma_commit(drain_bar(issuer));
         mbar_wait(drain_bar(issuer), 0u, abort_flag, p.status, 4u);
       }
       __syncwarp();
@@ -460,7 +556,7 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
       return v;
     };
     auto open_tile = [&](int tile) {
-      m0 = (tile / p.tiles_n) * BM;
+      m0 = (tile / p.tiles_n) * TM + row_off;
       n0 = (tile % p.tiles_n) * BN;
       const int m = m0 + r;
       m_ok = m < p.M;
@@ -478,8 +574,9 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
       sb_next = load_sb(0);
     };
 
-    if (blockIdx.x < n_tiles) open_tile(blockIdx.x);
-    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+    if (first_tile < n_tiles) open_tile(first_tile);
+    const uint32_t tempty_remote0 = CTA2 ? mapa(tempty_bar(0), 0u) : 0u;  // the leader's barrier, as seen from here
+    for (int tile = first_tile; tile < n_tiles; tile += tile_step) {
       const int tile_m0 = m0, tile_n0 = n0;
       float2 acc[kCols / 2];
 #pragma unroll
@@ -500,7 +597,8 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
           __syncwarp();
         }
         // After an abort the remaining iterations only keep the loop counters in step.
-        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar(buf), (it / kTmemBufs) & 1u, abort_flag, p.status, 5u));
+        const int tb = buf * kHalves + (kHalves == 2 ? (cg >> 1) : 0);   // this warp's half of the buffer
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar(tb), (it / kTmemBufs) & 1u, abort_flag, p.status, 5u));
         if (!ok) continue;
         tc_fence_after();
         const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(buf * BN + c0);
@@ -518,7 +616,7 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
           tmem_wait_ld16(v);
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(tempty_bar(buf));
+          if (lane == 0) { if (CTA2) mbar_arrive_cluster(tempty_remote0 + 8u * buf); else mbar_arrive(tempty_bar(tb)); }
           promote<SB_GRAN, 16>(acc + 24, v, stage + 48, sa_v, s_scalar);
         } else {
           uint32_t v[32];
@@ -527,13 +625,13 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
           // every partial sum of the buffer is in registers: hand it back to the tensor core
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(tempty_bar(buf));
+          if (lane == 0) { if (CTA2) mbar_arrive_cluster(tempty_remote0 + 8u * buf); else mbar_arrive(tempty_bar(tb)); }
           promote<SB_GRAN, 32>(acc, v, stage, sa_v, s_scalar);
         }
       }
 
       // start the next tile's first scale loads before the stores of this one
-      if (tile + int(gridDim.x) < n_tiles) open_tile(tile + gridDim.x);
+      if (tile + tile_step < n_tiles) open_tile(tile + tile_step);
 
       // ---- epilogue: registers -> this warp's swizzled staging rows -> coalesced stores ------
       // Each thread holds one row; a warp-private transpose through shared memory lets every
@@ -582,10 +680,12 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
   // ------------------------------ teardown ----------------------------------------------
   tc_fence_before();
   __syncthreads();
+  if (CTA2) cluster_sync_all();   // the peer no longer reads this CTA's shared memory or signals its barriers
   if (warp == 1) {
     __syncwarp();
     tc_fence_after();
-    tmem_dealloc(tmem_base, kTmemCols);
+    if (CTA2) tmem_dealloc_pair(tmem_base, kTmemCols);
+    else tmem_dealloc(tmem_base, kTmemCols);
   }
 }
 
@@ -627,21 +727,22 @@ static int make_tmap(CUtensorMap* map, CUtensorMapDataType dt, int esize, const 
   return TG_OK;
 }
 
-template <int BN_, int SB_GRAN, bool OUT_F32>
+template <int BN_, int SB_GRAN, bool OUT_F32, bool CTA2 = false>
 static int launch_gemm(const tg_gemm_args* a, GemmParams p, cudaStream_t st) {
-  using C = Cfg<BN_, SB_GRAN, OUT_F32>;
-  auto kern = gemm_fp8_blockscaled_kernel<BN_, SB_GRAN, OUT_F32>;
+  using C = Cfg<BN_, SB_GRAN, OUT_F32, CTA2>;
+  auto kern = gemm_fp8_blockscaled_kernel<BN_, SB_GRAN, OUT_F32, CTA2>;
   CUtensorMap ta, tb;
   const int64_t a_inner = p.a_mn ? a->M : a->K, a_outer = p.a_mn ? a->K : a->M;
   const int64_t b_inner = p.b_mn ? a->N : a->K, b_outer = p.b_mn ? a->K : a->N;
   if (int rc = make_tmap(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a->a, a_inner, a_outer, a->lda, 128, 128)) return rc;
   if (int rc = make_tmap(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a->b, b_inner, b_outer, a->ldb, 128, 128)) return rc;
-  p.tiles_m = int((a->M + BM - 1) / BM);
+  constexpr int TM = CTA2 ? 2 * BM : BM;
+  p.tiles_m = int((a->M + TM - 1) / TM);
   p.tiles_n = int((a->N + BN_ - 1) / BN_);
   const int64_t n_tiles = int64_t(p.tiles_m) * p.tiles_n;
   if (n_tiles > INT32_MAX || n_tiles * p.nkb > INT32_MAX) return TG_ERR_TOO_LARGE;
   const int sms = sm_count();
-  const int grid = int(n_tiles < sms ? n_tiles : sms);
+  int grid = int(n_tiles < sms ? n_tiles : sms);
   // the attribute is per device: set it once for each device this instantiation runs on
   static bool attr_set[64] = {};
   int dev = 0;
@@ -651,7 +752,45 @@ static int launch_gemm(const tg_gemm_args* a, GemmParams p, cudaStream_t st) {
     TG_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::smem_bytes));
     attr_set[dev] = true;
   }
-  kern<<<grid, kGemmThreads, C::smem_bytes, st>>>(ta, tb, p);
+  if (CTA2) {
+    // A persistent grid must be co-resident.  Pairs need two free SMs in one GPC, and GPCs
+    // with an odd SM count strand one, so ask the runtime how many pairs fit (cached per device).
+    static int max_pairs[64] = {};
+    if (max_pairs[dev] == 0) {
+      cudaLaunchConfig_t q = {};
+      q.gridDim = dim3(2 * (sms / 2));
+      q.blockDim = dim3(kGemmThreads);
+      q.dynamicSmemBytes = C::smem_bytes;
+      cudaLaunchAttribute qa[1];
+      qa[0].id = cudaLaunchAttributeClusterDimension;
+      qa[0].val.clusterDim.x = 2;
+      qa[0].val.clusterDim.y = 1;
+      qa[0].val.clusterDim.z = 1;
+      q.attrs = qa;
+      q.numAttrs = 1;
+      int n = 0;
+      TG_CUDA_CHECK(cudaOccupancyMaxActiveClusters(&n, kern, &q));
+      if (n < 1) return record_cuda_error(cudaErrorLaunchOutOfResources, "no CTA pair fits on this device");
+      max_pairs[dev] = n;
+    }
+    const int pairs = max_pairs[dev];
+    grid = 2 * int(n_tiles < pairs ? n_tiles : pairs);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = C::smem_bytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    TG_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, ta, tb, p));
+  } else {
+    kern<<<grid, kGemmThreads, C::smem_bytes, st>>>(ta, tb, p);
+  }
   TG_CUDA_CHECK(cudaGetLastError());
   return TG_OK;
 }
@@ -697,6 +836,12 @@ extern "C" int tg_gemm_fp8_blockscaled(const tg_gemm_args* a, void* stream) {
   // fit the 96 registers an 18-warp CTA gets (measured: 2x slower with the spills), so that
   // case keeps 128 x 128 tiles.
   const bool wide = a->N > 128 && !g1;
+  // CTA pairs (cta_group::2, 256 x 256 tiles, half the B bytes per CTA) are built and pass the
+  // parity tests, but measure SLOWER than one CTA per tile (1.03 vs 1.70 PFLOP/s forward): with
+  // only two 256-column TMEM buffers the barrier round trip through both CTAs' promotion warps
+  // is longer than one block of tensor work.  Kept behind TG_GEMM_PAIR=1 for the next attempt.
+  if (wide && a->M > 128 && getenv("TG_GEMM_PAIR") != nullptr)
+    return f32 ? launch_gemm<256, 128, true, true>(a, p, st) : launch_gemm<256, 128, false, true>(a, p, st);
   if (wide) return f32 ? launch_gemm<256, 128, true>(a, p, st) : launch_gemm<256, 128, false>(a, p, st);
   if (g1) return f32 ? launch_gemm<128, 1, true>(a, p, st) : launch_gemm<128, 1, false>(a, p, st);
   return f32 ? launch_gemm<128, 128, true>(a, p, st) : launch_gemm<128, 128, false>(a, p, st);
