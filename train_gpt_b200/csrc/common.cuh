@@ -109,6 +109,41 @@ __device__ __forceinline__ uint2 quantize8(const uint4& w, float scale) {
   return make_uint2(b0 | (b1 << 16), b2 | (b3 << 16));
 }
 
+// Quantise 8 values with a scale s and its reciprocal r = RN(1/s) that the caller already
+// has (finite scale): q = fma(-fma(x*r, s, -x), r, x*r) per value, see QuantDiv.
+__device__ __forceinline__ uint2 quantize8_sr(const uint4& w, float s, float r) {
+  QuantDiv d(1.0f);
+  d.s = s;
+  d.r = r;
+  const uint32_t b0 = cvt_e4m3x2(d.div(bf16lo(w.x)), d.div(bf16hi(w.x)));
+  const uint32_t b1 = cvt_e4m3x2(d.div(bf16lo(w.y)), d.div(bf16hi(w.y)));
+  const uint32_t b2 = cvt_e4m3x2(d.div(bf16lo(w.z)), d.div(bf16hi(w.z)));
+  const uint32_t b3 = cvt_e4m3x2(d.div(bf16lo(w.w)), d.div(bf16hi(w.w)));
+  return make_uint2(b0 | (b1 << 16), b2 | (b3 << 16));
+}
+
+// The scale arithmetic (an IEEE division by 448, a max, a correctly rounded reciprocal: ~20
+// instructions) is the same for all 16 lanes that share a tile.  When a warp has N tiles'
+// amax values in registers (N <= 16, a power of two, every lane of a half-warp holding the N
+// values of that half), lane j of each half computes tile j % N only and the results travel
+// back by shuffle: N x 20 instructions become 20 + 2 N.  `fin` is false if any scale of the
+// warp is not finite (the caller then takes the IEEE-division path).
+template <int N>
+__device__ __forceinline__ void tile_scales(const float (&amax)[N], float (&s)[N], float (&r)[N], float& s_mine, bool& fin) {
+  const int lane = threadIdx.x & 31, j = lane & (N - 1);
+  float msel = amax[0];
+#pragma unroll
+  for (int u = 1; u < N; ++u) msel = (j == u) ? amax[u] : msel;
+  s_mine = scale_from_amax(msel);
+  const float r_mine = __frcp_rn(s_mine);
+  fin = __all_sync(0xffffffffu, fabsf(s_mine) <= 3.402823466e38f);
+#pragma unroll
+  for (int u = 0; u < N; ++u) {
+    s[u] = __shfl_sync(0xffffffffu, s_mine, (lane & 16) | u);
+    r[u] = __shfl_sync(0xffffffffu, r_mine, (lane & 16) | u);
+  }
+}
+
 // |.|-max of bf16 values WITHOUT unpacking them: with the sign bit cleared, bf16 bit patterns
 // order like unsigned integers (0 < subnormals < normals < Inf 0x7F80 < NaN 0x7F81..), so a
 // per-halfword unsigned max of two packed words is the max of magnitudes, and a NaN wins as

@@ -51,8 +51,10 @@ __device__ __forceinline__ float row_sum(float v, float* s_red, int warp, int la
   return v;
 }
 
+// Two blocks per SM when the fused kernel holds a 2048-wide row per warp (three would spill),
+// three otherwise.
 template <int NCHUNK, int WPR, bool QUANT, bool PURE>
-__global__ void __launch_bounds__(kNormWarps * 32, 3)
+__global__ void __launch_bounds__(kNormWarps * 32, (QUANT && NCHUNK >= 8) ? 2 : 3)
 rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma,
                    float eps, uint8_t* __restrict__ q, float* __restrict__ scales,
                    __nv_bfloat16* __restrict__ y, float* __restrict__ rnorm_out, int64_t rows,
@@ -92,6 +94,8 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     if (row_ok && rnorm_out != nullptr && lane == 0 && (warp % WPR) == 0) rnorm_out[row] = rn;
     const float rn_b = __bfloat162float(__float2bfloat16_rn(rn));  // kernels.py:32 `.astype(x.dtype)`
 
+    // pass 2a: normalise, round to bf16 (the value the reference's norm returns), per-tile amax
+    float amax[NCHUNK];
 #pragma unroll
     for (int c = 0; c < NCHUNK; ++c) {
       const int col = col_base + c * 256;
@@ -115,17 +119,31 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
           yp[j] = pack_bf16x2(__fmul_rn(bf16lo(t), gf[2 * j]), __fmul_rn(bf16hi(t), gf[2 * j + 1]));
         }
       }
-      const bool ok = row_ok && col < cols;
-      if (y != nullptr && ok) *reinterpret_cast<uint4*>(y + row * cols + col) = yo;
+      if (y != nullptr && row_ok && col < cols) *reinterpret_cast<uint4*>(y + row * cols + col) = yo;
+      w[c] = yo;  // the row registers now hold the normalised bf16 values
       if constexpr (QUANT) {
         float m = amax8(yo);
 #pragma unroll
         for (int o = 8; o > 0; o >>= 1) m = max_nan(m, __shfl_xor_sync(0xffffffffu, m, o));
-        const float s = scale_from_amax(m);
-        if (ok) {
-          *reinterpret_cast<uint2*>(q + row * cols + col) = quantize8(yo, s);
-          if ((lane & 15) == 0) scales[row * (cols / kTile) + col / kTile] = s;
-        }
+        amax[c] = m;
+      }
+    }
+    if constexpr (QUANT) {
+      // pass 2b: the NCHUNK tile scales of this half-warp, computed lane-parallel
+      float s[NCHUNK], r[NCHUNK], s_mine;
+      bool fin;
+      tile_scales<NCHUNK>(amax, s, r, s_mine, fin);
+      {
+        const int j = lane & 15;                       // lane j of a half computed chunk j % NCHUNK
+        const int col = col_base - (lane & 15) * 8 + j * 256;   // = first column of that chunk's tile for this half
+        if (j < NCHUNK && row_ok && col < cols) scales[row * (cols / kTile) + col / kTile] = s_mine;
+      }
+      // pass 2c: divide and store
+#pragma unroll
+      for (int c = 0; c < NCHUNK; ++c) {
+        const int col = col_base + c * 256;
+        if (row_ok && col < cols)
+          *reinterpret_cast<uint2*>(q + row * cols + col) = fin ? quantize8_sr(w[c], s[c], r[c]) : quantize8(w[c], s[c]);
       }
     }
   }
