@@ -63,6 +63,15 @@ int tg_quantize_rowwise(const void* x, void* q, float* scales,
 int tg_quantize_colwise(const void* x, void* q, float* scales,
                         int64_t rows, int64_t cols, void* stream);
 
+/* Both of the above in one pass over x, for a tensor that two GEMMs contract along different
+ * axes (the upstream gradient g of fp8.py:85-98: along N for dgrad, along the tokens for
+ * wgrad): x is read from HBM once.  Outputs are bit-identical to tg_quantize_rowwise and
+ * tg_quantize_colwise.
+ *   x [rows, cols] bf16, cols % 128 == 0
+ *   q_row [rows, cols] e4m3, s_row [rows, cols/128];  q_col [rows, cols] e4m3, s_col [ceil(rows/128), cols] */
+int tg_quantize_rowcol(const void* x, void* q_row, float* s_row, void* q_col, float* s_col,
+                       int64_t rows, int64_t cols, void* stream);
+
 /* Tiles of 128 x 128, one scale per tile: the weight granularity the benchmark
  * configurations name (the reference itself uses tg_quantize_colwise's).  Same scale
  * rule, fp8.py:43-46.

@@ -136,3 +136,15 @@ def test_division_shortcut_is_exact_over_the_whole_domain():
     pairs, bare, shipped, two = ops.selftest_quantise_division()
     assert pairs == 1065402240        # sum over finite bf16 amax of #{x : |x| <= amax}
     assert shipped == 0 and two == 0, (pairs, bare, shipped, two)
+
+
+@pytest.mark.parametrize("shape", [(128, 128), (200, 256), (1000, 2048), (4096, 768)])
+def test_rowcol_equals_the_two_separate_quantisers(shape):
+    from train_gpt_b200 import ops
+    rng = np.random.default_rng(hash(shape) % 2**32)
+    x = to_torch_bf16(_awkward(rng, shape))
+    q_row, s_row, q_col, s_col = ops.quantize_rowcol(x)
+    q1, s1 = ops.quantize_rowwise(x)
+    q2, s2 = ops.quantize_colwise(x)
+    assert torch.equal(q_row.view(torch.uint8), q1.view(torch.uint8)) and torch.equal(s_row.view(torch.int32), s1.view(torch.int32))
+    assert torch.equal(q_col.view(torch.uint8), q2.view(torch.uint8)) and torch.equal(s_col.view(torch.int32), s2.view(torch.int32))

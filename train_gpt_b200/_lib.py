@@ -38,6 +38,7 @@ SYMBOLS = {
     "tg_last_cuda_error": (C.c_char_p, []),
     "tg_quantize_rowwise": (_i, [_p, _p, _p, _i64, _i64, _p]),
     "tg_quantize_colwise": (_i, [_p, _p, _p, _i64, _i64, _p]),
+    "tg_quantize_rowcol": (_i, [_p, _p, _p, _p, _p, _i64, _i64, _p]),
     "tg_quantize_block128": (_i, [_p, _p, _p, _i64, _i64, _p]),
     "tg_selftest_quantise_division": (_i, [_p, _p]),
     "tg_rmsnorm_fwd": (_i, [_p, _p, _f, _p, _p, _i64, _i64, _i, _p]),

@@ -55,9 +55,14 @@ constexpr int kColThreads = 256;
 constexpr int kColHalfWarps = kColThreads / 16;           // 16
 constexpr int kColRowsPerThread = kTile / kColHalfWarps;  // 8
 
+// WITH_ROWS: the same pass also emits the 1 x 128 (row-wise) quantisation of the panel -- a
+// half-warp spans exactly one row tile -- so a tensor that needs both forms (an upstream
+// gradient: row-wise for dgrad, column-wise for wgrad) is read from HBM once, not twice.
+template <bool WITH_ROWS>
 __global__ void __launch_bounds__(kColThreads, 2)
 quantize_colwise_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
-                        float* __restrict__ scales, int64_t rows, int64_t cols) {
+                        float* __restrict__ scales, uint8_t* __restrict__ q_row,
+                        float* __restrict__ s_row, int64_t rows, int64_t cols) {
   __shared__ float s_max[kColThreads / 32][kColPanelCols];
   __shared__ __align__(16) float s_scale[kColPanelCols], s_rcp[kColPanelCols];
   const int cx = threadIdx.x & 15, hw = threadIdx.x >> 4;
@@ -71,6 +76,28 @@ quantize_colwise_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict
   for (int r = 0; r < kColRowsPerThread; ++r) {
     const int64_t row = row0 + r * kColHalfWarps;
     w[r] = (col_ok && row < rows) ? ld_nc_v4(x + row * cols + col0) : make_uint4(0, 0, 0, 0);
+  }
+  if constexpr (WITH_ROWS) {   // cols % 128 == 0 here: every lane holds real columns
+    float mr[kColRowsPerThread];
+#pragma unroll
+    for (int r = 0; r < kColRowsPerThread; ++r) {
+      mr[r] = amax8(w[r]);
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) mr[r] = max_nan(mr[r], __shfl_xor_sync(0xffffffffu, mr[r], o));
+    }
+    float sr[kColRowsPerThread], rr[kColRowsPerThread], s_mine;
+    bool fin;
+    tile_scales<kColRowsPerThread>(mr, sr, rr, s_mine, fin);
+    {
+      const int64_t row = row0 + int64_t(cx & 7) * kColHalfWarps;   // lane j of the half computed row r = j % 8
+      if (cx < kColRowsPerThread && row < rows) s_row[row * (cols / kTile) + blockIdx.x] = s_mine;
+    }
+#pragma unroll
+    for (int r = 0; r < kColRowsPerThread; ++r) {
+      const int64_t row = row0 + r * kColHalfWarps;
+      if (row < rows)
+        *reinterpret_cast<uint2*>(q_row + row * cols + col0) = fin ? quantize8_sr(w[r], sr[r], rr[r]) : quantize8(w[r], sr[r]);
+    }
   }
   uint32_t m2[4] = {0u, 0u, 0u, 0u};  // packed |.|-maxima of column pairs (0,1) (2,3) (4,5) (6,7)
 #pragma unroll
@@ -206,9 +233,27 @@ extern "C" int tg_quantize_colwise(const void* x, void* q, float* scales, int64_
   if (int rc = check_arch()) return rc;
   const int64_t gx = (cols + kColPanelCols - 1) / kColPanelCols, gy = (rows + kTile - 1) / kTile;
   if (gy > 65535) return TG_ERR_TOO_LARGE;
-  quantize_colwise_kernel<<<dim3(unsigned(gx), unsigned(gy)), kColThreads, 0,
-                            static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(q), scales, rows, cols);
+  quantize_colwise_kernel<false><<<dim3(unsigned(gx), unsigned(gy)), kColThreads, 0,
+                                   static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(q), scales, nullptr, nullptr, rows, cols);
+  TG_CUDA_CHECK(cudaGetLastError());
+  return TG_OK;
+}
+
+extern "C" int tg_quantize_rowcol(const void* x, void* q_row, float* s_row, void* q_col, float* s_col,
+                                  int64_t rows, int64_t cols, void* stream) {
+  if (rows < 0 || cols < 0 || cols % kTile != 0) return TG_ERR_SHAPE;
+  if (rows == 0 || cols == 0) return TG_OK;
+  if (!aligned16(x) || !aligned16(q_row) || !aligned16(q_col) || !aligned16(s_col) ||
+      (reinterpret_cast<uintptr_t>(s_row) & 3u))
+    return TG_ERR_ALIGN;
+  if (int rc = check_arch()) return rc;
+  const int64_t gx = cols / kColPanelCols, gy = (rows + kTile - 1) / kTile;
+  if (gy > 65535) return TG_ERR_TOO_LARGE;
+  quantize_colwise_kernel<true><<<dim3(unsigned(gx), unsigned(gy)), kColThreads, 0,
+                                  static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(q_col), s_col, static_cast<uint8_t*>(q_row), s_row, rows,
+      cols);
   TG_CUDA_CHECK(cudaGetLastError());
   return TG_OK;
 }

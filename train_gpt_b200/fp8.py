@@ -36,6 +36,30 @@ def _quantize_to_fp8(x_f32: torch.Tensor, block_k: int = DEFAULT_BLOCK_K):
     return ops.quantize_rowwise(x)
 
 
+class QuantizedActivation:
+    """One activation in the forms the three GEMMs of a linear layer contract: the row-wise
+    (1x128) pair for the forward GEMM and, made on first use and then kept, the column-wise
+    (128 tokens x 1) pair for wgrad.  Passing the same object as `a_quantized=` to several
+    `block_scaled_matmul` calls (q, k, v share one normed activation, model.py:63-65) makes
+    each form once instead of once per call, as the reference does (bench_fp8_norm.py:91-93)."""
+
+    def __init__(self, a: torch.Tensor, q=None, scales=None, q_col=None, scales_col=None):
+        K = a.shape[-1]
+        self.a2d = a.reshape(-1, K)
+        self._row = None if q is None else (q.reshape(-1, K), scales.reshape(-1, K // DEFAULT_BLOCK_K))
+        self._col = None if q_col is None else (q_col, scales_col)
+
+    def rowwise(self):
+        if self._row is None:
+            self._row = ops.quantize_rowwise(self.a2d.to(torch.bfloat16))
+        return self._row
+
+    def colwise(self):
+        if self._col is None:
+            self._col = ops.quantize_colwise(self.a2d.to(torch.bfloat16))
+        return self._col
+
+
 def quantize_weight(b: torch.Tensor, weight_tile=(128, 1)):
     """Quantise b (K, N) for the forward GEMM without transposing it."""
     if tuple(weight_tile) == (128, 1):
@@ -63,6 +87,8 @@ def _fp8_forward(a, b, block_k=DEFAULT_BLOCK_K, weight_tile=(128, 1), a_quantize
     leading = a.shape[:-1]
     if a_quantized is None:
         a_q, a_s = ops.quantize_rowwise(a.reshape(-1, K).to(torch.bfloat16))
+    elif isinstance(a_quantized, QuantizedActivation):
+        a_q, a_s = a_quantized.rowwise()
     else:
         a_q, a_s = a_quantized[0].reshape(-1, K), a_quantized[1].reshape(-1, K // block_k)
     b = b.to(torch.bfloat16)
@@ -78,7 +104,7 @@ def _fp8_forward(a, b, block_k=DEFAULT_BLOCK_K, weight_tile=(128, 1), a_quantize
     return y.reshape(*leading, N)
 
 
-def _fp8_backward(block_k, residuals, g, weight_tile=(128, 1), mode="bf16_ste"):
+def _fp8_backward(block_k, residuals, g, weight_tile=(128, 1), mode="bf16_ste", a_quantized=None):
     """fp8.py:85-98 (mode "bf16_ste"), or the same two GEMMs in block-scaled e4m3."""
     a, b = residuals
     K = a.shape[-1]
@@ -93,14 +119,16 @@ def _fp8_backward(block_k, residuals, g, weight_tile=(128, 1), mode="bf16_ste"):
     elif mode == "fp8":
         if N % block_k != 0:
             raise ValueError(f"N={N} not divisible by block_k={block_k} (needed by the FP8 dgrad)")
-        g_q, g_s = ops.quantize_rowwise(g_2d)
+        g_q, g_s, g_qc, g_sc = ops.quantize_rowcol(g_2d)            # one read of g for both contractions
         if tuple(weight_tile) == (128, 1):
             w_q, w_s = ops.quantize_rowwise(b_bf)                   # tiles along N, the dgrad contraction
         else:
             w_q, w_s = ops.quantize_block128(b_bf)
         da = ops.gemm_dgrad(g_q, g_s, w_q, w_s, weight_tile)
-        x_qc, x_sc = ops.quantize_colwise(a_2d)
-        g_qc, g_sc = ops.quantize_colwise(g_2d)
+        if isinstance(a_quantized, QuantizedActivation):
+            x_qc, x_sc = a_quantized.colwise()                        # shared by every GEMM fed from this activation
+        else:
+            x_qc, x_sc = ops.quantize_colwise(a_2d)
         db = ops.gemm_wgrad(x_qc, x_sc, g_qc, g_sc)
     else:
         raise ValueError(f"unknown backward mode {mode!r}; use 'bf16_ste' or 'fp8'")
@@ -114,12 +142,13 @@ class _BlockScaledMatmul(torch.autograd.Function):
     def forward(ctx, a, b, block_k, weight_tile, backward, a_quantized):
         ctx.save_for_backward(a, b)                                 # fp8.py:81-82: unquantised residuals
         ctx.cfg = (block_k, tuple(weight_tile), backward)
+        ctx.aq = a_quantized if isinstance(a_quantized, QuantizedActivation) else None
         return _fp8_forward(a, b, block_k, weight_tile, a_quantized)
 
     @staticmethod
     def backward(ctx, g):
         block_k, weight_tile, mode = ctx.cfg
-        da, db = _fp8_backward(block_k, ctx.saved_tensors, g, weight_tile, mode)
+        da, db = _fp8_backward(block_k, ctx.saved_tensors, g, weight_tile, mode, ctx.aq)
         return da, db, None, None, None, None
 
 

@@ -66,6 +66,24 @@ def quantize_colwise(x: torch.Tensor):
     return q, s
 
 
+def quantize_rowcol(x: torch.Tensor):
+    """Row-wise (1x128) and column-wise (128x1) quantisation of a 2-D tensor in one pass.
+    Returns (q_row, s_row, q_col, s_col), bit-identical to the two separate kernels."""
+    x = _need(x, torch.bfloat16, "x")
+    if x.dim() != 2:
+        raise ValueError("quantize_rowcol takes a 2-D tensor")
+    R, Cc = x.shape
+    if Cc % TILE:
+        raise ValueError(f"K={Cc} not divisible by block_k={TILE}")
+    q_row = torch.empty((R, Cc), dtype=F8, device=x.device)
+    s_row = torch.empty((R, Cc // TILE), dtype=torch.float32, device=x.device)
+    q_col = torch.empty((R, Cc), dtype=F8, device=x.device)
+    s_col = torch.empty((_cdiv(R, TILE), Cc), dtype=torch.float32, device=x.device)
+    _lib.check(_lib.load().tg_quantize_rowcol(_ptr(x), _ptr(q_row), _ptr(s_row), _ptr(q_col), _ptr(s_col), R, Cc,
+                                              _stream()), "tg_quantize_rowcol")
+    return q_row, s_row, q_col, s_col
+
+
 def quantize_block128(x: torch.Tensor):
     """128x128 tiles.  x (R, C) bf16 -> q (R, C) e4m3, scales (ceil(R/128), C/128) f32."""
     x = _need(x, torch.bfloat16, "x")

@@ -128,7 +128,7 @@ class GPT:
         c = self.cfg
         if c.norm == "fused" and c.mm != "bf16":
             y, q, s = _NormQuant.apply(x, w, c.rms_eps)
-            return y, (q, s)
+            return y, fp8.QuantizedActivation(y, q, s)          # one object for every GEMM this activation feeds
         if c.norm == "pure":
             return kernels._rms_norm_pure(x, w, c.rms_eps), None
         if c.norm == "torch_reference":
