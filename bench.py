@@ -331,16 +331,44 @@ def run_e2e(args, torch, fp8, dev, tile, world, dist):
     h2d = sum(h[k].numel() * 2 for h in host for k in ("x", "w", "g"))
     d2h = sum(h[k].numel() * 2 for h in host for k in ("y", "dx", "dw"))
 
-    def one():
-        for h in host:
-            x = h["x"].to(dev, non_blocking=True).requires_grad_(True)
-            w = h["w"].to(dev, non_blocking=True).requires_grad_(True)
+    # Three streams: host->device copies of the NEXT layer's inputs and device->host copies of the
+    # PREVIOUS layer's results run beside the current layer's kernels (PCIe is full duplex), all
+    # inside the timed region.
+    cur = torch.cuda.current_stream()
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+
+    def stage_in(h):
+        with torch.cuda.stream(s_in):
+            x = h["x"].to(dev, non_blocking=True)
+            w = h["w"].to(dev, non_blocking=True)
             g = h["g"].to(dev, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(s_in)
+        return x, w, g, ev
+
+    def one():
+        nxt = stage_in(host[0])
+        for i, h in enumerate(host):
+            x, w, g, ev = nxt
+            if i + 1 < len(host):
+                nxt = stage_in(host[i + 1])
+            cur.wait_event(ev)
+            for t in (x, w, g):
+                t.record_stream(cur)                      # allocated on the copy stream, consumed here
+            x.requires_grad_(True)
+            w.requires_grad_(True)
             y = fp8.block_scaled_matmul(x, w, weight_tile=tile, backward="fp8")
             y.backward(g)
-            h["y"].copy_(y.detach(), non_blocking=True)
-            h["dx"].copy_(x.grad, non_blocking=True)
-            h["dw"].copy_(w.grad, non_blocking=True)
+            done = torch.cuda.Event()
+            done.record(cur)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(done)
+                h["y"].copy_(y.detach(), non_blocking=True)
+                h["dx"].copy_(x.grad, non_blocking=True)
+                h["dw"].copy_(w.grad, non_blocking=True)
+            for t in (y, x.grad, w.grad):
+                t.record_stream(s_out)
+        cur.wait_stream(s_out)                            # the step ends when its last result is on the host
 
     for _ in range(2):
         one()
