@@ -188,7 +188,7 @@ def backward_bf16_ste(a, b, g):
     return da, db
 
 
-def backward_fp8(a, b, g, block: int = DEFAULT_BLOCK_K, weight_tile=(128, 1)):
+def backward_fp8(a, b, g, block: int = DEFAULT_BLOCK_K, weight_tile=(128, 1), wgrad_grad_tile=(128, 1)):
     """Like-for-like oracle of the FP8 backward this build adds (the reference's own
     backward is `backward_bf16_ste`).  Same quantiser (fp8.py:39-47) applied along
     each GEMM's contraction:
@@ -196,7 +196,8 @@ def backward_fp8(a, b, g, block: int = DEFAULT_BLOCK_K, weight_tile=(128, 1)):
       dgrad  da[m,k] = sum_n g[m,n] b[k,n]   g tiles 1x128 along N; b tiles 1x128
                                              along N (weight_tile (128,1)) or the
                                              shared 128x128 tiles.
-      wgrad  db[k,n] = sum_m a[m,k] g[m,n]   a and g tiles 128x1 along the tokens.
+      wgrad  db[k,n] = sum_m a[m,k] g[m,n]   a and g tiles 128x1 along the tokens
+                                             (wgrad_grad_tile (128,128): g in 128x128 blocks).
     """
     a = np.asarray(a)
     b = np.asarray(b)
@@ -219,7 +220,11 @@ def backward_fp8(a, b, g, block: int = DEFAULT_BLOCK_K, weight_tile=(128, 1)):
     # wgrad: contraction over the tokens (ragged last block allowed)
     M = a2.shape[0]
     a_q, a_s = quantize_colwise(a2, block)                         # (M,K), (Mb,K)
-    gq2, gs2 = quantize_colwise(g2, block)                         # (M,N), (Mb,N)
+    if tuple(wgrad_grad_tile) == (128, 1):
+        gq2, gs2 = quantize_colwise(g2, block)                     # (M,N), (Mb,N)
+    else:
+        gq2, gs_b = quantize_block2d(g2, block)                    # (M,N), (Mb,N/128)
+        gs2 = np.repeat(gs_b, block, axis=1)
     pad = (-M) % block
     aq = np.pad(a_q.astype(np.float32), ((0, pad), (0, 0))).astype(F8)
     gq = np.pad(gq2.astype(np.float32), ((0, pad), (0, 0))).astype(F8)

@@ -156,3 +156,17 @@ def test_linearity_at_full_k():
     assert torch.equal(y2.float(), y1.float() * 2)
     ref = a.float() @ b.float()
     assert float((y1.float() - ref).norm() / ref.norm()) < 0.05
+
+
+@pytest.mark.parametrize("M,K,N", [(200, 256, 384), (1536, 512, 1024)])
+def test_fp8_backward_with_block_quantised_gradient(M, K, N):
+    """backward="fp8_blockgrad": wgrad with the upstream gradient in 128x128 blocks, like-for-like."""
+    from train_gpt_b200 import fp8
+    rng = np.random.default_rng(M + N)
+    a = normal_bf16(rng, (M, K))
+    b = normal_bf16(rng, (K, N), std=0.02)
+    g = normal_bf16(rng, (M, N))
+    da, db = fp8._fp8_backward(128, (to_torch_bf16(a), to_torch_bf16(b)), to_torch_bf16(g), (128, 128), "fp8_blockgrad")
+    da_ref, db_ref = fo.backward_fp8(a, b, g, weight_tile=(128, 128), wgrad_grad_tile=(128, 128))
+    _close(from_torch_bf16(da), da_ref)
+    _close(from_torch_bf16(db), db_ref)

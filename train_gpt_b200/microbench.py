@@ -119,6 +119,10 @@ def _gemm_case(M, N, K, mode, tile, warmup, iters, student_t=False):
         g_q, g_s = ops.quantize_rowwise(gr)
         w_q, w_s = ops.quantize_rowwise(w) if tile == (128, 1) else ops.quantize_block128(w)
         fn = lambda i: ops.gemm_dgrad(g_q, g_s, w_q, w_s, tile, status=st)
+    elif mode == "wgrad_blockgrad":
+        x_q, x_s = ops.quantize_colwise(x)
+        g_q, g_s = ops.quantize_block128(gr)
+        fn = lambda i: ops.gemm_wgrad(x_q, x_s, g_q, g_s, status=st, grad_tile=(128, 128))
     else:
         x_q, x_s = ops.quantize_colwise(x)
         g_q, g_s = ops.quantize_colwise(gr)
@@ -138,7 +142,7 @@ def main():
     ap.add_argument("--m", type=int, default=32768)
     ap.add_argument("--n", type=int, default=6144)
     ap.add_argument("--k", type=int, default=2048)
-    ap.add_argument("--mode", default="fwd", choices=["fwd", "dgrad", "wgrad", "all"])
+    ap.add_argument("--mode", default="fwd", choices=["fwd", "dgrad", "wgrad", "wgrad_blockgrad", "all"])
     ap.add_argument("--tile", default="128x128", choices=["128x128", "128x1"])
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--iters", type=int, default=30)
