@@ -9,6 +9,8 @@
 // each lane 8 consecutive columns (one 128-bit load) per chunk, so a half-warp owns
 // exactly one 128-column quantisation tile.  The whole row stays in registers between the
 // sum-of-squares pass and the normalise/quantise pass: x is read from HBM once.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace tg {
@@ -19,11 +21,9 @@ constexpr int kNormWarps = 8;  // warps per thread block
 // Sum of squares of the 8 bf16 values in w, as a balanced tree (keeps the rounding error of
 // a row's variance at a few 2^-24 regardless of outliers).
 __device__ __forceinline__ float sumsq8(const uint4& w) {
-  const float a0 = bf16lo(w.x), a1 = bf16hi(w.x), a2 = bf16lo(w.y), a3 = bf16hi(w.y);
-  const float a4 = bf16lo(w.z), a5 = bf16hi(w.z), a6 = bf16lo(w.w), a7 = bf16hi(w.w);
-  const float t0 = fmaf(a1, a1, a0 * a0), t1 = fmaf(a3, a3, a2 * a2);
-  const float t2 = fmaf(a5, a5, a4 * a4), t3 = fmaf(a7, a7, a6 * a6);
-  return (t0 + t1) + (t2 + t3);
+  const float2 v0 = bf16x2_unpack(w.x), v1 = bf16x2_unpack(w.y), v2 = bf16x2_unpack(w.z), v3 = bf16x2_unpack(w.w);
+  const float2 t = __fadd2_rn(__ffma2_rn(v2, v2, __fmul2_rn(v0, v0)), __ffma2_rn(v3, v3, __fmul2_rn(v1, v1)));
+  return t.x + t.y;
 }
 
 template <int N>
@@ -95,7 +95,8 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     const float rn_b = __bfloat162float(__float2bfloat16_rn(rn));  // kernels.py:32 `.astype(x.dtype)`
 
     // pass 2a: normalise, round to bf16 (the value the reference's norm returns), per-tile amax
-    float amax[NCHUNK];
+    const float2 rn2 = PURE ? make_float2(rn_b, rn_b) : make_float2(rn, rn);
+    uint32_t amax_bits[NCHUNK];
 #pragma unroll
     for (int c = 0; c < NCHUNK; ++c) {
       const int col = col_base + c * 256;
@@ -105,34 +106,26 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
         g0 = s_gamma[col >> 2];
         g1 = s_gamma[(col >> 2) + 1];
       }
-      const float gf[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+      const float2 gf[4] = {make_float2(g0.x, g0.y), make_float2(g0.z, g0.w), make_float2(g1.x, g1.y), make_float2(g1.z, g1.w)};
       uint4 yo;
       uint32_t* yp = &yo.x;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        if (!PURE) {
-          const float lo = __fmul_rn(__fmul_rn(bf16lo(xi[j]), rn), gf[2 * j]);
-          const float hi = __fmul_rn(__fmul_rn(bf16hi(xi[j]), rn), gf[2 * j + 1]);
-          yp[j] = pack_bf16x2(lo, hi);
-        } else {
-          const uint32_t t = pack_bf16x2(__fmul_rn(bf16lo(xi[j]), rn_b), __fmul_rn(bf16hi(xi[j]), rn_b));
-          yp[j] = pack_bf16x2(__fmul_rn(bf16lo(t), gf[2 * j]), __fmul_rn(bf16hi(t), gf[2 * j + 1]));
-        }
+        float2 t = __fmul2_rn(bf16x2_unpack(xi[j]), rn2);
+        if (PURE) t = bf16x2_unpack(pack_bf16x2(t.x, t.y));   // kernels.py:32 rounds before the gamma multiply
+        t = __fmul2_rn(t, gf[j]);
+        yp[j] = pack_bf16x2(t.x, t.y);
       }
       if (y != nullptr && row_ok && col < cols) *reinterpret_cast<uint4*>(y + row * cols + col) = yo;
       w[c] = yo;  // the row registers now hold the normalised bf16 values
-      if constexpr (QUANT) {
-        float m = amax8(yo);
-#pragma unroll
-        for (int o = 8; o > 0; o >>= 1) m = max_nan(m, __shfl_xor_sync(0xffffffffu, m, o));
-        amax[c] = m;
-      }
+      if constexpr (QUANT) amax_bits[c] = absmax8(yo);
     }
     if constexpr (QUANT) {
-      // pass 2b: the NCHUNK tile scales of this half-warp, computed lane-parallel
+      // pass 2b: one exchange brings lane j of each half the amax of chunk j % NCHUNK; that lane
+      // computes the tile's scale and reciprocal, and shuffles hand them to the lanes that need them
       float s[NCHUNK], r[NCHUNK], s_mine;
       bool fin;
-      tile_scales<NCHUNK>(amax, s, r, s_mine, fin);
+      tile_scales_own<NCHUNK>(exchange_tile_amax<NCHUNK>(amax_bits), s, r, s_mine, fin);
       {
         const int j = lane & 15;                       // lane j of a half computed chunk j % NCHUNK
         const int col = col_base - (lane & 15) * 8 + j * 256;   // = first column of that chunk's tile for this half
@@ -147,6 +140,129 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
       }
     }
   }
+}
+
+// ---------------------------------------------------------------------------------------
+// Fused norm + quantise for rows that one warp can hold (cols <= 2048), staged through shared
+// memory.  The register-resident kernel above needs ~120 registers at 2048 columns, so only
+// 16 warps fit on an SM and every warp idles while its next row's loads are in flight.  Here
+// each warp owns two row-sized slots of shared memory: cp.async fetches row i+1 into one
+// slot while the warp makes its three passes (sum of squares; normalise + amax, writing the
+// bf16 result back in place; divide + store) over row i in the other.  A lane only ever
+// touches the 16-byte pieces it fetched itself, so cp.async.wait_group is the only
+// synchronisation; nothing spins.  Same arithmetic, same results as rmsnorm_fwd_kernel.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, const uint4& v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+constexpr int kStagedBlocksPerSm = 3;
+
+template <int NCHUNK, bool PURE, bool FULL>
+__global__ void __launch_bounds__(kNormWarps * 32, kStagedBlocksPerSm)
+rmsnorm_quant_staged_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma,
+                            float eps, uint8_t* __restrict__ q, float* __restrict__ scales,
+                            __nv_bfloat16* __restrict__ y, float* __restrict__ rnorm_out, int64_t rows,
+                            int cols) {
+  constexpr int kSlotBytes = NCHUNK * 512;
+  extern __shared__ float4 s_gamma[];   // [cols] floats, then [warps][2][NCHUNK * 256] bf16
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int col_base = lane * 8;
+  const uint32_t slot0 = uint32_t(__cvta_generic_to_shared(s_gamma)) + uint32_t(cols) * 4u +
+                         uint32_t(warp) * 2u * kSlotBytes + uint32_t(lane) * 16u;
+
+  for (int i = threadIdx.x; i < cols / 8; i += blockDim.x) {
+    const uint4 gq = reinterpret_cast<const uint4*>(gamma)[i];
+    s_gamma[2 * i] = make_float4(bf16lo(gq.x), bf16hi(gq.x), bf16lo(gq.y), bf16hi(gq.y));
+    s_gamma[2 * i + 1] = make_float4(bf16lo(gq.z), bf16hi(gq.z), bf16lo(gq.w), bf16hi(gq.w));
+  }
+  __syncthreads();
+
+  const int64_t stride = int64_t(gridDim.x) * kNormWarps;
+  int64_t row = int64_t(blockIdx.x) * kNormWarps + warp;
+  auto prefetch = [&](int64_t r, int slot) {
+    if (r < rows) {
+#pragma unroll
+      for (int c = 0; c < NCHUNK; ++c) {
+        const int col = col_base + c * 256;
+        if (FULL || col < cols) cp_async16(slot0 + slot * kSlotBytes + c * 512, x + r * cols + col);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");   // an empty group keeps the wait count uniform
+  };
+  prefetch(row, 0);
+  for (int it = 0; row < rows; row += stride, ++it) {
+    const uint32_t base = slot0 + (it & 1) * kSlotBytes;
+    prefetch(row + stride, (it & 1) ^ 1);
+    asm volatile("cp.async.wait_group 1;" ::: "memory");
+
+    // pass 1: sum of squares
+    float part[NCHUNK];
+#pragma unroll
+    for (int c = 0; c < NCHUNK; ++c) part[c] = (FULL || col_base + c * 256 < cols) ? sumsq8(lds128(base + c * 512)) : 0.f;
+    float ss = tree_sum(part);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float var = __fdiv_rn(ss, float(cols));
+    const float rn = __frsqrt_rn(var + eps);
+    if (rnorm_out != nullptr && lane == 0) rnorm_out[row] = rn;
+    const float rn_b = __bfloat162float(__float2bfloat16_rn(rn));  // kernels.py:32 `.astype(x.dtype)`
+
+    // pass 2: normalise, round to bf16 (the value the reference's norm returns), per-tile amax
+    const float2 rn2 = PURE ? make_float2(rn_b, rn_b) : make_float2(rn, rn);
+    uint32_t amax_bits[NCHUNK];
+#pragma unroll
+    for (int c = 0; c < NCHUNK; ++c) {
+      const int col = col_base + c * 256;
+      amax_bits[c] = 0u;
+      if (FULL || col < cols) {
+        const uint4 xv = lds128(base + c * 512);
+        const uint32_t xi[4] = {xv.x, xv.y, xv.z, xv.w};
+        const float4 g0 = s_gamma[col >> 2], g1 = s_gamma[(col >> 2) + 1];
+        const float2 gf[4] = {make_float2(g0.x, g0.y), make_float2(g0.z, g0.w), make_float2(g1.x, g1.y), make_float2(g1.z, g1.w)};
+        uint4 yo;
+        uint32_t* yp = &yo.x;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 t = __fmul2_rn(bf16x2_unpack(xi[j]), rn2);
+          if (PURE) t = bf16x2_unpack(pack_bf16x2(t.x, t.y));   // kernels.py:32 rounds before the gamma multiply
+          t = __fmul2_rn(t, gf[j]);
+          yp[j] = pack_bf16x2(t.x, t.y);
+        }
+        sts128(base + c * 512, yo);
+        if (y != nullptr) *reinterpret_cast<uint4*>(y + row * cols + col) = yo;
+        amax_bits[c] = absmax8_h(yo);
+      }
+    }
+    // one exchange brings lane j of each half the amax of chunk j % NCHUNK; that lane computes
+    // the tile's scale and reciprocal, and shuffles hand them to the lanes that need them
+    float s[NCHUNK], r[NCHUNK], s_mine;
+    bool fin;
+    tile_scales_own<NCHUNK>(exchange_tile_amax<NCHUNK>(amax_bits), s, r, s_mine, fin);
+    {
+      const int j = lane & 15;
+      const int col = j * 256 + (lane & 16) * 8;     // first column of the tile this lane computed
+      if (j < NCHUNK && (FULL || col < cols)) scales[row * (cols / kTile) + col / kTile] = s_mine;
+    }
+    // pass 3: divide and store
+#pragma unroll
+    for (int c = 0; c < NCHUNK; ++c) {
+      const int col = col_base + c * 256;
+      if (FULL || col < cols) {
+        const uint4 yo = lds128(base + c * 512);
+        *reinterpret_cast<uint2*>(q + row * cols + col) = fin ? quantize8_sr(yo, s[c], r[c]) : quantize8(yo, s[c]);
+      }
+    }
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
 }
 
 // ---------------------------------------------------------------------------------------
@@ -307,6 +423,34 @@ static int launch_fwd(const void* x, const void* gamma, float eps, void* q, floa
                       float* rnorm, int64_t rows, int64_t cols, int mode, cudaStream_t st) {
   NormGeom g;
   if (!norm_geom(cols, &g)) return cols > 8192 ? TG_ERR_TOO_LARGE : TG_ERR_SHAPE;
+  if (QUANT && g.wpr == 1 && getenv("TG_NORM_UNSTAGED") == nullptr) {
+    const size_t smem = size_t(cols) * 4 + size_t(kNormWarps) * 2 * g.nchunk * 512;
+    const int blocks = norm_blocks(rows, 1, kStagedBlocksPerSm);
+    int dev = 0;
+    TG_CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return TG_ERR_SHAPE;
+#define TG_STAGED_CASE(NC)                                                                       \
+  if (g.nchunk == NC) {                                                                          \
+    const bool full = cols == NC * 256;   /* no ragged chunk: the column guards compile away */ \
+    auto kern = mode == TG_NORM_PURE                                                             \
+                    ? (full ? rmsnorm_quant_staged_kernel<NC, true, true> : rmsnorm_quant_staged_kernel<NC, true, false>)   \
+                    : (full ? rmsnorm_quant_staged_kernel<NC, false, true> : rmsnorm_quant_staged_kernel<NC, false, false>); \
+    static bool attr_set[4][64] = {};                                                            \
+    if (!attr_set[(mode == TG_NORM_PURE) * 2 + full][dev]) {                                     \
+      TG_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,      \
+                                         int(2048 * 4 + kNormWarps * 2 * NC * 512)));            \
+      attr_set[(mode == TG_NORM_PURE) * 2 + full][dev] = true;                                   \
+    }                                                                                            \
+    kern<<<blocks, kNormWarps * 32, smem, st>>>(                                                 \
+        static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(gamma), eps,     \
+        static_cast<uint8_t*>(q), scales, static_cast<__nv_bfloat16*>(y), rnorm, rows,           \
+        int(cols));                                                                              \
+  } else
+    TG_STAGED_CASE(1) TG_STAGED_CASE(2) TG_STAGED_CASE(4) TG_STAGED_CASE(8) { return TG_ERR_SHAPE; }
+#undef TG_STAGED_CASE
+    TG_CUDA_CHECK(cudaGetLastError());
+    return TG_OK;
+  }
   const int blocks = norm_blocks(rows, g.wpr, 16);
 #define TG_FWD_CASE(NC, W)                                                                      \
   if (g.nchunk == NC && g.wpr == W) {                                                           \

@@ -20,6 +20,8 @@ selftest_division_kernel(unsigned long long* __restrict__ counts) {
     const uint32_t ref = cvt_e4m3x2(__fdiv_rn(x, s), 0.f) & 0xffu;
     bad1 += (cvt_e4m3x2(d.div<1>(x), 0.f) & 0xffu) != ref;
     bad2 += (cvt_e4m3x2(d.div<2>(x), 0.f) & 0xffu) != ref;
+    // the packed two-at-a-time form the kernels use: both halves must give the same byte
+    bad2 += quantize2_sr(xb | (xb << 16), make_float2(s, s), make_float2(-d.r, -d.r)) != (ref | (ref << 8));
     bad3 += (cvt_e4m3x2(d.div<3>(x), 0.f) & 0xffu) != ref;
     ++n;
   }
