@@ -38,7 +38,13 @@ __device__ __forceinline__ float max_nan(float a, float b) {
 }
 
 // two bf16 packed in a 32-bit word -> two floats (exact)
-__device__ __forceinline__ float bf16lo(uint32_t w) { return __uint_as_float(w << 16); }
+// (the low half moves up by an integer multiply: that runs on the FMA pipe, and the streaming
+// kernels keep the ALU pipe, which does the masks, packs and conversions, the busiest)
+__device__ __forceinline__ float bf16lo(uint32_t w) {
+  uint32_t r;
+  asm("mul.lo.u32 %0, %1, 65536;" : "=r"(r) : "r"(w));
+  return __uint_as_float(r);
+}
 __device__ __forceinline__ float bf16hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
 
 // round two floats to bf16 (RNE) and pack (lo in bits 0..15)
@@ -100,7 +106,9 @@ struct QuantDiv {
 // bit for bit, signed zeros included.
 __device__ __forceinline__ float2 bf16x2_unpack(uint32_t w) { return make_float2(bf16lo(w), bf16hi(w)); }
 __device__ __forceinline__ float2 bf16x2_unpack_neg(uint32_t w) {
-  return make_float2(__uint_as_float((w << 16) ^ 0x80000000u), __uint_as_float((w & 0xffff0000u) ^ 0x80000000u));
+  uint32_t lo;
+  asm("mad.lo.u32 %0, %1, 65536, 0x80000000;" : "=r"(lo) : "r"(w));   // (w << 16) ^ sign bit, one FMA-pipe instruction
+  return make_float2(__uint_as_float(lo), __uint_as_float((w & 0xffff0000u) ^ 0x80000000u));
 }
 // two bf16 values (one word) -> two e4m3 bytes (low 16 bits), finite scale s, nr = -RN(1/s)
 __device__ __forceinline__ uint32_t quantize2_sr(uint32_t w, float2 s2, float2 nr2) {

@@ -165,6 +165,7 @@ __device__ __forceinline__ void sts128(uint32_t addr, const uint4& v) {
 }
 
 constexpr int kStagedBlocksPerSm = 3;
+constexpr int kGroup = 8;   // chunks normalised, scaled and quantised together (their bf16 values stay in registers)
 
 template <int NCHUNK, bool PURE, bool FULL>
 __global__ void __launch_bounds__(kNormWarps * 32, kStagedBlocksPerSm)
@@ -179,10 +180,13 @@ rmsnorm_quant_staged_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bflo
   const uint32_t slot0 = uint32_t(__cvta_generic_to_shared(s_gamma)) + uint32_t(cols) * 4u +
                          uint32_t(warp) * 2u * kSlotBytes + uint32_t(lane) * 16u;
 
-  for (int i = threadIdx.x; i < cols / 8; i += blockDim.x) {
+  // gamma widened to float in two planes (columns 8i..8i+3 of every 8-column piece, then columns
+  // 8i+4..8i+7): a warp's 16-byte reads of either plane are contiguous, hence conflict-free
+  const int pieces = cols / 8;
+  for (int i = threadIdx.x; i < pieces; i += blockDim.x) {
     const uint4 gq = reinterpret_cast<const uint4*>(gamma)[i];
-    s_gamma[2 * i] = make_float4(bf16lo(gq.x), bf16hi(gq.x), bf16lo(gq.y), bf16hi(gq.y));
-    s_gamma[2 * i + 1] = make_float4(bf16lo(gq.z), bf16hi(gq.z), bf16lo(gq.w), bf16hi(gq.w));
+    s_gamma[i] = make_float4(bf16lo(gq.x), bf16hi(gq.x), bf16lo(gq.y), bf16hi(gq.y));
+    s_gamma[pieces + i] = make_float4(bf16lo(gq.z), bf16hi(gq.z), bf16lo(gq.w), bf16hi(gq.w));
   }
   __syncthreads();
 
@@ -216,49 +220,52 @@ rmsnorm_quant_staged_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bflo
     if (rnorm_out != nullptr && lane == 0) rnorm_out[row] = rn;
     const float rn_b = __bfloat162float(__float2bfloat16_rn(rn));  // kernels.py:32 `.astype(x.dtype)`
 
-    // pass 2: normalise, round to bf16 (the value the reference's norm returns), per-tile amax
+    // pass 2, in groups of G chunks whose normalised values stay in registers: normalise, round
+    // to bf16 (the value the reference's norm returns), per-tile amax; one exchange brings lane j
+    // of each half the amax of the group's chunk j % G, that lane computes the tile's scale and
+    // reciprocal, shuffles hand them to the lanes that need them; divide and store.
     const float2 rn2 = PURE ? make_float2(rn_b, rn_b) : make_float2(rn, rn);
-    uint32_t amax_bits[NCHUNK];
+    constexpr int G = NCHUNK < kGroup ? NCHUNK : kGroup;
 #pragma unroll
-    for (int c = 0; c < NCHUNK; ++c) {
-      const int col = col_base + c * 256;
-      amax_bits[c] = 0u;
-      if (FULL || col < cols) {
-        const uint4 xv = lds128(base + c * 512);
-        const uint32_t xi[4] = {xv.x, xv.y, xv.z, xv.w};
-        const float4 g0 = s_gamma[col >> 2], g1 = s_gamma[(col >> 2) + 1];
-        const float2 gf[4] = {make_float2(g0.x, g0.y), make_float2(g0.z, g0.w), make_float2(g1.x, g1.y), make_float2(g1.z, g1.w)};
-        uint4 yo;
-        uint32_t* yp = &yo.x;
+    for (int g = 0; g < NCHUNK / G; ++g) {
+      uint4 yo[G];
+      uint32_t amax_bits[G];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          float2 t = __fmul2_rn(bf16x2_unpack(xi[j]), rn2);
-          if (PURE) t = bf16x2_unpack(pack_bf16x2(t.x, t.y));   // kernels.py:32 rounds before the gamma multiply
-          t = __fmul2_rn(t, gf[j]);
-          yp[j] = pack_bf16x2(t.x, t.y);
+      for (int u = 0; u < G; ++u) {
+        const int c = g * G + u;
+        const int col = col_base + c * 256;
+        amax_bits[u] = 0u;
+        yo[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (FULL || col < cols) {
+          const uint4 xv = lds128(base + c * 512);
+          const uint32_t xi[4] = {xv.x, xv.y, xv.z, xv.w};
+          const float4 g0 = s_gamma[col >> 3], g1 = s_gamma[pieces + (col >> 3)];
+          const float2 gf[4] = {make_float2(g0.x, g0.y), make_float2(g0.z, g0.w), make_float2(g1.x, g1.y), make_float2(g1.z, g1.w)};
+          uint32_t* yp = &yo[u].x;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float2 t = __fmul2_rn(bf16x2_unpack(xi[j]), rn2);
+            if (PURE) t = bf16x2_unpack(pack_bf16x2(t.x, t.y));   // kernels.py:32 rounds before the gamma multiply
+            t = __fmul2_rn(t, gf[j]);
+            yp[j] = pack_bf16x2(t.x, t.y);
+          }
+          if (y != nullptr) *reinterpret_cast<uint4*>(y + row * cols + col) = yo[u];
+          amax_bits[u] = absmax8_h(yo[u]);
         }
-        sts128(base + c * 512, yo);
-        if (y != nullptr) *reinterpret_cast<uint4*>(y + row * cols + col) = yo;
-        amax_bits[c] = absmax8_h(yo);
       }
-    }
-    // one exchange brings lane j of each half the amax of chunk j % NCHUNK; that lane computes
-    // the tile's scale and reciprocal, and shuffles hand them to the lanes that need them
-    float s[NCHUNK], r[NCHUNK], s_mine;
-    bool fin;
-    tile_scales_own<NCHUNK>(exchange_tile_amax<NCHUNK>(amax_bits), s, r, s_mine, fin);
-    {
-      const int j = lane & 15;
-      const int col = j * 256 + (lane & 16) * 8;     // first column of the tile this lane computed
-      if (j < NCHUNK && (FULL || col < cols)) scales[row * (cols / kTile) + col / kTile] = s_mine;
-    }
-    // pass 3: divide and store
+      float s[G], r[G], s_mine;
+      bool fin;
+      tile_scales_own<G>(exchange_tile_amax<G>(amax_bits), s, r, s_mine, fin);
+      {
+        const int j = lane & 15;
+        const int col = (g * G + j) * 256 + (lane & 16) * 8;     // first column of the tile this lane computed
+        if (j < G && (FULL || col < cols)) scales[row * (cols / kTile) + col / kTile] = s_mine;
+      }
 #pragma unroll
-    for (int c = 0; c < NCHUNK; ++c) {
-      const int col = col_base + c * 256;
-      if (FULL || col < cols) {
-        const uint4 yo = lds128(base + c * 512);
-        *reinterpret_cast<uint2*>(q + row * cols + col) = fin ? quantize8_sr(yo, s[c], r[c]) : quantize8(yo, s[c]);
+      for (int u = 0; u < G; ++u) {
+        const int col = col_base + (g * G + u) * 256;
+        if (FULL || col < cols)
+          *reinterpret_cast<uint2*>(q + row * cols + col) = fin ? quantize8_sr(yo[u], s[u], r[u]) : quantize8(yo[u], s[u]);
       }
     }
   }
