@@ -147,6 +147,29 @@ int64_t tg_rmsnorm_bwd_static_max_scratch_bytes(void);
 int tg_rmsnorm_bwd_static(const void* x, const void* gamma, const void* g, float eps, void* dx,
                           void* dgamma, int64_t rows, int64_t cols, void* stream);
 
+/* ---- capped-logit cross-entropy --------------------------------------------------- */
+
+/* train-gpt model.py:97 (`cap * tanh(logits / cap)`, bf16, every op rounding) followed by
+ * losses.py:9-12 (float32 log_softmax over the vocabulary, gather of the target, per-token
+ * negative log-likelihood; the caller takes the mean).  One pass over the logits.
+ *   logits   bf16 [rows, ld], the unembedding GEMM's output, vocab <= ld
+ *   targets  int32 [rows]; values outside [0, vocab) clamp, as jnp.take_along_axis does
+ *   tanh_out bf16 [rows, ld_tanh] or NULL: bf16(tanh(bf16(logits / cap))), what the backward
+ *            needs (cap * tanh_out, rounded to bf16, is the capped logits model.forward returns)
+ *   lse, nll float32 [rows]: logsumexp of the capped logits, and lse - capped[target]
+ *   vocab, ld, ld_tanh multiples of 8; pointers 16-byte aligned.                          */
+int tg_softcap_ce_fwd(const void* logits, const int32_t* targets, float cap, void* tanh_out, float* lse,
+                      float* nll, int64_t rows, int64_t vocab, int64_t ld, int64_t ld_tanh, void* stream);
+
+/* The gradient of mean(nll) with respect to the uncapped logits (the reference gets it from
+ * jax.value_and_grad through losses.py:8-12 and model.py:97, train.py:129):
+ *   dlogits = gscale / rows * (softmax(capped) - onehot(target)) * (1 - tanh^2), bf16.
+ *   gscale  device float32 scalar (the cotangent of the mean loss) or NULL for 1
+ *   dlogits bf16 [rows, ld_d]; may be the very buffer tanh_in points to (in place).       */
+int tg_softcap_ce_bwd(const void* tanh_in, const int32_t* targets, const float* lse, const float* gscale,
+                      float cap, void* dlogits, int64_t rows, int64_t vocab, int64_t ld_tanh, int64_t ld_d,
+                      void* stream);
+
 /* ---- block-scaled FP8 GEMM -------------------------------------------------------- */
 
 /* Operand storage, seen from the GEMM  D[m,n] = sum_k A[m,k] * B[n,k]. */

@@ -18,6 +18,8 @@ What gets stored (bf16 as uint16 bit patterns, e4m3 as uint8):
   * `_fp8_backward`                                           (fp8.py:85-98)
   * `_rms_norm_pure`                                          (kernels.py:30-33)
   * the custom-VJP `_bwd` of the GPU norm                     (kernels.py:104-118)
+  * `cross_entropy_loss` on given capped logits               (losses.py:8-12; `model.forward`
+    and `config.Config` are stubbed, log_softmax is the float64 formula rounded once)
 The test-suite never imports the reference; it reads only the .npz.
 """
 import functools
@@ -63,6 +65,14 @@ def _install_jax_stand_in():
     jnp.max = np.max
     jnp.maximum = np.maximum
     jnp.tile = np.tile
+    jnp.take_along_axis = lambda a, i, axis: _wrap(np.take_along_axis(np.asarray(a), np.asarray(i), axis=axis))
+
+    def log_softmax(x, axis=-1):
+        x64 = np.asarray(x).astype(np.float64)
+        m = x64.max(axis=axis, keepdims=True)
+        return _wrap((x64 - m - np.log(np.exp(x64 - m).sum(axis=axis, keepdims=True))).astype(np.float32))
+
+    nn.log_softmax = log_softmax
 
     def mean(x, axis=None, keepdims=False):
         return _wrap(np.mean(np.asarray(x).astype(np.float64), axis=axis, keepdims=keepdims).astype(np.float32))
@@ -161,6 +171,21 @@ def main(ref_dir: str):
     out["norm_gy"] = gy.view(np.uint16)
     out["norm_dx"] = np.asarray(dx).view(np.uint16)
     out["norm_dgamma"] = np.asarray(dgamma).view(np.uint16)
+
+    # ---- cross-entropy on capped logits (losses.py:8-12) -----------------------------
+    ce_logits = (rng.standard_normal((40, 512)) * 6.0).clip(-15, 15).astype(BF16)
+    ce_targets = rng.integers(0, 512, size=(40,)).astype(np.int32)
+    model_stub = types.ModuleType("model")
+    model_stub.forward = lambda params, input_ids, cfg: _wrap(ce_logits)
+    config_stub = types.ModuleType("config")
+    config_stub.Config = object
+    sys.modules["model"], sys.modules["config"] = model_stub, config_stub
+    losses = importlib.import_module("losses")
+    ce = losses.cross_entropy_loss(None, None, _wrap(ce_targets), None)
+    del sys.modules["model"], sys.modules["config"]
+    out["ce_logits"] = ce_logits.view(np.uint16)
+    out["ce_targets"] = ce_targets
+    out["ce_loss"] = np.float32(ce)
 
     dst = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_vectors.npz")
     np.savez_compressed(dst, **out)

@@ -11,11 +11,11 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _run(mm, norm, steps, activation="gelu"):
+def _run(mm, norm, steps, activation="gelu", graph=False):
     from train_gpt_b200.step import StepConfig, Trainer, synthetic_batch
     cfg = StepConfig(vocab_size=512, seq_len=128, d_model=256, n_layers=2, n_heads=4, head_dim=64, d_ff=1024,
-                     mm=mm, norm=norm, activation=activation, lr=1e-3)
-    tr = Trainer(cfg, torch.device("cuda", 0), world_size=1, seed=0)
+                     mm=mm, norm=norm, loss="torch" if mm == "bf16" else "fused", activation=activation, lr=1e-3)
+    tr = Trainer(cfg, torch.device("cuda", 0), world_size=1, seed=0, graph=graph)
     losses, gnorms = [], []
     for i in range(steps):
         ids, tgt = synthetic_batch(cfg, 16, "cuda", seed=i, learnable=True)
@@ -47,3 +47,12 @@ def test_reference_configuration_step_runs():
     separate norm kernel, squared-ReLU MLP) trains too."""
     losses, _ = _run("fp8_ref", "kernel", 60, activation="relu2")
     assert torch.isfinite(losses).all() and float(losses[-10:].mean()) < float(losses[:5].mean()) - 0.5
+
+
+def test_graph_captured_step_follows_the_eager_trajectory():
+    """The whole step replayed from one CUDA graph gives the eager run's losses: the capture's
+    warm-up steps are undone, and every kernel on the path is deterministic."""
+    eager, eager_gn = _run("fp8", "fused", 12)
+    graph, graph_gn = _run("fp8", "fused", 12, graph=True)
+    assert torch.allclose(eager, graph, rtol=1e-4, atol=1e-5), (eager, graph)
+    assert torch.allclose(eager_gn, graph_gn, rtol=1e-3, atol=1e-5), (eager_gn, graph_gn)

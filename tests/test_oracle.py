@@ -111,3 +111,42 @@ def test_rmsnorm_quant_composition():
     q2, s2 = fo.quantize_to_fp8(no.rms_norm(x, gamma, 1e-6).astype(np.float32))
     assert np.array_equal(q.view(np.uint8), q2.view(np.uint8)) and np.array_equal(s, s2)
     assert q.shape == x.shape and s.shape == (5, 7, 2)
+
+
+def test_loss_oracle_matches_the_reference_fixture(golden):
+    """losses.py:8-12 executed from the reference's source on capped logits."""
+    from oracle import loss_oracle as lo
+    z = golden["ce_logits"].view(fo.BF16)
+    loss, nll, lse = lo.cross_entropy(z, golden["ce_targets"])
+    assert abs(float(loss) - float(golden["ce_loss"])) <= 2e-6 * abs(float(golden["ce_loss"]))
+    assert nll.shape == (z.shape[0],) and np.all(nll > 0)
+
+
+def test_softcap_restatement_properties():
+    """model.py:97 op by op in bf16: odd, bounded by the cap, identity-like near zero."""
+    from oracle import loss_oracle as lo
+    bits = np.arange(0, 0x7F80, dtype=np.uint16)                     # every finite non-negative bf16
+    x = bits.view(fo.BF16)
+    z, t = lo.softcap(x, 15.0)
+    zn, _ = lo.softcap((-x.astype(np.float32)).astype(fo.BF16), 15.0)
+    assert np.array_equal(z.view(np.uint16) ^ 0x8000, zn.view(np.uint16))
+    zf = z.astype(np.float32)
+    assert zf.max() == 15.0 and np.all(np.diff(zf) >= 0)
+    small = (x.astype(np.float32) < 0.05) & (x.astype(np.float32) > 1e-30)     # subnormals lose bits in x / cap
+    assert np.allclose(zf[small], x.astype(np.float32)[small], rtol=2 ** -7, atol=0)
+
+
+def test_loss_gradient_restatement_against_finite_differences():
+    from oracle import loss_oracle as lo
+    rng = np.random.default_rng(5)
+    x = (rng.standard_normal((6, 64)) * 4).astype(fo.BF16)
+    tg = rng.integers(0, 64, size=6)
+    g = lo.softcap_cross_entropy_grad(x, tg, 15.0)
+    assert np.allclose(g.sum(axis=1) * 0, 0) and g.shape == x.shape
+    # the analytic gradient of the SMOOTH function (no bf16 rounding) agrees to rounding level
+    xs = x.astype(np.float64)
+    z = 15.0 * np.tanh(xs / 15.0)
+    p = np.exp(z - z.max(1, keepdims=True)); p /= p.sum(1, keepdims=True)
+    p[np.arange(6), tg] -= 1
+    smooth = p * (1 - np.tanh(xs / 15.0) ** 2) / 6
+    assert np.allclose(g, smooth, rtol=0.05, atol=2e-3)

@@ -47,6 +47,8 @@ SYMBOLS = {
     "tg_rmsnorm_bwd": (_i, [_p, _p, _p, _f, _p, _p, _p, _i64, _i64, _p]),
     "tg_rmsnorm_bwd_static_max_scratch_bytes": (_i64, []),
     "tg_rmsnorm_bwd_static": (_i, [_p, _p, _p, _f, _p, _p, _i64, _i64, _p]),
+    "tg_softcap_ce_fwd": (_i, [_p, _p, _f, _p, _p, _p, _i64, _i64, _i64, _i64, _p]),
+    "tg_softcap_ce_bwd": (_i, [_p, _p, _p, _p, _f, _p, _i64, _i64, _i64, _i64, _p]),
     "tg_gemm_fp8_blockscaled": (_i, [C.POINTER(GemmArgs), _p]),
 }
 

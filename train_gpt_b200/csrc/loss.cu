@@ -1,0 +1,163 @@
+// Capped-logit cross-entropy, forward and backward, one pass over the logits each.
+//
+// Reference semantics: train-gpt model.py:97 (`cap * tanh(logits / cap)` on the bf16 output of
+// the unembedding GEMM, every op rounding to bf16, the Python-float cap weakly typed = bf16)
+// followed by losses.py:9-12 (cast to float32, log_softmax over the vocabulary, gather the
+// target's log-probability, mean over tokens).  Done op by op that is five elementwise passes
+// and two softmax passes over a (tokens x vocab) tensor (3.3 GB in bf16 at 32768 x 50304, twice
+// that in float32); here the forward reads the logits once and writes the bf16 tanh values,
+// and the backward turns those into the logits' gradient in place.
+//
+// Layout: one thread block per token row; each thread walks the row in 16-byte pieces (8 bf16)
+// and keeps a running (max, sum of exp) pair; the block combines the pairs.
+#include "common.cuh"
+
+namespace tg {
+
+constexpr int kLossThreads = 256;
+
+// RN_bf16(v) as a float
+__device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+struct Softcap {
+  float c, r;   // the cap rounded to bf16, and RN(1/c)
+  __device__ __forceinline__ explicit Softcap(float cap) {
+    c = round_bf16(cap);
+    r = __frcp_rn(c);
+  }
+  // bf16(tanh(bf16(x / c))): the division is q0 = x*r, q = fma(-fma(q0, c, -x), r, q0), which is
+  // the correctly rounded quotient when r is the correctly rounded reciprocal (Markstein); the
+  // residual is taken as q0*c - x and subtracted so that x = -0 stays -0
+  __device__ __forceinline__ float tanh_of(float x) const {
+    const float q0 = __fmul_rn(x, r);
+    const float a = round_bf16(__fmaf_rn(-__fmaf_rn(q0, c, -x), r, q0));
+    return round_bf16(tanhf(a));
+  }
+  __device__ __forceinline__ float z_of_tanh(float t) const { return round_bf16(__fmul_rn(c, t)); }
+};
+
+// (m, s) <- combine with (m2, s2): s counts exp(z - m)
+__device__ __forceinline__ void lse_merge(float& m, float& s, float m2, float s2) {
+  const float mn = fmaxf(m, m2);
+  s = s * __expf(m - mn) + s2 * __expf(m2 - mn);
+  m = mn;
+}
+
+__global__ void __launch_bounds__(kLossThreads)
+softcap_ce_fwd_kernel(const __nv_bfloat16* __restrict__ logits, const int32_t* __restrict__ targets, float cap,
+                      __nv_bfloat16* __restrict__ tanh_out, float* __restrict__ lse_out, float* __restrict__ nll_out,
+                      int vocab, int64_t ld, int64_t ld_t) {
+  __shared__ float s_m[kLossThreads / 32], s_s[kLossThreads / 32];
+  const int64_t row = blockIdx.x;
+  const __nv_bfloat16* p = logits + row * ld;
+  const Softcap sc(cap);
+  float m = -3.0e38f, s = 0.f;
+  for (int i = threadIdx.x * 8; i < vocab; i += kLossThreads * 8) {
+    const uint4 w = ld_nc_v4(p + i);
+    const uint32_t xi[4] = {w.x, w.y, w.z, w.w};
+    float z[8];
+    uint4 to;
+    uint32_t* tp = &to.x;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float t0 = sc.tanh_of(bf16lo(xi[j])), t1 = sc.tanh_of(bf16hi(xi[j]));
+      tp[j] = pack_bf16x2(t0, t1);   // exact: both are bf16 values already
+      z[2 * j] = sc.z_of_tanh(t0);
+      z[2 * j + 1] = sc.z_of_tanh(t1);
+    }
+    if (tanh_out != nullptr) *reinterpret_cast<uint4*>(tanh_out + row * ld_t + i) = to;
+    float mx = z[0];
+#pragma unroll
+    for (int j = 1; j < 8; ++j) mx = fmaxf(mx, z[j]);
+    const float mn = fmaxf(m, mx);
+    float acc = s * __expf(m - mn);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc += __expf(z[j] - mn);
+    s = acc;
+    m = mn;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) lse_merge(m, s, __shfl_xor_sync(0xffffffffu, m, o), __shfl_xor_sync(0xffffffffu, s, o));
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) { s_m[warp] = m; s_s[warp] = s; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    m = s_m[0]; s = s_s[0];
+#pragma unroll
+    for (int wi = 1; wi < kLossThreads / 32; ++wi) lse_merge(m, s, s_m[wi], s_s[wi]);
+    const float lse = m + logf(s);
+    int t = targets[row];
+    t = t < 0 ? 0 : (t >= vocab ? vocab - 1 : t);   // out-of-range targets clamp, as jnp.take_along_axis does
+    const float zt = sc.z_of_tanh(sc.tanh_of(__bfloat162float(p[t])));
+    lse_out[row] = lse;
+    nll_out[row] = lse - zt;
+  }
+}
+
+// dlogits = gscale / rows * (exp(z - lse) - [col == target]) * (1 - tanh^2), rounded to bf16.
+// `d` may be the buffer `tanh_in` lives in: every element is read and then written by one thread.
+__global__ void __launch_bounds__(kLossThreads)
+softcap_ce_bwd_kernel(const __nv_bfloat16* tanh_in, const int32_t* __restrict__ targets,
+                      const float* __restrict__ lse, const float* __restrict__ gscale, float cap, float inv_rows,
+                      __nv_bfloat16* d, int vocab, int64_t ld_t, int64_t ld_d) {
+  const int64_t row = blockIdx.x;
+  const Softcap sc(cap);
+  const float l = lse[row];
+  const float g = (gscale != nullptr ? *gscale : 1.0f) * inv_rows;
+  int t = targets[row];
+  t = t < 0 ? 0 : (t >= vocab ? vocab - 1 : t);
+  const __nv_bfloat16* p = tanh_in + row * ld_t;
+  for (int i = threadIdx.x * 8; i < vocab; i += kLossThreads * 8) {
+    const uint4 w = *reinterpret_cast<const uint4*>(p + i);
+    const uint32_t ti[4] = {w.x, w.y, w.z, w.w};
+    uint4 o;
+    uint32_t* op = &o.x;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float t0 = bf16lo(ti[j]), t1 = bf16hi(ti[j]);
+      float p0 = __expf(sc.z_of_tanh(t0) - l), p1 = __expf(sc.z_of_tanh(t1) - l);
+      if (i + 2 * j == t) p0 -= 1.0f;
+      if (i + 2 * j + 1 == t) p1 -= 1.0f;
+      op[j] = pack_bf16x2(p0 * g * __fmaf_rn(-t0, t0, 1.0f), p1 * g * __fmaf_rn(-t1, t1, 1.0f));
+    }
+    *reinterpret_cast<uint4*>(d + row * ld_d + i) = o;
+  }
+}
+
+}  // namespace tg
+
+using namespace tg;
+
+extern "C" int tg_softcap_ce_fwd(const void* logits, const int32_t* targets, float cap, void* tanh_out, float* lse,
+                                 float* nll, int64_t rows, int64_t vocab, int64_t ld, int64_t ld_tanh, void* stream) {
+  if (rows < 0 || vocab <= 0 || vocab % 8 != 0 || ld % 8 != 0 || ld < vocab || vocab > INT32_MAX) return TG_ERR_SHAPE;
+  if (tanh_out != nullptr && (ld_tanh % 8 != 0 || ld_tanh < vocab)) return TG_ERR_SHAPE;
+  if (!(cap > 0.0f)) return TG_ERR_SHAPE;
+  if (rows > INT32_MAX) return TG_ERR_TOO_LARGE;
+  if (rows == 0) return TG_OK;
+  if (!aligned16(logits) || !aligned16(tanh_out)) return TG_ERR_ALIGN;
+  if (int rc = check_arch()) return rc;
+  softcap_ce_fwd_kernel<<<int(rows), kLossThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(logits), targets, cap, static_cast<__nv_bfloat16*>(tanh_out), lse, nll,
+      int(vocab), ld, ld_tanh);
+  TG_CUDA_CHECK(cudaGetLastError());
+  return TG_OK;
+}
+
+extern "C" int tg_softcap_ce_bwd(const void* tanh_in, const int32_t* targets, const float* lse, const float* gscale,
+                                 float cap, void* dlogits, int64_t rows, int64_t vocab, int64_t ld_tanh, int64_t ld_d,
+                                 void* stream) {
+  if (rows < 0 || vocab <= 0 || vocab % 8 != 0 || ld_tanh % 8 != 0 || ld_d % 8 != 0 || ld_tanh < vocab || ld_d < vocab ||
+      vocab > INT32_MAX)
+    return TG_ERR_SHAPE;
+  if (!(cap > 0.0f)) return TG_ERR_SHAPE;
+  if (rows > INT32_MAX) return TG_ERR_TOO_LARGE;
+  if (rows == 0) return TG_OK;
+  if (!aligned16(tanh_in) || !aligned16(dlogits)) return TG_ERR_ALIGN;
+  if (int rc = check_arch()) return rc;
+  softcap_ce_bwd_kernel<<<int(rows), kLossThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(tanh_in), targets, lse, gscale, cap, 1.0f / float(rows),
+      static_cast<__nv_bfloat16*>(dlogits), int(vocab), ld_tanh, ld_d);
+  TG_CUDA_CHECK(cudaGetLastError());
+  return TG_OK;
+}

@@ -162,6 +162,42 @@ def rmsnorm_bwd(x, gamma, g, eps: float):
     return dx, dgamma
 
 
+# ---- capped-logit cross-entropy -----------------------------------------------------------
+
+def softcap_ce_fwd(logits, targets, cap: float, want_tanh: bool = True):
+    """model.py:97 + losses.py:9-12 on the uncapped bf16 logits (rows, vocab).
+    Returns (nll f32 (rows,), lse f32 (rows,), tanh bf16 (rows, vocab) or None)."""
+    logits = _need(logits, torch.bfloat16, "logits")
+    if logits.dim() != 2:
+        raise ValueError("logits must be 2-D (rows, vocab)")
+    if targets.dtype != torch.int32 or not targets.is_cuda or not targets.is_contiguous():
+        raise TypeError("targets must be a contiguous int32 CUDA tensor")
+    rows, vocab = logits.shape
+    if targets.numel() != rows:
+        raise ValueError("one target per row")
+    lib = _lib.load()
+    nll = torch.empty((rows,), dtype=torch.float32, device=logits.device)
+    lse = torch.empty((rows,), dtype=torch.float32, device=logits.device)
+    th = torch.empty_like(logits) if want_tanh else None
+    _lib.check(lib.tg_softcap_ce_fwd(_ptr(logits), _ptr(targets), float(cap), _ptr(th), _ptr(lse), _ptr(nll),
+                                     rows, vocab, vocab, vocab, _stream()), "tg_softcap_ce_fwd")
+    return nll, lse, th
+
+
+def softcap_ce_bwd(th, targets, lse, gscale, cap: float, in_place: bool = False):
+    """Gradient of mean(nll) w.r.t. the uncapped logits; `gscale` is a float32 device scalar
+    (or None for 1).  in_place=True overwrites `th` with the gradient."""
+    th = _need(th, torch.bfloat16, "tanh")
+    rows, vocab = th.shape
+    d = th if in_place else torch.empty_like(th)
+    if gscale is not None:
+        gscale = _need(gscale.reshape(1), torch.float32, "gscale")
+    lib = _lib.load()
+    _lib.check(lib.tg_softcap_ce_bwd(_ptr(th), _ptr(targets), _ptr(lse), _ptr(gscale), float(cap), _ptr(d),
+                                     rows, vocab, vocab, vocab, _stream()), "tg_softcap_ce_bwd")
+    return d
+
+
 # ---- GEMM ---------------------------------------------------------------------------------
 
 def new_status(device) -> torch.Tensor:

@@ -29,7 +29,7 @@ from dataclasses import dataclass
 import torch
 import torch.nn.functional as F
 
-from . import fp8, kernels, ops
+from . import fp8, kernels, losses, ops
 from .dp import GradBuckets
 
 
@@ -48,6 +48,7 @@ class StepConfig:
     activation: str = "gelu"        # "gelu" (BASELINE configuration 3) or "relu2" (model.py:72)
     mm: str = "fp8"
     norm: str = "fused"
+    loss: str = "fused"             # "fused": one CUDA pass each way over the logits; "torch": op by op (CPU tests)
     lr: float = 3e-4
     weight_decay: float = 0.1       # train.py make_optimizer default use
     clip_norm: float = 1.0
@@ -139,7 +140,8 @@ class GPT:
     def _act(self, u):
         return F.gelu(u) if self.cfg.activation == "gelu" else F.relu(u) ** 2      # model.py:72
 
-    def forward(self, ids):
+    def raw_logits(self, ids):
+        """model.py:75-96: everything up to the unembedding GEMM (no cap)."""
         c = self.cfg
         B, T = ids.shape
         x = self.embed[ids] + self.pos[:T]                                          # model.py:83
@@ -153,27 +155,43 @@ class GPT:
             h, hq = self._norm(x, lp["norm2"])                                      # model.py:77
             x = x + self._mm(self._act(self._mm(h, lp["w_up"], hq)), lp["w_down"])
         x, _ = self._norm(x, self.final_norm)                                       # model.py:93
-        logits = x @ self.unembed                                                   # stays bf16 (bench_fp8_norm.py:86)
-        return c.logit_cap * torch.tanh(logits / c.logit_cap)                       # model.py:97
+        return x @ self.unembed                                                     # stays bf16 (bench_fp8_norm.py:86)
+
+    def forward(self, ids):
+        logits = self.raw_logits(ids)
+        return self.cfg.logit_cap * torch.tanh(logits / self.cfg.logit_cap)         # model.py:97
 
     def loss(self, ids, targets):
+        if self.cfg.loss == "fused":
+            return losses.capped_cross_entropy(self.raw_logits(ids), targets, self.cfg.logit_cap)
         logits = self.forward(ids).float()                                          # losses.py:9
         return F.cross_entropy(logits.view(-1, logits.shape[-1]), targets.view(-1))  # losses.py:10-12
 
 
 class Trainer:
     """train.py:126-137 with the gradient exchange inserted: loss + backward (bucketed
-    all-reduce overlapping it), global norm, clip, AdamW."""
+    all-reduce overlapping it), global norm, clip, AdamW.
 
-    def __init__(self, cfg: StepConfig, device, world_size: int = 1, seed: int = 0):
+    graph=True captures the whole step (forward, backward, the bucket all-reduces, clip and
+    AdamW) into ONE CUDA graph at the first call and replays it afterwards: the step issues
+    about 1900 kernel launches through Python, which leaves the GPU idle a quarter of the time
+    when they are launched one by one.  Batches are copied into fixed device buffers before each
+    replay; the returned loss and gradient norm are the graph's own output tensors (read them
+    before the next step).  Capture needs two eager warm-up steps; parameters and optimizer
+    state are restored after them, so a captured run follows the same trajectory as an eager one.
+    """
+
+    def __init__(self, cfg: StepConfig, device, world_size: int = 1, seed: int = 0, graph: bool = False):
         self.cfg, self.device, self.world = cfg, device, world_size
         self.model = GPT(cfg, device, seed)                     # same seed on every rank: replicated weights
         self.buckets = GradBuckets(self.model.buckets(), world_size)
-        use_fused = torch.device(device).type == "cuda"
+        on_gpu = torch.device(device).type == "cuda"
+        self._want_graph = bool(graph) and on_gpu
+        self._graph = None
         self.opt = torch.optim.AdamW(self.model.parameters(), lr=cfg.lr, weight_decay=cfg.weight_decay,
-                                     betas=(0.9, 0.999), eps=1e-8, fused=use_fused)
+                                     betas=(0.9, 0.999), eps=1e-8, fused=on_gpu, capturable=self._want_graph)
 
-    def step(self, ids, targets):
+    def _eager_step(self, ids, targets):
         self.buckets.zero()
         loss = self.model.loss(ids, targets)
         loss.backward()
@@ -185,6 +203,44 @@ class Trainer:
                 f.mul_(scale.to(f.dtype))
         self.opt.step()
         return loss.detach(), gnorm
+
+    def _opt_state_tensors(self):
+        return [t for st in self.opt.state.values() for t in st.values() if torch.is_tensor(t)]
+
+    def _capture(self, ids, targets):
+        self._ids, self._tgt = ids.clone(), targets.clone()
+        params = self.model.parameters()
+        saved_p = [p.detach().clone() for p in params]
+        saved_s = {id(t): t.clone() for t in self._opt_state_tensors()}
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):                      # lazy initialisations (optimizer state, kernel attributes, NCCL)
+                self._eager_step(self._ids, self._tgt)
+        torch.cuda.current_stream().wait_stream(side)
+        with torch.no_grad():
+            for p, q in zip(params, saved_p):
+                p.copy_(q)
+            for t in self._opt_state_tensors():
+                if id(t) in saved_s:
+                    t.copy_(saved_s[id(t)])
+                else:
+                    t.zero_()                       # state created by the warm-up: back to its initial value
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self._loss, self._gnorm = self._eager_step(self._ids, self._tgt)
+        self._graph = g
+
+    def step(self, ids, targets):
+        if not self._want_graph:
+            return self._eager_step(ids, targets)
+        if self._graph is None:
+            self._capture(ids, targets)
+        self._ids.copy_(ids)
+        self._tgt.copy_(targets)
+        self._graph.replay()
+        return self._loss, self._gnorm
 
 
 def synthetic_batch(cfg: StepConfig, batch: int, device, seed: int, learnable: bool = False):
@@ -214,10 +270,10 @@ def step_flops(cfg: StepConfig, tokens: int) -> float:
 
 
 def bench_train_step(world: int, rank: int, device, dist, steps: int = 5, warmup: int = 3, batch_per_gpu: int = 32,
-                     cfg: StepConfig = StepConfig()):
+                     cfg: StepConfig = StepConfig(), graph: bool = True):
     """Tokens/s of the data-parallel step (BASELINE configuration 3): batch sharded by rank,
     weights replicated, gradients all-reduced per layer bucket over NCCL."""
-    tr = Trainer(cfg, device, world_size=world)
+    tr = Trainer(cfg, device, world_size=world, graph=graph)
     batches = [synthetic_batch(cfg, batch_per_gpu, device, seed=1000 * rank + i) for i in range(2)]
     for i in range(warmup):
         loss, _ = tr.step(*batches[i % 2])
@@ -245,6 +301,6 @@ def bench_train_step(world: int, rank: int, device, dist, steps: int = 5, warmup
         "mfu_flops_per_s": step_flops(cfg, tokens) / sec,
         "config": {"layers": cfg.n_layers, "d_model": cfg.d_model, "heads": cfg.n_heads, "d_ff": cfg.d_ff,
                    "vocab": cfg.vocab_size, "seq": cfg.seq_len, "batch_per_gpu": batch_per_gpu, "activation": cfg.activation,
-                   "mm": cfg.mm, "norm": cfg.norm, "optimizer": "AdamW lr 3e-4", "parallelism": f"dp{world}",
+                   "mm": cfg.mm, "norm": cfg.norm, "optimizer": "AdamW lr 3e-4", "parallelism": f"dp{world}", "cuda_graph": bool(graph),
                    "grad_bytes_allreduced": tr.buckets.bytes(), "data": "tokens uniform over the vocabulary (seeded)"},
     }
