@@ -200,7 +200,17 @@ typedef struct tg_gemm_args {
   uint32_t* status; /* device word, must be 0 on entry; a kernel whose bounded wait on
                        a copy or MMA barrier runs out stores a non-zero code here and
                        returns (results are then invalid).  May be NULL.              */
+  void* workspace;  /* optional, caller-owned, 16-byte aligned.  With at least
+                       tg_gemm_workspace_bytes() bytes here, a GEMM with few output tiles
+                       and a long contraction (the weight gradient) is cut along the
+                       contraction so that all SMs work; float32 partial sums go here and
+                       are added in a fixed order.  NULL or too small: no cut.           */
+  int64_t workspace_bytes;
 } tg_gemm_args;
+
+/* Bytes of workspace with which tg_gemm_fp8_blockscaled would cut this problem's contraction
+ * (0 when it would not).  No counterpart in the reference.                              */
+int64_t tg_gemm_workspace_bytes(const tg_gemm_args* a);
 
 /* Replaces `jax.nn.scaled_matmul` as called at fp8.py:70-76 (lhs (M,K), rhs (N,K),
  * scales per 128 of K) followed by the bf16 cast of fp8.py:78 -- and, with other

@@ -37,8 +37,8 @@ def test_header_symbols_are_exported_and_bound(lib):
 
 def test_gemm_args_struct_matches_header_layout():
     from train_gpt_b200._lib import GemmArgs
-    # 20 fields; pointers/int64 8-byte aligned, ints padded as a C compiler would
-    assert ctypes.sizeof(GemmArgs) == 8 * 2 + 8 * 2 + 4 * 2 + 8 * 3 + 8 * 3 + 8 + 8 * 2 + 8 + 8 * 3 + 8
+    # 22 fields; pointers/int64 8-byte aligned, ints padded as a C compiler would
+    assert ctypes.sizeof(GemmArgs) == 8 * 2 + 8 * 2 + 4 * 2 + 8 * 3 + 8 * 3 + 8 + 8 * 2 + 8 + 8 * 3 + 8 + 8 * 2
     assert GemmArgs.sa.offset == 40 and GemmArgs.d.offset == 96 and GemmArgs.status.offset == 144
 
 

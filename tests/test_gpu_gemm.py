@@ -170,3 +170,38 @@ def test_fp8_backward_with_block_quantised_gradient(M, K, N):
     da_ref, db_ref = fo.backward_fp8(a, b, g, weight_tile=(128, 128), wgrad_grad_tile=(128, 128))
     _close(from_torch_bf16(da), da_ref)
     _close(from_torch_bf16(db), db_ref)
+
+
+@pytest.mark.parametrize("K,N,T,gran", [(256, 384, 4096, 1), (512, 512, 8192, 1), (256, 512, 4096, 128)])
+def test_wgrad_with_split_contraction_matches_unsplit_and_oracle(K, N, T, gran):
+    """Few output tiles, long contraction: the library cuts the contraction when given workspace.
+    The cut changes only the float32 summation order."""
+    from train_gpt_b200 import ops
+    rng = np.random.default_rng(K + N + T)
+    x = normal_bf16(rng, (T, K))
+    g = normal_bf16(rng, (T, N))
+    xq, xs = ops.quantize_colwise(to_torch_bf16(x))
+    if gran == 1:
+        gq, gs = ops.quantize_colwise(to_torch_bf16(g))
+        tile = (128, 1)
+    else:
+        gq, gs = ops.quantize_block128(to_torch_bf16(g))
+        tile = (128, 128)
+    import ctypes as C
+    from train_gpt_b200 import _lib
+    st = ops.new_status("cuda")
+    a = ops.gemm_blockscaled(xq, gq, xs, gs, M=K, N=N, K=T, a_major=_lib.TG_MAJOR_MN, b_major=_lib.TG_MAJOR_MN,
+                             sa_strides=(1, K), sb_strides=(1, gs.shape[1]), sb_gran_n=gran, out_dtype=torch.float32,
+                             status=st, split=False)
+    b = ops.gemm_wgrad(xq, xs, gq, gs, out_dtype=torch.float32, status=st, grad_tile=tile)
+    assert int(st.item()) == 0
+    assert torch.allclose(a, b, rtol=1e-5, atol=1e-5 * float(a.abs().max()))
+    assert not torch.equal(a, b) or T < 2048          # the split path really ran (different rounding somewhere)
+    x_q, x_s = fo.quantize_colwise(x.astype(np.float32))
+    if gran == 1:
+        g_q, g_s = fo.quantize_colwise(g.astype(np.float32))
+    else:
+        g_q, g_sb = fo.quantize_block2d(g.astype(np.float32))
+        g_s = np.repeat(g_sb, 128, axis=1)
+    ref = fo.scaled_matmul(x_q.T, g_q.T, x_s.T, g_s.T)
+    _close(b.cpu().numpy(), ref)

@@ -29,6 +29,7 @@ class GemmArgs(C.Structure):
         ("sb", _p), ("sb_stride_n", _i64), ("sb_stride_kb", _i64), ("sb_gran_n", _i),
         ("d", _p), ("ldd", _i64), ("out_dtype", _i),
         ("M", _i64), ("N", _i64), ("K", _i64), ("status", _p),
+        ("workspace", _p), ("workspace_bytes", _i64),
     ]
 
 
@@ -49,6 +50,7 @@ SYMBOLS = {
     "tg_rmsnorm_bwd_static": (_i, [_p, _p, _p, _f, _p, _p, _i64, _i64, _p]),
     "tg_softcap_ce_fwd": (_i, [_p, _p, _f, _p, _p, _p, _i64, _i64, _i64, _i64, _p]),
     "tg_softcap_ce_bwd": (_i, [_p, _p, _p, _p, _f, _p, _i64, _i64, _i64, _i64, _p]),
+    "tg_gemm_workspace_bytes": (_i64, [C.POINTER(GemmArgs)]),
     "tg_gemm_fp8_blockscaled": (_i, [C.POINTER(GemmArgs), _p]),
 }
 

@@ -102,9 +102,12 @@ struct GemmParams {
   long long sb_sn, sb_sk;
   void* d;              // output, row pitch ldd elements
   long long ldd;
-  int M, N, nkb;
+  int M, N, nkb;        // nkb = contraction blocks per work item (all of them unless the contraction is split)
   int a_mn, b_mn;       // 1 = MN-major storage
   int tiles_m, tiles_n;
+  int ksplit;           // the contraction is cut into this many equal ranges; range s of a tile is its own
+                        // work item and writes its float32 partial sums to d + s * slice_elems
+  long long slice_elems;
   unsigned* status;
 };
 
@@ -384,6 +387,7 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_tiles = p.tiles_m * p.tiles_n;
+  const int n_items = n_tiles * p.ksplit;     // work item i = (tile i % n_tiles, contraction range i / n_tiles)
   // A pair (cluster of two CTAs) shares one 256 x 256 tile: CTA r of the pair owns rows
   // r*128.. of it (its A tile, its TMEM, its output rows) and fetches B rows r*128.. for both.
   const uint32_t crank = CTA2 ? cluster_ctarank() : 0u;
@@ -429,14 +433,15 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
       // The whole warp walks the loop (uniform control flow); one elected lane issues.
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = first_tile; ok && tile < n_tiles; tile += tile_step) {
+      for (int item = first_tile; ok && item < n_items; item += tile_step) {
+        const int tile = item % n_tiles, kb_off = (item / n_tiles) * p.nkb;
         const int m0 = (tile / p.tiles_n) * TM + row_off, n0 = (tile % p.tiles_n) * BN;
         for (int kb = 0; kb < p.nkb; ++kb, ++it) {
           const int s = it % kStages;
           ok = __all_sync(0xffffffffu, mbar_wait(empty_bar(s), ((it / kStages) & 1u) ^ 1u, abort_flag, p.status, 1u));
           if (!ok) break;
           if (elect_one()) {
-            const int k0 = kb * BK;
+            const int k0 = (kb_off + kb) * BK;
             const uint32_t dst = sbase + s * C::stage_bytes;
             if (CTA2) {
               // both CTAs count their bytes on the LEADER's barrier: its MMA thread consumes both halves
@@ -472,7 +477,7 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const uint64_t a_desc0 = make_smem_desc(sbase);
       const uint64_t b_desc0 = make_smem_desc(sbase + kTileBytes);
       int my_tiles = 0;
-      for (int tile = first_tile; tile < n_tiles; tile += tile_step) ++my_tiles;
+      for (int item = first_tile; item < n_items; item += tile_step) ++my_tiles;
       const uint32_t total = uint32_t(my_tiles) * uint32_t(p.nkb);
       bool ok = true;
       bool ready = false;  // barriers of block `it` already seen complete by an early probe
@@ -555,29 +560,34 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
       return v;
     };
-    auto open_tile = [&](int tile) {
+    uint8_t* d_base = static_cast<uint8_t*>(p.d);
+    auto open_tile = [&](int item) {
+      const int tile = item % n_tiles;
+      const long long ks = item / n_tiles, kb_off = ks * p.nkb;
+      d_base = static_cast<uint8_t*>(p.d) + ks * p.slice_elems * C::esize;
       m0 = (tile / p.tiles_n) * TM + row_off;
       n0 = (tile % p.tiles_n) * BN;
       const int m = m0 + r;
       m_ok = m < p.M;
-      sa_ptr = p.sa + (long long)(m_ok ? m : 0) * p.sa_sm;
+      sa_ptr = p.sa + (long long)(m_ok ? m : 0) * p.sa_sm + kb_off * p.sa_sk;
       if (SB_GRAN == 1) {
         const int col = n0 + c0 + kPerLane * lane;   // N % 8 == 0, so a pair is in or out together
         sb_ok = col < p.N;
-        sb_ptr = p.sb + (long long)(sb_ok ? col : 0) * p.sb_sn;
+        sb_ptr = p.sb + (long long)(sb_ok ? col : 0) * p.sb_sn + kb_off * p.sb_sk;
       } else {                                       // one scale per 128 columns
         const int nblk = (n0 + c0) / 128;
         sb_ok = true;
-        sb_ptr = p.sb + (long long)((nblk * 128 < p.N) ? nblk : 0) * p.sb_sn;
+        sb_ptr = p.sb + (long long)((nblk * 128 < p.N) ? nblk : 0) * p.sb_sn + kb_off * p.sb_sk;
       }
       sa_next = m_ok ? __ldg(sa_ptr) : 0.f;
       sb_next = load_sb(0);
     };
 
-    if (first_tile < n_tiles) open_tile(first_tile);
+    if (first_tile < n_items) open_tile(first_tile);
     const uint32_t tempty_remote0 = CTA2 ? mapa(tempty_bar(0), 0u) : 0u;  // the leader's barrier, as seen from here
-    for (int tile = first_tile; tile < n_tiles; tile += tile_step) {
+    for (int tile = first_tile; tile < n_items; tile += tile_step) {
       const int tile_m0 = m0, tile_n0 = n0;
+      uint8_t* const tile_d = d_base;
       float2 acc[kCols / 2];
 #pragma unroll
       for (int j = 0; j < kCols / 2; ++j) acc[j] = make_float2(0.f, 0.f);
@@ -631,7 +641,7 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
 
       // start the next tile's first scale loads before the stores of this one
-      if (tile + tile_step < n_tiles) open_tile(tile + tile_step);
+      if (tile + tile_step < n_items) open_tile(tile + tile_step);
 
       // ---- epilogue: registers -> this warp's swizzled staging rows -> coalesced stores ------
       // Each thread holds one row; a warp-private transpose through shared memory lets every
@@ -664,7 +674,7 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
         __syncwarp();
         const int col = tile_n0 + c0 + ph * C::phase_cols + my_chunk * (16 / C::esize);
-        uint8_t* dcol = static_cast<uint8_t*>(p.d) + (long long)col * C::esize;
+        uint8_t* dcol = tile_d + (long long)col * C::esize;
 #pragma unroll
         for (int i = 0; i < 32 / RPI; ++i) {
           const int rr = i * RPI + lane / LPR;
@@ -739,7 +749,7 @@ static int launch_gemm(const tg_gemm_args* a, GemmParams p, cudaStream_t st) {
   constexpr int TM = CTA2 ? 2 * BM : BM;
   p.tiles_m = int((a->M + TM - 1) / TM);
   p.tiles_n = int((a->N + BN_ - 1) / BN_);
-  const int64_t n_tiles = int64_t(p.tiles_m) * p.tiles_n;
+  const int64_t n_tiles = int64_t(p.tiles_m) * p.tiles_n * p.ksplit;   // work items
   if (n_tiles > INT32_MAX || n_tiles * p.nkb > INT32_MAX) return TG_ERR_TOO_LARGE;
   const int sms = sm_count();
   int grid = int(n_tiles < sms ? n_tiles : sms);
@@ -795,14 +805,68 @@ static int launch_gemm(const tg_gemm_args* a, GemmParams p, cudaStream_t st) {
   return TG_OK;
 }
 
+// ---- split contraction -------------------------------------------------------------------
+// A GEMM with few output tiles and a long contraction (the weight gradient: d_model x d_model
+// outputs, tens of thousands of tokens contracted) leaves most SMs idle.  With caller-provided
+// workspace the contraction is cut into S equal ranges, every (tile, range) pair becomes a work
+// item writing float32 partial sums to its own slice of the workspace, and a second kernel adds
+// the slices in range order (deterministic) and converts to the output type.
+
+template <bool OUT_F32>
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const float* __restrict__ ws, void* __restrict__ d, int M, int N, long long ldd, int S,
+                     long long slice_elems) {
+  const long long quads = (long long)M * (N / 4);
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < quads; i += (long long)gridDim.x * blockDim.x) {
+    const long long m = i / (N / 4);
+    const int n = int(i % (N / 4)) * 4;
+    float4 acc = *reinterpret_cast<const float4*>(ws + m * N + n);
+    for (int sl = 1; sl < S; ++sl) {
+      const float4 v = *reinterpret_cast<const float4*>(ws + sl * slice_elems + m * N + n);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    if (OUT_F32) {
+      *reinterpret_cast<float4*>(static_cast<float*>(d) + m * ldd + n) = acc;
+    } else {
+      *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(d) + m * ldd + n) =
+          make_uint2(pack_bf16x2(acc.x, acc.y), pack_bf16x2(acc.z, acc.w));
+    }
+  }
+}
+
+struct SplitPlan {
+  int S;             // 1 = no split
+  int64_t bytes;     // workspace the split needs
+};
+
+// The smallest S in {1, 2, 4, 8} that fills at least 85 % of the SM slots of the last wave, among
+// those that divide the block count and leave every range at least 8 blocks; else the best of them.
+static SplitPlan plan_split(const tg_gemm_args* a, bool wide) {
+  SplitPlan pl = {1, 0};
+  if (a->K % BK != 0) return pl;
+  const int64_t nkb = a->K / BK;
+  const int64_t tiles = ((a->M + BM - 1) / BM) * ((a->N + (wide ? 256 : 128) - 1) / (wide ? 256 : 128));
+  const int sms = sm_count();
+  if (sms <= 0) return pl;
+  double best = 0.0;
+  for (int S = 1; S <= 8; S *= 2) {
+    if (nkb % S != 0 || nkb / S < 8) break;
+    const int64_t items = tiles * S;
+    const double eff = double(items) / double(((items + sms - 1) / sms) * sms);
+    if (eff > best + 0.02) { best = eff; pl.S = S; }
+    if (eff >= 0.85) break;
+  }
+  if (pl.S > 1) pl.bytes = int64_t(pl.S) * a->M * a->N * int64_t(sizeof(float));
+  return pl;
+}
+
 }  // namespace tg
 
 using namespace tg;
 
-extern "C" int tg_gemm_fp8_blockscaled(const tg_gemm_args* a, void* stream) {
+static int validate_gemm(const tg_gemm_args* a) {
   if (a == nullptr) return TG_ERR_SHAPE;
   if (a->M < 0 || a->N < 0 || a->K < 0) return TG_ERR_SHAPE;
-  if (a->M == 0 || a->N == 0) return TG_OK;
   if (a->M > INT32_MAX || a->N > INT32_MAX || a->K > INT32_MAX) return TG_ERR_TOO_LARGE;
   if ((a->a_major != TG_MAJOR_K && a->a_major != TG_MAJOR_MN) || (a->b_major != TG_MAJOR_K && a->b_major != TG_MAJOR_MN))
     return TG_ERR_SHAPE;
@@ -813,6 +877,17 @@ extern "C" int tg_gemm_fp8_blockscaled(const tg_gemm_args* a, void* stream) {
   const int64_t a_inner = a->a_major == TG_MAJOR_K ? a->K : a->M;
   const int64_t b_inner = a->b_major == TG_MAJOR_K ? a->K : a->N;
   if (a->lda < a_inner || a->ldb < b_inner) return TG_ERR_SHAPE;
+  return TG_OK;
+}
+
+extern "C" int64_t tg_gemm_workspace_bytes(const tg_gemm_args* a) {
+  if (validate_gemm(a) != TG_OK || a->M == 0 || a->N == 0 || a->K == 0) return 0;
+  return plan_split(a, a->N > 128 && a->sb_gran_n != 1).bytes;
+}
+
+extern "C" int tg_gemm_fp8_blockscaled(const tg_gemm_args* a, void* stream) {
+  if (int rc = validate_gemm(a)) return rc;
+  if (a->M == 0 || a->N == 0) return TG_OK;
   if (!aligned16(a->a) || !aligned16(a->b) || !aligned16(a->d)) return TG_ERR_ALIGN;
   if (int rc = check_arch()) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -829,6 +904,8 @@ extern "C" int tg_gemm_fp8_blockscaled(const tg_gemm_args* a, void* stream) {
   p.M = int(a->M); p.N = int(a->N); p.nkb = int((a->K + BK - 1) / BK);
   p.a_mn = a->a_major == TG_MAJOR_MN; p.b_mn = a->b_major == TG_MAJOR_MN;
   p.tiles_m = p.tiles_n = 0;
+  p.ksplit = 1;
+  p.slice_elems = 0;
   p.status = a->status;
   const bool g1 = a->sb_gran_n == 1;
   // 128 x 256 tiles when one scale covers 128 columns.  Per-column scales double the
@@ -842,6 +919,27 @@ extern "C" int tg_gemm_fp8_blockscaled(const tg_gemm_args* a, void* stream) {
   // is longer than one block of tensor work.  Kept behind TG_GEMM_PAIR=1 for the next attempt.
   if (wide && a->M > 128 && getenv("TG_GEMM_PAIR") != nullptr)
     return f32 ? launch_gemm<256, 128, true, true>(a, p, st) : launch_gemm<256, 128, false, true>(a, p, st);
+  const SplitPlan pl = plan_split(a, wide);
+  if (pl.S > 1 && a->workspace != nullptr && a->workspace_bytes >= pl.bytes && aligned16(a->workspace)) {
+    p.ksplit = pl.S;
+    p.nkb /= pl.S;
+    p.slice_elems = a->M * a->N;
+    p.d = a->workspace;
+    p.ldd = a->N;
+    int rc = wide ? launch_gemm<256, 128, true>(a, p, st)
+                  : (g1 ? launch_gemm<128, 1, true>(a, p, st) : launch_gemm<128, 128, true>(a, p, st));
+    if (rc != TG_OK) return rc;
+    const long long quads = a->M * (a->N / 4);
+    const int blocks = int(quads / 256 + 1 < 4096 ? quads / 256 + 1 : 4096);
+    if (f32)
+      splitk_reduce_kernel<true><<<blocks, 256, 0, st>>>(static_cast<const float*>(a->workspace), a->d, int(a->M),
+                                                         int(a->N), a->ldd, pl.S, p.slice_elems);
+    else
+      splitk_reduce_kernel<false><<<blocks, 256, 0, st>>>(static_cast<const float*>(a->workspace), a->d, int(a->M),
+                                                          int(a->N), a->ldd, pl.S, p.slice_elems);
+    TG_CUDA_CHECK(cudaGetLastError());
+    return TG_OK;
+  }
   if (wide) return f32 ? launch_gemm<256, 128, true>(a, p, st) : launch_gemm<256, 128, false>(a, p, st);
   if (g1) return f32 ? launch_gemm<128, 1, true>(a, p, st) : launch_gemm<128, 1, false>(a, p, st);
   return f32 ? launch_gemm<128, 128, true>(a, p, st) : launch_gemm<128, 128, false>(a, p, st);

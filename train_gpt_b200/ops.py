@@ -206,9 +206,11 @@ def new_status(device) -> torch.Tensor:
 
 
 def gemm_blockscaled(a, b, sa, sb, *, M, N, K, a_major, b_major, sa_strides, sb_strides, sb_gran_n,
-                     out_dtype=torch.bfloat16, status=None, out=None):
+                     out_dtype=torch.bfloat16, status=None, out=None, split=True):
     """Raw call of tg_gemm_fp8_blockscaled; see include/train_gpt_b200.h for the argument
-    meaning.  a, b are 2-D e4m3 tensors as stored; strides are in elements."""
+    meaning.  a, b are 2-D e4m3 tensors as stored; strides are in elements.  split=True hands
+    the library the workspace it asks for (tg_gemm_workspace_bytes), so that a problem with few
+    output tiles and a long contraction is cut along the contraction."""
     for t, n in ((a, "a"), (b, "b")):
         if t.dtype != F8 or t.dim() != 2 or t.stride(1) != 1:
             raise TypeError(f"{n} must be a 2-D e4m3 tensor with unit inner stride")
@@ -219,8 +221,15 @@ def gemm_blockscaled(a, b, sa, sb, *, M, N, K, a_major, b_major, sa_strides, sb_
         sa=_ptr(sa), sa_stride_m=sa_strides[0], sa_stride_kb=sa_strides[1],
         sb=_ptr(sb), sb_stride_n=sb_strides[0], sb_stride_kb=sb_strides[1], sb_gran_n=sb_gran_n,
         d=_ptr(out), ldd=out.stride(0), out_dtype=TG_OUT_F32 if out.dtype == torch.float32 else TG_OUT_BF16,
-        M=M, N=N, K=K, status=_ptr(status))
-    _lib.check(_lib.load().tg_gemm_fp8_blockscaled(C.byref(args), _stream()), "tg_gemm_fp8_blockscaled")
+        M=M, N=N, K=K, status=_ptr(status), workspace=0, workspace_bytes=0)
+    lib = _lib.load()
+    ws = None
+    if split:
+        need = lib.tg_gemm_workspace_bytes(C.byref(args))
+        if need > 0:
+            ws = torch.empty((need,), dtype=torch.uint8, device=a.device)
+            args.workspace, args.workspace_bytes = _ptr(ws), need
+    _lib.check(lib.tg_gemm_fp8_blockscaled(C.byref(args), _stream()), "tg_gemm_fp8_blockscaled")
     return out
 
 
