@@ -83,9 +83,10 @@ def _validate(a, b, block_k):
     return K, N
 
 
-def _fp8_forward(a, b, block_k=DEFAULT_BLOCK_K, weight_tile=(128, 1), a_quantized=None):
+def _fp8_forward(a, b, block_k=DEFAULT_BLOCK_K, weight_tile=(128, 1), a_quantized=None, return_weight=False):
     """fp8.py:50-78.  `a_quantized` = (q, scales) of `a` made earlier (e.g. by the fused
-    norm+quantise kernel) skips the activation quantiser."""
+    norm+quantise kernel) skips the activation quantiser.  return_weight=True also returns the
+    quantised weight pair (128x128 tiles serve the backward's dgrad unchanged)."""
     K, N = _validate(a, b, block_k)
     leading = a.shape[:-1]
     if a_quantized is None:
@@ -104,11 +105,13 @@ def _fp8_forward(a, b, block_k=DEFAULT_BLOCK_K, weight_tile=(128, 1), a_quantize
     y = ops.gemm_fwd(a_q, a_s, w_q, w_s, weight_tile)
     if pad:
         y = y[:, :N]
-    return y.reshape(*leading, N)
+    y = y.reshape(*leading, N)
+    return (y, (w_q, w_s)) if return_weight else y
 
 
-def _fp8_backward(block_k, residuals, g, weight_tile=(128, 1), mode="bf16_ste", a_quantized=None):
-    """fp8.py:85-98 (mode "bf16_ste"), or the same two GEMMs in block-scaled e4m3."""
+def _fp8_backward(block_k, residuals, g, weight_tile=(128, 1), mode="bf16_ste", a_quantized=None, w_quantized=None):
+    """fp8.py:85-98 (mode "bf16_ste"), or the same two GEMMs in block-scaled e4m3.
+    `w_quantized`: the forward's 128x128-tile weight pair, reused instead of quantising again."""
     a, b = residuals
     K = a.shape[-1]
     N = b.shape[1]
@@ -131,6 +134,8 @@ def _fp8_backward(block_k, residuals, g, weight_tile=(128, 1), mode="bf16_ste", 
             grad_tile = (128, 128)
         if tuple(weight_tile) == (128, 1):
             w_q, w_s = ops.quantize_rowwise(b_bf)                   # tiles along N, the dgrad contraction
+        elif w_quantized is not None:
+            w_q, w_s = w_quantized
         else:
             w_q, w_s = ops.quantize_block128(b_bf)
         da = ops.gemm_dgrad(g_q, g_s, w_q, w_s, weight_tile)
@@ -152,12 +157,14 @@ class _BlockScaledMatmul(torch.autograd.Function):
         ctx.save_for_backward(a, b)                                 # fp8.py:81-82: unquantised residuals
         ctx.cfg = (block_k, tuple(weight_tile), backward)
         ctx.aq = a_quantized if isinstance(a_quantized, QuantizedActivation) else None
-        return _fp8_forward(a, b, block_k, weight_tile, a_quantized)
+        y, wq = _fp8_forward(a, b, block_k, weight_tile, a_quantized, return_weight=True)
+        ctx.wq = wq if (tuple(weight_tile) == (128, 128) and backward != "bf16_ste") else None
+        return y
 
     @staticmethod
     def backward(ctx, g):
         block_k, weight_tile, mode = ctx.cfg
-        da, db = _fp8_backward(block_k, ctx.saved_tensors, g, weight_tile, mode, ctx.aq)
+        da, db = _fp8_backward(block_k, ctx.saved_tensors, g, weight_tile, mode, ctx.aq, ctx.wq)
         return da, db, None, None, None, None
 
 

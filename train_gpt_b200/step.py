@@ -67,11 +67,14 @@ class _NormQuant(torch.autograd.Function):
         ctx.save_for_backward(x, gamma)
         ctx.eps = eps
         ctx.mark_non_differentiable(q, s)
+        ctx.set_materialize_grads(False)        # no zero-filled "gradients" for the quantised pair
         return y, q, s
 
     @staticmethod
     def backward(ctx, gy, _gq, _gs):
         x, gamma = ctx.saved_tensors
+        if gy is None:
+            return None, None, None
         dx, dgamma = ops.rmsnorm_bwd(x, gamma, gy.contiguous(), ctx.eps)
         return dx, dgamma, None
 
