@@ -81,6 +81,24 @@ def bench_quant(rows, cols, warmup, iters):
     _report("quantize_colwise", m, b, bytes_=3.03125 * E, shape=[rows, cols])
     m, b = _time(lambda i: ops.quantize_block128(xs[i]), n, warmup, iters, batch=10)
     _report("quantize_block128", m, b, bytes_=(3.0 + 4.0 / 16384) * E, shape=[rows, cols])
+    m, b = _time(lambda i: ops.quantize_rowcol(xs[i]), n, warmup, iters, batch=10)
+    _report("quantize_rowcol", m, b, bytes_=(2.0 + 2 * 1.03125) * E, shape=[rows, cols])
+
+
+def bench_loss(rows, vocab, warmup, iters):
+    """Capped-logit cross-entropy: forward reads the logits and writes the tanh values (4 B per
+    element), backward rewrites them as the gradient in place (4 B per element)."""
+    E = rows * vocab
+    g = torch.Generator(device="cuda").manual_seed(0)
+    xs = [(torch.randn(rows, vocab, device="cuda", generator=g) * 4).to(torch.bfloat16) for _ in range(2)]
+    tg = torch.randint(0, vocab, (rows,), device="cuda", generator=g).to(torch.int32)
+    m, b = _time(lambda i: ops.softcap_ce_fwd(xs[i], tg, 15.0), 2, warmup, iters)
+    _report("softcap_ce_fwd", m, b, bytes_=4.0 * E + 12 * rows, shape=[rows, vocab])
+    _, lse, th = ops.softcap_ce_fwd(xs[0], tg, 15.0)
+    ths = [th, th.clone()]
+    # timing the in-place form would feed gradients back in as tanh values: time the out-of-place form
+    m, b = _time(lambda i: ops.softcap_ce_bwd(ths[i], tg, lse, None, 15.0), 2, warmup, iters)
+    _report("softcap_ce_bwd", m, b, bytes_=4.0 * E + 8 * rows, shape=[rows, vocab])
 
 
 def bench_norm(rows, cols, warmup, iters):
@@ -136,7 +154,8 @@ def _gemm_case(M, N, K, mode, tile, warmup, iters, student_t=False):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["quant", "norm", "gemm", "sweep"])
+    ap.add_argument("what", choices=["quant", "norm", "gemm", "loss", "sweep"])
+    ap.add_argument("--vocab", type=int, default=50304)
     ap.add_argument("--rows", type=int, default=32768)
     ap.add_argument("--cols", type=int, default=2048)
     ap.add_argument("--m", type=int, default=32768)
@@ -152,6 +171,8 @@ def main():
         bench_quant(a.rows, a.cols, a.warmup, a.iters)
     elif a.what == "norm":
         bench_norm(a.rows, a.cols, a.warmup, a.iters)
+    elif a.what == "loss":
+        bench_loss(a.rows, a.vocab, a.warmup, a.iters)
     elif a.what == "gemm":
         for mode in (["fwd", "dgrad", "wgrad"] if a.mode == "all" else [a.mode]):
             _gemm_case(a.m, a.n, a.k, mode, tile, a.warmup, a.iters)
