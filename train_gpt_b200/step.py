@@ -307,3 +307,41 @@ def bench_train_step(world: int, rank: int, device, dist, steps: int = 5, warmup
                    "mm": cfg.mm, "norm": cfg.norm, "optimizer": "AdamW lr 3e-4", "parallelism": f"dp{world}", "cuda_graph": bool(graph),
                    "grad_bytes_allreduced": tr.buckets.bytes(), "data": "tokens uniform over the vocabulary (seeded)"},
     }
+
+
+def kernel_breakdown(steps: int = 2, batch_per_gpu: int = 32, cfg: StepConfig = StepConfig(), top: int = 40):
+    """Device time per kernel of the (eager) training step on cuda:0, from torch's profiler.
+    Prints one line per kernel: ms per step, launches per step, name."""
+    from torch.autograd import DeviceType
+    from torch.profiler import ProfilerActivity, profile
+    dev = torch.device("cuda", 0)
+    tr = Trainer(cfg, dev)
+    batch = synthetic_batch(cfg, batch_per_gpu, dev, seed=1)
+    for _ in range(3):
+        tr.step(*batch)
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(steps):
+            tr.step(*batch)
+        torch.cuda.synchronize()
+    ev = sorted((e for e in prof.key_averages() if e.device_type == DeviceType.CUDA),
+                key=lambda e: -e.self_device_time_total)
+    total = sum(e.self_device_time_total for e in ev) / steps / 1e3
+    print(f"device time per step: {total:.2f} ms  ({len(ev)} distinct kernels)")
+    for e in ev[:top]:
+        ms = e.self_device_time_total / steps / 1e3
+        print(f"{ms:8.2f} ms {100 * ms / total:5.1f} % {e.count // steps:5d}  {e.key[:120]}")
+
+
+if __name__ == "__main__":
+    import argparse
+    ap = argparse.ArgumentParser(description="Training step of BASELINE configuration 3 on one GPU")
+    ap.add_argument("--kernel-breakdown", action="store_true", help="device time per kernel (torch profiler)")
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--no-graph", action="store_true")
+    a = ap.parse_args()
+    if a.kernel_breakdown:
+        kernel_breakdown(steps=min(a.steps, 2))
+    else:
+        import json
+        print(json.dumps(bench_train_step(1, 0, torch.device("cuda", 0), None, steps=a.steps, graph=not a.no_graph)))
