@@ -276,10 +276,22 @@ def bench_train_step(world: int, rank: int, device, dist, steps: int = 5, warmup
                      cfg: StepConfig = StepConfig(), graph: bool = True):
     """Tokens/s of the data-parallel step (BASELINE configuration 3): batch sharded by rank,
     weights replicated, gradients all-reduced per layer bucket over NCCL."""
-    tr = Trainer(cfg, device, world_size=world, graph=graph)
     batches = [synthetic_batch(cfg, batch_per_gpu, device, seed=1000 * rank + i) for i in range(2)]
-    for i in range(warmup):
-        loss, _ = tr.step(*batches[i % 2])
+    graph_error = None
+    tr = Trainer(cfg, device, world_size=world, graph=graph)
+    try:
+        for i in range(warmup):
+            loss, _ = tr.step(*batches[i % 2])
+    except RuntimeError as e:
+        if not graph:
+            raise
+        # capture refused (e.g. by a collective): time the eager step instead and say so
+        graph_error, graph = str(e).splitlines()[0][:200], False
+        del tr
+        torch.cuda.synchronize()
+        tr = Trainer(cfg, device, world_size=world, graph=False)
+        for i in range(warmup):
+            loss, _ = tr.step(*batches[i % 2])
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
@@ -304,7 +316,7 @@ def bench_train_step(world: int, rank: int, device, dist, steps: int = 5, warmup
         "mfu_flops_per_s": step_flops(cfg, tokens) / sec,
         "config": {"layers": cfg.n_layers, "d_model": cfg.d_model, "heads": cfg.n_heads, "d_ff": cfg.d_ff,
                    "vocab": cfg.vocab_size, "seq": cfg.seq_len, "batch_per_gpu": batch_per_gpu, "activation": cfg.activation,
-                   "mm": cfg.mm, "norm": cfg.norm, "optimizer": "AdamW lr 3e-4", "parallelism": f"dp{world}", "cuda_graph": bool(graph),
+                   "mm": cfg.mm, "norm": cfg.norm, "optimizer": "AdamW lr 3e-4", "parallelism": f"dp{world}", "cuda_graph": bool(graph), "cuda_graph_error": graph_error,
                    "grad_bytes_allreduced": tr.buckets.bytes(), "data": "tokens uniform over the vocabulary (seeded)"},
     }
 
