@@ -50,8 +50,6 @@ constexpr int kTmemCols = 512;
 constexpr int kTileBytes = 128 * 128;            // one operand TMA box: 128 rows x 128 bytes
 constexpr int kIssuers = 1;                      // MMA-issuing warps
 constexpr int kFirstPromoWarp = 1 + kIssuers;    // 2
-constexpr int kPromoWarps = 16;
-constexpr int kGemmThreads = 32 * (kFirstPromoWarp + kPromoWarps);  // 576: 112 registers per thread
 constexpr int kSmemLimit = 227 * 1024;
 constexpr long long kWaitLimitCycles = 4000000000LL;  // ~2 s at 2 GHz
 
@@ -59,9 +57,14 @@ constexpr long long kWaitLimitCycles = 4000000000LL;  // ~2 s at 2 GHz
 template <int BN_, int SB_GRAN, bool OUT_F32, bool CTA2>
 struct Cfg {
   static constexpr int BN = BN_;
-  static constexpr int tmem_bufs = kTmemCols / BN;            // 2 or 4
-  static constexpr int cols_per_warp = BN / 4;                // 64 or 32
-  static constexpr int b_boxes = CTA2 ? 1 : BN / 128;         // a CTA of a pair loads half of B
+  // 192-column tiles run 12 promotion warps (14 warps in all: 128 registers per thread instead
+  // of the 96 an 18-warp CTA gets), the others 16
+  static constexpr int promo_warps = BN == 192 ? 12 : 16;
+  static constexpr int threads = 32 * (kFirstPromoWarp + promo_warps);
+  static constexpr int tmem_bufs = BN > 128 ? 2 : 4;
+  static constexpr int tmem_stride = kTmemCols / tmem_bufs;   // columns between accumulator buffers
+  static constexpr int cols_per_warp = BN / (promo_warps / 4);  // 64 or 32
+  static constexpr int b_boxes = CTA2 ? 1 : (BN + 127) / 128; // a CTA of a pair loads half of B
   static constexpr int stage_bytes = kTileBytes * (1 + b_boxes);
   static constexpr int esize = OUT_F32 ? 4 : 2;
   // epilogue: a warp stages its 32 rows x `phase_cols` columns at a time (rows of <= 128
@@ -72,8 +75,8 @@ struct Cfg {
   static constexpr int phases = row_bytes / phase_row_bytes;
   static constexpr int phase_cols = phase_row_bytes / esize;
   static constexpr int warp_out_bytes = 32 * phase_row_bytes;
-  static constexpr int out_bytes = kPromoWarps * warp_out_bytes;
-  static constexpr int sb_bytes = SB_GRAN == 1 ? kPromoWarps * 2 * cols_per_warp * 4 : 0;  // float[warps][2][cols_per_warp]
+  static constexpr int out_bytes = promo_warps * warp_out_bytes;
+  static constexpr int sb_bytes = SB_GRAN == 1 ? promo_warps * 2 * cols_per_warp * 4 : 0;  // float[warps][2][cols_per_warp]
   static constexpr int misc_bytes = 512;                      // barriers, TMEM pointer, abort flag
   static constexpr int stages_fit = (kSmemLimit - 1024 - out_bytes - sb_bytes - misc_bytes) / stage_bytes;
   static constexpr int stages = stages_fit > 6 ? 6 : stages_fit;
@@ -367,11 +370,12 @@ __device__ __forceinline__ void promote(float2* acc, const uint32_t (&v)[NC], co
 }
 
 template <int BN_, int SB_GRAN, bool OUT_F32, bool CTA2>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__((Cfg<BN_, SB_GRAN, OUT_F32, CTA2>::threads), 1)
 gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
                             const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
   using C = Cfg<BN_, SB_GRAN, OUT_F32, CTA2>;
   constexpr int BN = C::BN, kStages = C::stages, kTmemBufs = C::tmem_bufs, kCols = C::cols_per_warp;
+  constexpr int kPromoWarps = C::promo_warps;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t sbase = smem_u32(smem);
@@ -498,7 +502,7 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
                      mbar_test(full_bar(nx % kStages), (nx / kStages) & 1u);
         const uint64_t a_desc = a_desc0 + uint64_t((s * C::stage_bytes) >> 4);
         const uint64_t b_desc = b_desc0 + uint64_t((s * C::stage_bytes) >> 4);
-        const uint32_t d_tmem = tmem_base + uint32_t(buf * BN);
+        const uint32_t d_tmem = tmem_base + uint32_t(buf * C::tmem_stride);
         if (CTA2) {
           if (elect_one()) {
 #pragma unroll
@@ -611,9 +615,22 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (ok) ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar(tb), (it / kTmemBufs) & 1u, abort_flag, p.status, 5u));
         if (!ok) continue;
         tc_fence_after();
-        const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(buf * BN + c0);
+        const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(buf * C::tmem_stride + c0);
         const float s_scalar = sa_v * sb_v.x;
-        if (kCols > 32) {
+        if (kCols > 32 && kPromoWarps == 12 && SB_GRAN != 1) {
+          // 64 columns in two 32-column loads (128 registers per thread make room): one TMEM round
+          // trip and 16 packed FMAs stand between the barrier and the buffer's release, not three
+          uint32_t v[32];
+          tmem_ld32(taddr, v);
+          tmem_wait_ld(v);
+          promote<SB_GRAN, 32>(acc, v, stage, sa_v, s_scalar);
+          tmem_ld32(taddr + 32, v);
+          tmem_wait_ld(v);
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(tempty_bar(tb));
+          promote<SB_GRAN, 32>(acc + 16, v, stage + 32, sa_v, s_scalar);
+        } else if (kCols > 32) {
           // 64 columns in four 16-column pieces; the buffer goes back after the last load lands
           uint32_t v[16];
 #pragma unroll
@@ -769,7 +786,7 @@ static int launch_gemm(const tg_gemm_args* a, GemmParams p, cudaStream_t st) {
     if (max_pairs[dev] == 0) {
       cudaLaunchConfig_t q = {};
       q.gridDim = dim3(2 * (sms / 2));
-      q.blockDim = dim3(kGemmThreads);
+      q.blockDim = dim3(C::threads);
       q.dynamicSmemBytes = C::smem_bytes;
       cudaLaunchAttribute qa[1];
       qa[0].id = cudaLaunchAttributeClusterDimension;
@@ -787,7 +804,7 @@ static int launch_gemm(const tg_gemm_args* a, GemmParams p, cudaStream_t st) {
     grid = 2 * int(n_tiles < pairs ? n_tiles : pairs);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(kGemmThreads);
+    cfg.blockDim = dim3(C::threads);
     cfg.dynamicSmemBytes = C::smem_bytes;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
@@ -799,7 +816,7 @@ static int launch_gemm(const tg_gemm_args* a, GemmParams p, cudaStream_t st) {
     cfg.numAttrs = 1;
     TG_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, ta, tb, p));
   } else {
-    kern<<<grid, kGemmThreads, C::smem_bytes, st>>>(ta, tb, p);
+    kern<<<grid, C::threads, C::smem_bytes, st>>>(ta, tb, p);
   }
   TG_CUDA_CHECK(cudaGetLastError());
   return TG_OK;
@@ -841,11 +858,11 @@ struct SplitPlan {
 
 // The smallest S in {1, 2, 4, 8} that fills at least 85 % of the SM slots of the last wave, among
 // those that divide the block count and leave every range at least 8 blocks; else the best of them.
-static SplitPlan plan_split(const tg_gemm_args* a, bool wide) {
+static SplitPlan plan_split(const tg_gemm_args* a, int bn) {
   SplitPlan pl = {1, 0};
   if (a->K % BK != 0) return pl;
   const int64_t nkb = a->K / BK;
-  const int64_t tiles = ((a->M + BM - 1) / BM) * ((a->N + (wide ? 256 : 128) - 1) / (wide ? 256 : 128));
+  const int64_t tiles = ((a->M + BM - 1) / BM) * ((a->N + bn - 1) / bn);
   const int sms = sm_count();
   if (sms <= 0) return pl;
   double best = 0.0;
@@ -863,6 +880,19 @@ static SplitPlan plan_split(const tg_gemm_args* a, bool wide) {
 }  // namespace tg
 
 using namespace tg;
+
+// Tile width of a problem.  One scale per 128 columns: 128 x 256 tiles, 16 promotion warps
+// (measured 1.70 / 1.92 PFLOP/s forward / dgrad against 1.53 / 1.59 for 128 x 192).  A scale per
+// column (the weight gradient): 128 x 192 tiles with 12 promotion warps, whose 128 registers per
+// thread hold the 64 accumulator columns plus the scale staging that 96 do not (1.04 PFLOP/s
+// against 0.85 for 128 x 128).  TG_GEMM_BN=128|192|256 overrides, for measurements.
+static int tile_width(const tg_gemm_args* a) {
+  if (a->N <= 128) return 128;
+  const char* e = getenv("TG_GEMM_BN");
+  const int want = e != nullptr ? atoi(e) : 0;
+  if (a->sb_gran_n == 1) return want == 128 ? 128 : 192;
+  return want == 192 ? 192 : (want == 128 ? 128 : 256);
+}
 
 static int validate_gemm(const tg_gemm_args* a) {
   if (a == nullptr) return TG_ERR_SHAPE;
@@ -882,7 +912,7 @@ static int validate_gemm(const tg_gemm_args* a) {
 
 extern "C" int64_t tg_gemm_workspace_bytes(const tg_gemm_args* a) {
   if (validate_gemm(a) != TG_OK || a->M == 0 || a->N == 0 || a->K == 0) return 0;
-  return plan_split(a, a->N > 128 && a->sb_gran_n != 1).bytes;
+  return plan_split(a, tile_width(a)).bytes;
 }
 
 extern "C" int tg_gemm_fp8_blockscaled(const tg_gemm_args* a, void* stream) {
@@ -908,26 +938,25 @@ extern "C" int tg_gemm_fp8_blockscaled(const tg_gemm_args* a, void* stream) {
   p.slice_elems = 0;
   p.status = a->status;
   const bool g1 = a->sb_gran_n == 1;
-  // 128 x 256 tiles when one scale covers 128 columns.  Per-column scales double the
-  // promotion arithmetic and 64 accumulator columns per thread plus their staging do not
-  // fit the 96 registers an 18-warp CTA gets (measured: 2x slower with the spills), so that
-  // case keeps 128 x 128 tiles.
-  const bool wide = a->N > 128 && !g1;
+  const int bn = tile_width(a);
+  const bool wide = bn == 256;
   // CTA pairs (cta_group::2, 256 x 256 tiles, half the B bytes per CTA) are built and pass the
   // parity tests, but measure SLOWER than one CTA per tile (1.03 vs 1.70 PFLOP/s forward): with
   // only two 256-column TMEM buffers the barrier round trip through both CTAs' promotion warps
   // is longer than one block of tensor work.  Kept behind TG_GEMM_PAIR=1 for the next attempt.
-  if (wide && a->M > 128 && getenv("TG_GEMM_PAIR") != nullptr)
+  if (!g1 && a->N > 128 && a->M > 128 && getenv("TG_GEMM_PAIR") != nullptr)
     return f32 ? launch_gemm<256, 128, true, true>(a, p, st) : launch_gemm<256, 128, false, true>(a, p, st);
-  const SplitPlan pl = plan_split(a, wide);
+  const SplitPlan pl = plan_split(a, bn);
   if (pl.S > 1 && a->workspace != nullptr && a->workspace_bytes >= pl.bytes && aligned16(a->workspace)) {
     p.ksplit = pl.S;
     p.nkb /= pl.S;
     p.slice_elems = a->M * a->N;
     p.d = a->workspace;
     p.ldd = a->N;
-    int rc = wide ? launch_gemm<256, 128, true>(a, p, st)
-                  : (g1 ? launch_gemm<128, 1, true>(a, p, st) : launch_gemm<128, 128, true>(a, p, st));
+    int rc;
+    if (bn == 256) rc = launch_gemm<256, 128, true>(a, p, st);
+    else if (bn == 192) rc = g1 ? launch_gemm<192, 1, true>(a, p, st) : launch_gemm<192, 128, true>(a, p, st);
+    else rc = g1 ? launch_gemm<128, 1, true>(a, p, st) : launch_gemm<128, 128, true>(a, p, st);
     if (rc != TG_OK) return rc;
     const long long quads = a->M * (a->N / 4);
     const int blocks = int(quads / 256 + 1 < 4096 ? quads / 256 + 1 : 4096);
@@ -941,6 +970,8 @@ extern "C" int tg_gemm_fp8_blockscaled(const tg_gemm_args* a, void* stream) {
     return TG_OK;
   }
   if (wide) return f32 ? launch_gemm<256, 128, true>(a, p, st) : launch_gemm<256, 128, false>(a, p, st);
+  if (bn == 192 && g1) return f32 ? launch_gemm<192, 1, true>(a, p, st) : launch_gemm<192, 1, false>(a, p, st);
+  if (bn == 192) return f32 ? launch_gemm<192, 128, true>(a, p, st) : launch_gemm<192, 128, false>(a, p, st);
   if (g1) return f32 ? launch_gemm<128, 1, true>(a, p, st) : launch_gemm<128, 1, false>(a, p, st);
   return f32 ? launch_gemm<128, 128, true>(a, p, st) : launch_gemm<128, 128, false>(a, p, st);
 }
