@@ -170,6 +170,24 @@ int tg_softcap_ce_bwd(const void* tanh_in, const int32_t* targets, const float* 
                       float cap, void* dlogits, int64_t rows, int64_t vocab, int64_t ld_tanh, int64_t ld_d,
                       void* stream);
 
+/* ---- optimiser step --------------------------------------------------------------- */
+
+/* Sum of squares of n bf16 values into out[0] (float32): one term of optax.global_norm
+ * (train-gpt train.py:132).  scratch: tg_sumsq_scratch_bytes() bytes, caller-owned.  Block
+ * partials are added in index order, so the result does not depend on scheduling.       */
+int64_t tg_sumsq_scratch_bytes(void);
+int tg_sumsq_bf16(const void* x, int64_t n, float* out, void* scratch, void* stream);
+
+/* One step of optax.chain(clip_by_global_norm, adamw) (train-gpt train.py:120-123,133-134) on n
+ * bf16 parameters with bf16 moments, in place:
+ *   g' = bf16(g * gscale);  m = bf16(b1 m + (1-b1) g');  v = bf16(b2 v + (1-b2) g'^2);
+ *   p = bf16(p - lr * ((m / (1 - b1^t)) / (sqrt(v / (1 - b2^t)) + eps) + weight_decay * p)).
+ *   step   device int32: t, the number of this step (1 for the first); a device word so that a
+ *          captured CUDA graph can be replayed with a counter the caller increments
+ *   gscale device float32 clip factor min(1, clip / global_norm), or NULL for 1           */
+int tg_adamw_bf16(void* p, const void* g, void* m, void* v, int64_t n, float lr, float b1, float b2,
+                  float eps, float weight_decay, const int32_t* step, const float* gscale, void* stream);
+
 /* ---- block-scaled FP8 GEMM -------------------------------------------------------- */
 
 /* Operand storage, seen from the GEMM  D[m,n] = sum_k A[m,k] * B[n,k]. */

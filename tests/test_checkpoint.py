@@ -11,7 +11,7 @@ from train_gpt_b200.step import GPT, SMALL, StepConfig
 
 
 def _cfg():
-    return StepConfig(**SMALL, mm="bf16", norm="torch_reference", loss="torch")
+    return StepConfig(**SMALL, mm="bf16", norm="torch_reference", loss="torch", optimizer="torch")
 
 
 def test_round_trip_keeps_every_bit(tmp_path):

@@ -23,7 +23,7 @@ def _free_port():
 
 def _cfg():
     from train_gpt_b200.step import SMALL, StepConfig
-    return StepConfig(**SMALL, mm="bf16", norm="torch_reference", loss="torch", activation="relu2")
+    return StepConfig(**SMALL, mm="bf16", norm="torch_reference", loss="torch", optimizer="torch", activation="relu2")
 
 
 def _worker(rank, world, port, out_dir):

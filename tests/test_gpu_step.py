@@ -14,7 +14,8 @@ pytestmark = pytest.mark.gpu
 def _run(mm, norm, steps, activation="gelu", graph=False):
     from train_gpt_b200.step import StepConfig, Trainer, synthetic_batch
     cfg = StepConfig(vocab_size=512, seq_len=128, d_model=256, n_layers=2, n_heads=4, head_dim=64, d_ff=1024,
-                     mm=mm, norm=norm, loss="torch" if mm == "bf16" else "fused", activation=activation, lr=1e-3)
+                     mm=mm, norm=norm, loss="torch" if mm == "bf16" else "fused",
+                     optimizer="torch" if mm == "bf16" else "fused", activation=activation, lr=1e-3)
     tr = Trainer(cfg, torch.device("cuda", 0), world_size=1, seed=0, graph=graph)
     losses, gnorms = [], []
     for i in range(steps):

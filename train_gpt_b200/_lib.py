@@ -50,6 +50,9 @@ SYMBOLS = {
     "tg_rmsnorm_bwd_static": (_i, [_p, _p, _p, _f, _p, _p, _i64, _i64, _p]),
     "tg_softcap_ce_fwd": (_i, [_p, _p, _f, _p, _p, _p, _i64, _i64, _i64, _i64, _p]),
     "tg_softcap_ce_bwd": (_i, [_p, _p, _p, _p, _f, _p, _i64, _i64, _i64, _i64, _p]),
+    "tg_sumsq_scratch_bytes": (_i64, []),
+    "tg_sumsq_bf16": (_i, [_p, _i64, _p, _p, _p]),
+    "tg_adamw_bf16": (_i, [_p, _p, _p, _p, _i64, _f, _f, _f, _f, _f, _p, _p, _p]),
     "tg_gemm_workspace_bytes": (_i64, [C.POINTER(GemmArgs)]),
     "tg_gemm_fp8_blockscaled": (_i, [C.POINTER(GemmArgs), _p]),
 }

@@ -17,7 +17,7 @@ CSRC = os.path.join(PKG_DIR, "csrc")
 INCLUDE = os.path.join(os.path.dirname(PKG_DIR), "include")
 LIB_PATH = os.path.join(PKG_DIR, "libtrain_gpt_b200.so")
 
-SOURCES = ["runtime.cu", "quantize.cu", "rmsnorm.cu", "gemm_fp8.cu", "selftest.cu", "loss.cu"]
+SOURCES = ["runtime.cu", "quantize.cu", "rmsnorm.cu", "gemm_fp8.cu", "selftest.cu", "loss.cu", "optim.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -198,6 +198,35 @@ def softcap_ce_bwd(th, targets, lse, gscale, cap: float, in_place: bool = False)
     return d
 
 
+# ---- optimiser ------------------------------------------------------------------------------
+
+def sumsq(x, out=None, scratch=None):
+    """Sum of squares of a bf16 tensor as a float32 device scalar (one term of optax.global_norm)."""
+    x = _need(x, torch.bfloat16, "x")
+    lib = _lib.load()
+    if out is None:
+        out = torch.empty((1,), dtype=torch.float32, device=x.device)
+    if scratch is None:
+        scratch = torch.empty((lib.tg_sumsq_scratch_bytes(),), dtype=torch.uint8, device=x.device)
+    _lib.check(lib.tg_sumsq_bf16(_ptr(x), x.numel(), _ptr(out), _ptr(scratch), _stream()), "tg_sumsq_bf16")
+    return out
+
+
+def adamw_step(p, g, m, v, step, lr, b1=0.9, b2=0.999, eps=1e-8, weight_decay=0.0, gscale=None):
+    """optax clip + adamw on one bf16 parameter tensor, in place (p, m, v).  `step` is an int32
+    device scalar holding t (1 for the first step); `gscale` a float32 device scalar or None."""
+    for t, n in ((p, "p"), (g, "g"), (m, "m"), (v, "v")):
+        if not t.is_cuda or t.dtype != torch.bfloat16 or not t.is_contiguous():
+            raise TypeError(f"{n} must be a contiguous bf16 CUDA tensor")
+    if not (p.numel() == g.numel() == m.numel() == v.numel()):
+        raise ValueError("p, g, m, v sizes differ")
+    if step.dtype != torch.int32 or not step.is_cuda:
+        raise TypeError("step must be an int32 CUDA scalar")
+    _lib.check(_lib.load().tg_adamw_bf16(_ptr(p), _ptr(g), _ptr(m), _ptr(v), p.numel(), float(lr), float(b1), float(b2),
+                                         float(eps), float(weight_decay), _ptr(step), _ptr(gscale), _stream()),
+               "tg_adamw_bf16")
+
+
 # ---- GEMM ---------------------------------------------------------------------------------
 
 def new_status(device) -> torch.Tensor:

@@ -29,7 +29,7 @@ from dataclasses import dataclass
 import torch
 import torch.nn.functional as F
 
-from . import fp8, kernels, losses, ops
+from . import fp8, kernels, losses, ops, optim
 from .dp import GradBuckets
 
 
@@ -49,6 +49,7 @@ class StepConfig:
     mm: str = "fp8"
     norm: str = "fused"
     loss: str = "fused"             # "fused": one CUDA pass each way over the logits; "torch": op by op (CPU tests)
+    optimizer: str = "fused"        # "fused": optim.ClippedAdamW (CUDA kernels); "torch": torch.optim.AdamW + tensor-op clip
     lr: float = 3e-4
     weight_decay: float = 0.1       # train.py make_optimizer default use
     clip_norm: float = 1.0
@@ -191,14 +192,23 @@ class Trainer:
         on_gpu = torch.device(device).type == "cuda"
         self._want_graph = bool(graph) and on_gpu
         self._graph = None
-        self.opt = torch.optim.AdamW(self.model.parameters(), lr=cfg.lr, weight_decay=cfg.weight_decay,
-                                     betas=(0.9, 0.999), eps=1e-8, fused=on_gpu, capturable=self._want_graph)
+        self._fused_opt = cfg.optimizer == "fused"
+        if self._fused_opt:
+            self.opt = optim.ClippedAdamW(self.model.parameters(), lr=cfg.lr, weight_decay=cfg.weight_decay,
+                                          clip_norm=cfg.clip_norm)
+        else:
+            self.opt = torch.optim.AdamW(self.model.parameters(), lr=cfg.lr, weight_decay=cfg.weight_decay,
+                                         betas=(0.9, 0.999), eps=1e-8, fused=on_gpu, capturable=self._want_graph)
 
     def _eager_step(self, ids, targets):
         self.buckets.zero()
         loss = self.model.loss(ids, targets)
         loss.backward()
         self.buckets.finish()
+        if self._fused_opt:
+            gnorm = self.opt.global_norm(self.buckets.flat)                          # train.py:132
+            self.opt.step(gnorm)                                                     # train.py:133-134
+            return loss.detach(), gnorm
         gnorm = self.buckets.global_norm()                                           # train.py:132
         scale = torch.clamp(self.cfg.clip_norm / (gnorm + 1e-6), max=1.0)            # optax.clip_by_global_norm
         for f in self.buckets.flat:
@@ -208,6 +218,8 @@ class Trainer:
         return loss.detach(), gnorm
 
     def _opt_state_tensors(self):
+        if self._fused_opt:
+            return self.opt.state_tensors()
         return [t for st in self.opt.state.values() for t in st.values() if torch.is_tensor(t)]
 
     def _capture(self, ids, targets):
