@@ -339,6 +339,12 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
   return d;
 }
 
+__device__ __forceinline__ float ldg_f32(const float* ptr) {
+  float v;
+  asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(ptr));
+  return v;
+}
+
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
 }
@@ -484,22 +490,18 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
       for (int item = first_tile; item < n_items; item += tile_step) ++my_tiles;
       const uint32_t total = uint32_t(my_tiles) * uint32_t(p.nkb);
       bool ok = true;
-      bool ready = false;  // barriers of block `it` already seen complete by an early probe
+      // One barrier operation costs ~150 cycles even when the barrier is already complete (measured
+      // with clock64 stamps: two waits plus two look-ahead probes per block made this loop ~1040
+      // cycles long against 512 of tensor work per block).  So the loop does ONE wait instruction per
+      // block: lanes 0-15 poll the accumulator buffer's barrier, lanes 16-31 the stage's.
+      const bool stage_lane = lane >= 16;
       for (uint32_t it = issuer; ok && it < total; it += kIssuers) {
         const int s = it % kStages, buf = it % kTmemBufs;
-        const uint32_t tpar = ((it / kTmemBufs) & 1u) ^ 1u;
-        if (!ready) {
-          ok = __all_sync(0xffffffffu, mbar_wait(tempty_bar(buf * kHalves), tpar, abort_flag, p.status, 2u) &&
-                                           mbar_wait(full_bar(s), (it / kStages) & 1u, abort_flag, p.status, 3u));
-          if (!ok) break;
-        }
+        const uint32_t bar = stage_lane ? full_bar(s) : tempty_bar(buf * kHalves);
+        const uint32_t par = stage_lane ? ((it / kStages) & 1u) : (((it / kTmemBufs) & 1u) ^ 1u);
+        ok = __all_sync(0xffffffffu, mbar_wait(bar, par, abort_flag, p.status, stage_lane ? 3u : 2u));
+        if (!ok) break;
         tc_fence_after();
-        // probe the next block's barriers now; the answers are read after this block is issued
-        const uint32_t nx = it + kIssuers;
-        bool nx_ready = false;
-        if (nx < total)
-          nx_ready = mbar_test(tempty_bar((nx % kTmemBufs) * kHalves), ((nx / kTmemBufs) & 1u) ^ 1u) &
-                     mbar_test(full_bar(nx % kStages), (nx / kStages) & 1u);
         const uint64_t a_desc = a_desc0 + uint64_t((s * C::stage_bytes) >> 4);
         const uint64_t b_desc = b_desc0 + uint64_t((s * C::stage_bytes) >> 4);
         const uint32_t d_tmem = tmem_base + uint32_t(buf * C::tmem_stride);
@@ -521,7 +523,6 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
         }
         __syncwarp();
-        ready = __all_sync(0xffffffffu, nx_ready);
       }
       // make sure nothing issued here is still running when TMEM is freed
       if (elect_one()) {
@@ -551,16 +552,25 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
     bool m_ok = false, sb_ok = false;
     const float* sa_ptr = p.sa;
     const float* sb_ptr = p.sb;
-    float sa_next = 0.f;
-    float2 sb_next = make_float2(0.f, 0.f);
+    // The scales of block k+1 are loaded at the top of block k's iteration, by volatile asm so
+    // that the compiler cannot sink the loads to their use: with ordinary loads it did, and clock64
+    // stamps showed ~450 cycles of exposed L2 latency per block in these warps.  (Two blocks ahead
+    // costs three more registers, which the 96-register variants do not have: measured slower.)
+    float sa_q0 = 0.f;
+    float2 sb_q0 = make_float2(0.f, 0.f);
     // per-column scales: lane j stages column c0 + j (32-column warps) or the pair c0 + 2j, c0 + 2j + 1
     constexpr int kPerLane = kCols / 32;
-    auto load_sb = [&](long long kb) {
+    auto load_sa = [&](int kb) {
+      float v = 0.f;
+      if (m_ok && kb < p.nkb) v = ldg_f32(sa_ptr + (long long)kb * p.sa_sk);
+      return v;
+    };
+    auto load_sb = [&](int kb) {
       float2 v = make_float2(0.f, 0.f);
-      if (sb_ok) {
-        const float* q = sb_ptr + kb * p.sb_sk;
-        v.x = __ldg(q);
-        if (SB_GRAN == 1 && kPerLane == 2) v.y = __ldg(q + p.sb_sn);
+      if (sb_ok && kb < p.nkb) {
+        const float* q = sb_ptr + (long long)kb * p.sb_sk;
+        v.x = ldg_f32(q);
+        if (SB_GRAN == 1 && kPerLane == 2) v.y = ldg_f32(q + p.sb_sn);
       }
       return v;
     };
@@ -583,8 +593,8 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
         sb_ok = true;
         sb_ptr = p.sb + (long long)((nblk * 128 < p.N) ? nblk : 0) * p.sb_sn + kb_off * p.sb_sk;
       }
-      sa_next = m_ok ? __ldg(sa_ptr) : 0.f;
-      sb_next = load_sb(0);
+      sa_q0 = load_sa(0);
+      sb_q0 = load_sb(0);
     };
 
     if (first_tile < n_items) open_tile(first_tile);
@@ -598,12 +608,10 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
       for (int kb = 0; kb < p.nkb; ++kb, ++it) {
         const int buf = it % kTmemBufs;
-        const float sa_v = sa_next;
-        const float2 sb_v = sb_next;
-        if (kb + 1 < p.nkb) {
-          sa_next = m_ok ? __ldg(sa_ptr + (long long)(kb + 1) * p.sa_sk) : 0.f;
-          sb_next = load_sb(kb + 1);
-        }
+        const float sa_v = sa_q0;
+        const float2 sb_v = sb_q0;
+        sa_q0 = load_sa(kb + 1);
+        sb_q0 = load_sb(kb + 1);
         float* stage = sb_stage + (it & 1u) * kCols;
         if (SB_GRAN == 1) {
           if (kPerLane == 2) *reinterpret_cast<float2*>(stage + 2 * lane) = sb_v;
