@@ -59,7 +59,7 @@ constexpr int kColRowsPerThread = kTile / kColHalfWarps;  // 8
 // half-warp spans exactly one row tile -- so a tensor that needs both forms (an upstream
 // gradient: row-wise for dgrad, column-wise for wgrad) is read from HBM once, not twice.
 template <bool WITH_ROWS>
-__global__ void __launch_bounds__(kColThreads, 2)
+__global__ void __launch_bounds__(kColThreads, 3)
 quantize_colwise_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
                         float* __restrict__ scales, uint8_t* __restrict__ q_row,
                         float* __restrict__ s_row, int64_t rows, int64_t cols) {
@@ -78,16 +78,13 @@ quantize_colwise_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict
     w[r] = (col_ok && row < rows) ? ld_nc_v4(x + row * cols + col0) : make_uint4(0, 0, 0, 0);
   }
   if constexpr (WITH_ROWS) {   // cols % 128 == 0 here: every lane holds real columns
-    float mr[kColRowsPerThread];
+    // the 8 row tiles of a half-warp: one exchange leaves lane j with the amax of row j % 8
+    uint32_t mr[kColRowsPerThread];
 #pragma unroll
-    for (int r = 0; r < kColRowsPerThread; ++r) {
-      mr[r] = amax8(w[r]);
-#pragma unroll
-      for (int o = 8; o > 0; o >>= 1) mr[r] = max_nan(mr[r], __shfl_xor_sync(0xffffffffu, mr[r], o));
-    }
+    for (int r = 0; r < kColRowsPerThread; ++r) mr[r] = absmax8_h(w[r]);
     float sr[kColRowsPerThread], rr[kColRowsPerThread], s_mine;
     bool fin;
-    tile_scales<kColRowsPerThread>(mr, sr, rr, s_mine, fin);
+    tile_scales_own<kColRowsPerThread>(exchange_tile_amax<kColRowsPerThread>(mr), sr, rr, s_mine, fin);
     {
       const int64_t row = row0 + int64_t(cx & 7) * kColHalfWarps;   // lane j of the half computed row r = j % 8
       if (cx < kColRowsPerThread && row < rows) s_row[row * (cols / kTile) + blockIdx.x] = s_mine;
@@ -143,27 +140,31 @@ quantize_colwise_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict
   bool all_finite = true;
 #pragma unroll
   for (int j = 0; j < 8; ++j) all_finite = all_finite && (fabsf(s[j]) <= 3.402823466e38f);
+  // this thread's four column pairs: scale and negated reciprocal as packed operands (see quantize2_sr)
+  float2 s2[4], nr2[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    s2[j] = make_float2(s[2 * j], s[2 * j + 1]);
+    nr2[j] = make_float2(-rc[2 * j], -rc[2 * j + 1]);
+  }
 #pragma unroll
   for (int r = 0; r < kColRowsPerThread; ++r) {
     const int64_t row = row0 + r * kColHalfWarps;
     if (row >= rows) break;
     const uint4 v = w[r];
-    const float xs[8] = {bf16lo(v.x), bf16hi(v.x), bf16lo(v.y), bf16hi(v.y),
-                         bf16lo(v.z), bf16hi(v.z), bf16lo(v.w), bf16hi(v.w)};
-    float qv[8];
+    uint32_t b0, b1, b2, b3;
     if (all_finite) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {  // x/s as q0 = x*r, q = fma(-fma(q0,s,-x), r, q0): see QuantDiv
-        const float q0 = __fmul_rn(xs[j], rc[j]);
-        qv[j] = __fmaf_rn(-__fmaf_rn(q0, s[j], -xs[j]), rc[j], q0);
-      }
+      b0 = quantize2_sr(v.x, s2[0], nr2[0]);
+      b1 = quantize2_sr(v.y, s2[1], nr2[1]);
+      b2 = quantize2_sr(v.z, s2[2], nr2[2]);
+      b3 = quantize2_sr(v.w, s2[3], nr2[3]);
     } else {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) qv[j] = __fdiv_rn(xs[j], s[j]);
+      b0 = cvt_e4m3x2(__fdiv_rn(bf16lo(v.x), s[0]), __fdiv_rn(bf16hi(v.x), s[1]));
+      b1 = cvt_e4m3x2(__fdiv_rn(bf16lo(v.y), s[2]), __fdiv_rn(bf16hi(v.y), s[3]));
+      b2 = cvt_e4m3x2(__fdiv_rn(bf16lo(v.z), s[4]), __fdiv_rn(bf16hi(v.z), s[5]));
+      b3 = cvt_e4m3x2(__fdiv_rn(bf16lo(v.w), s[6]), __fdiv_rn(bf16hi(v.w), s[7]));
     }
-    const uint32_t b0 = cvt_e4m3x2(qv[0], qv[1]), b1 = cvt_e4m3x2(qv[2], qv[3]);
-    const uint32_t b2 = cvt_e4m3x2(qv[4], qv[5]), b3 = cvt_e4m3x2(qv[6], qv[7]);
-    *reinterpret_cast<uint2*>(q + row * cols + col0) = make_uint2(b0 | (b1 << 16), b2 | (b3 << 16));
+    *reinterpret_cast<uint2*>(q + row * cols + col0) = make_uint2(__byte_perm(b0, b1, 0x5410), __byte_perm(b2, b3, 0x5410));
   }
 }
 
