@@ -15,18 +15,19 @@
 // time per issued instruction, which is what keeps the single-thread issue loop and the
 // barrier round trips off the critical path.
 //
-// Warp roles in the 576-thread CTA (persistent, one CTA per SM, tiles round-robin):
-//   warp 0       TMA producer: A (one 128 x 128-byte box) and B (BN/128 boxes), 128B swizzle
-//   warp 1       MMA issuer (owns the TMEM allocation).  Its barrier polls for block k+1 are
-//                issued before the tcgen05.mma of block k, so their latency hides under the
-//                ~300-cycle issue of four MMAs and a commit
-//   warps 2..17  promotion + epilogue; warp w may touch TMEM lanes 32*(w%4).. (a hardware
-//                rule) and owns accumulator columns (BN/4)*((w-2)/4)..; four warps per
-//                scheduler hide each other's TMEM-load latency.  Each warp stores its own
-//                32 x BN/4 piece of the tile: registers -> its private swizzled staging
-//                rows -> 16-byte global stores that cover whole 128-byte lines; no cross-warp
-//                barrier, no asynchronous-proxy fence or wait (a TMA-store epilogue measured
-//                ~2300 cycles per tile, most of it in those waits).
+// Warp roles in the CTA (persistent, one CTA per SM, tiles round-robin):
+//   warps 0..P-1 promotion + epilogue (P = 16, or 12 for 192-column tiles); warp w may touch TMEM
+//                lanes 32*(w%4).. (a hardware rule) and owns accumulator columns (BN/4)*(w/4)..;
+//                four warps per scheduler hide each other's TMEM-load latency.  bf16 tiles leave
+//                through one bulk tensor store per warp (registers -> the warp's swizzled staging
+//                rows -> cp.async.bulk.tensor), waited for only when the rows are reused a tile
+//                later; float32 tiles use the warp's own 16-byte coalesced stores.
+//   warp P       TMA producer: A (one 128 x 128-byte box) and B (BN/128 boxes), 128B swizzle
+//   warp P+1     MMA issuer (owns the TMEM allocation): one lane-split barrier wait per block
+//   warps P+2,3  (256-column tiles only) idle padding of the producer's warpgroup, so that it can
+//                release registers to the promotion warpgroups with setmaxnreg: 96 -> 40 / 104.
+//                The 8 extra registers take the tile-boundary spills from 14 stores / 8 loads to
+//                3 / 7; their reloads miss the 28 KB of L1 left beside 214 KB of shared memory.
 //
 // Operand orientation is data, not code: the TMA box is 128 bytes x 128 rows for both
 // K-major and MN-major storage (only the coordinates swap), and the shared-memory operand
@@ -41,6 +42,13 @@
 
 #include "common.cuh"
 
+#ifndef TG_REGSTEAL
+#define TG_REGSTEAL 1
+#endif
+#ifndef TG_SCALE_LD
+#define TG_SCALE_LD "ld.global.nc.f32"
+#endif
+
 namespace tg {
 
 constexpr int BM = 128;          // tile rows (TMEM lanes)
@@ -49,7 +57,6 @@ constexpr int UMMA_K = 32;       // K of one tcgen05.mma.kind::f8f6f4
 constexpr int kTmemCols = 512;
 constexpr int kTileBytes = 128 * 128;            // one operand TMA box: 128 rows x 128 bytes
 constexpr int kIssuers = 1;                      // MMA-issuing warps
-constexpr int kFirstPromoWarp = 1 + kIssuers;    // 2
 constexpr int kSmemLimit = 227 * 1024;
 constexpr long long kWaitLimitCycles = 4000000000LL;  // ~2 s at 2 GHz
 
@@ -60,7 +67,19 @@ struct Cfg {
   // 192-column tiles run 12 promotion warps (14 warps in all: 128 registers per thread instead
   // of the 96 an 18-warp CTA gets), the others 16
   static constexpr int promo_warps = BN == 192 ? 12 : 16;
-  static constexpr int threads = 32 * (kFirstPromoWarp + promo_warps);
+  // Warp layout: promotion warps 0..P-1 (whole warpgroups), then the TMA producer, then the MMA
+  // issuer.  The 256-column tile pads that last warpgroup with two idle warps so that it can hand
+  // registers over with setmaxnreg: 20 warps start at 96 registers per thread; the producer's
+  // warpgroup drops to `service_regs` and each promotion warpgroup grows to `promo_regs`
+  // (service_regs + 4 * promo_regs <= 5 * 96 per scheduler, so the growth never waits for
+  // registers that nobody releases).
+  static constexpr bool regsteal = TG_REGSTEAL && BN == 256;
+  static constexpr int producer_warp = promo_warps;
+  static constexpr int issuer_warp = promo_warps + 1;
+  static constexpr int warps = promo_warps + (regsteal ? 4 : 2);
+  static constexpr int threads = 32 * warps;
+  static constexpr int promo_regs = 104, service_regs = 40;
+  static_assert(service_regs + 4 * promo_regs <= 5 * 96, "register hand-over asks for more than is released");
   static constexpr int tmem_bufs = BN > 128 ? 2 : 4;
   static constexpr int tmem_stride = kTmemCols / tmem_bufs;   // columns between accumulator buffers
   static constexpr int cols_per_warp = BN / (promo_warps / 4);  // 64 or 32
@@ -74,6 +93,10 @@ struct Cfg {
   static constexpr int phase_row_bytes = row_bytes < phase_cap ? row_bytes : phase_cap;
   static constexpr int phases = row_bytes / phase_row_bytes;
   static constexpr int phase_cols = phase_row_bytes / esize;
+  // bf16 tiles leave through bulk tensor stores (one 32-row box per promotion warp, never waited
+  // for inside the tile loop); float32 tiles (two staging phases per warp, and the split-contraction
+  // slices whose row bound is not the tensor's) keep the warp's own coalesced stores
+  static constexpr bool bulk_store = !OUT_F32 && !CTA2;
   static constexpr int warp_out_bytes = 32 * phase_row_bytes;
   static constexpr int out_bytes = promo_warps * warp_out_bytes;
   static constexpr int sb_bytes = SB_GRAN == 1 ? promo_warps * 2 * cols_per_warp * 4 : 0;  // float[warps][2][cols_per_warp]
@@ -192,6 +215,19 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
       : "memory");
+}
+
+// Bulk tensor store of one box from shared memory; completion is tracked by the issuing thread's
+// bulk async-group, so the same lane must commit and later wait.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(x), "r"(y)
+               : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// returns once every bulk store this thread committed has finished READING shared memory
+__device__ __forceinline__ void tma_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
 
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
@@ -341,7 +377,7 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
 
 __device__ __forceinline__ float ldg_f32(const float* ptr) {
   float v;
-  asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(ptr));
+  asm volatile(TG_SCALE_LD " %0, [%1];" : "=f"(v) : "l"(ptr));
   return v;
 }
 
@@ -378,7 +414,8 @@ __device__ __forceinline__ void promote(float2* acc, const uint32_t (&v)[NC], co
 template <int BN_, int SB_GRAN, bool OUT_F32, bool CTA2>
 __global__ void __launch_bounds__((Cfg<BN_, SB_GRAN, OUT_F32, CTA2>::threads), 1)
 gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                            const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+                            const __grid_constant__ CUtensorMap tmap_b,
+                            const __grid_constant__ CUtensorMap tmap_d, const GemmParams p) {
   using C = Cfg<BN_, SB_GRAN, OUT_F32, CTA2>;
   constexpr int BN = C::BN, kStages = C::stages, kTmemBufs = C::tmem_bufs, kCols = C::cols_per_warp;
   constexpr int kPromoWarps = C::promo_warps;
@@ -422,7 +459,7 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_a)) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_b)) : "memory");
   }
-  if (warp == 1) {
+  if (warp == C::issuer_warp) {
     if (CTA2) {
       tmem_alloc_pair(sbase + C::off_tmem_ptr, kTmemCols);
       tmem_relinquish_pair();
@@ -437,8 +474,9 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_smem;
 
-  if (warp < kFirstPromoWarp) {
-    if (warp == 0) {
+  if (warp >= C::promo_warps) {
+    if (C::regsteal) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(C::service_regs));
+    if (warp == C::producer_warp) {
       // ------------------------------ TMA producer -------------------------------------
       // The whole warp walks the loop (uniform control flow); one elected lane issues.
       uint32_t it = 0;
@@ -473,11 +511,11 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
           __syncwarp();
         }
       }
-    } else if (warp <= kIssuers && leader) {
+    } else if (warp == C::issuer_warp && leader) {
       // ------------------------------ MMA issuers --------------------------------------
       // Issuer i takes the contraction blocks with (global block counter) % kIssuers == i.
       // Blocks are independent: each has its own TMEM buffer and shared-memory stage.
-      const int issuer = warp - 1;
+      const int issuer = 0;
       // instruction descriptor: D f32 (bit 4), A/B e4m3 (0), major bits 15/16, N>>3 at 17, M>>4 at 24
       const uint32_t idesc = (1u << 4) | (uint32_t(p.a_mn) << 15) | (uint32_t(p.b_mn) << 16) |
                              (uint32_t((BN / C::halves) >> 3) << 17) | (uint32_t(TM >> 4) << 24);
@@ -534,7 +572,8 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   } else {
     // ------------------------------ promotion + epilogue --------------------------------
-    const int pw = warp - kFirstPromoWarp;     // 0..kPromoWarps-1
+    if (C::regsteal) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(C::promo_regs));
+    const int pw = warp;                       // 0..kPromoWarps-1
     const int quarter = warp & 3;              // TMEM lanes this warp may touch
     const int cg = pw >> 2;                    // column group
     const int r = quarter * 32 + lane;         // row inside the tile
@@ -563,6 +602,16 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
     auto load_sa = [&](int kb) {
       float v = 0.f;
       if (m_ok && kb < p.nkb) v = ldg_f32(sa_ptr + (long long)kb * p.sa_sk);
+      return v;
+    };
+    // One scale per 128 columns: its address changes line with every block, so a load per block
+    // misses L1 every time and the loop would run at one L2 round trip per block.  Instead lane l
+    // fetches the scale of block 32 g + l once per 32 blocks and a shuffle hands each block its value.
+    float sb_grp = 0.f, sb_nxt = 0.f;
+    auto load_sb_lane = [&](int g) {
+      float v = 0.f;
+      const int kb = 32 * g + lane;
+      if (sb_ok && kb < p.nkb) v = ldg_f32(sb_ptr + (long long)kb * p.sb_sk);
       return v;
     };
     auto load_sb = [&](int kb) {
@@ -594,7 +643,8 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
         sb_ptr = p.sb + (long long)((nblk * 128 < p.N) ? nblk : 0) * p.sb_sn + kb_off * p.sb_sk;
       }
       sa_q0 = load_sa(0);
-      sb_q0 = load_sb(0);
+      if (SB_GRAN == 1) sb_q0 = load_sb(0);
+      else sb_grp = load_sb_lane(0);
     };
 
     if (first_tile < n_items) open_tile(first_tile);
@@ -609,9 +659,18 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
       for (int kb = 0; kb < p.nkb; ++kb, ++it) {
         const int buf = it % kTmemBufs;
         const float sa_v = sa_q0;
-        const float2 sb_v = sb_q0;
+        float2 sb_v = sb_q0;
         sa_q0 = load_sa(kb + 1);
-        sb_q0 = load_sb(kb + 1);
+        if (SB_GRAN == 1) {
+          sb_q0 = load_sb(kb + 1);
+        } else {
+          const int kl = kb & 31;
+          if (kl == 0) {
+            if (kb != 0) sb_grp = sb_nxt;
+            sb_nxt = load_sb_lane((kb >> 5) + 1);
+          }
+          sb_v.x = __shfl_sync(0xffffffffu, sb_grp, kl);
+        }
         float* stage = sb_stage + (it & 1u) * kCols;
         if (SB_GRAN == 1) {
           if (kPerLane == 2) *reinterpret_cast<float2*>(stage + 2 * lane) = sb_v;
@@ -678,6 +737,25 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
       constexpr int PRB = C::phase_row_bytes, LPR = PRB / 16, RPI = 32 / LPR;
       uint8_t* warp_out = smem + C::off_out + pw * C::warp_out_bytes;
       const int my_chunk = lane % LPR;
+      if (C::bulk_store) {
+        // bf16 output: the warp's 32 x kCols piece is one box.  Lane 0 hands it to the copy engine
+        // and the warp goes straight on to the next tile; the wait for the engine to have read the
+        // staging rows comes only before they are overwritten, one whole tile later.
+        if (lane == 0) tma_store_wait_read();
+        __syncwarp();
+#pragma unroll
+        for (int c = 0; c < PRB / 16; ++c) {   // 8 bf16 per 16-byte chunk
+          const int j = 4 * c;
+          st_shared_v4(out_base + (uint32_t(c ^ swz) << 4), pack_bf16x2(acc[j].x, acc[j].y),
+                       pack_bf16x2(acc[j + 1].x, acc[j + 1].y), pack_bf16x2(acc[j + 2].x, acc[j + 2].y),
+                       pack_bf16x2(acc[j + 3].x, acc[j + 3].y));
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the copy engine
+        __syncwarp();
+        if (lane == 0)   // rows past M and columns past N are clipped by the tensor map
+          tma_store_2d(&tmap_d, sbase + C::off_out + uint32_t(pw) * C::warp_out_bytes, tile_n0 + c0, row_base);
+        continue;
+      }
 #pragma unroll
       for (int ph = 0; ph < C::phases; ++ph) {
         __syncwarp();  // the previous read-back of these staging rows is complete
@@ -713,10 +791,12 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
   }
 
   // ------------------------------ teardown ----------------------------------------------
+  // the last bulk stores must have read their staging rows before the CTA's shared memory goes away
+  if (C::bulk_store && warp < C::promo_warps && lane == 0) tma_store_wait_read();
   tc_fence_before();
   __syncthreads();
   if (CTA2) cluster_sync_all();   // the peer no longer reads this CTA's shared memory or signals its barriers
-  if (warp == 1) {
+  if (warp == C::issuer_warp) {
     __syncwarp();
     tc_fence_after();
     if (CTA2) tmem_dealloc_pair(tmem_base, kTmemCols);
@@ -771,6 +851,11 @@ static int launch_gemm(const tg_gemm_args* a, GemmParams p, cudaStream_t st) {
   const int64_t b_inner = p.b_mn ? a->N : a->K, b_outer = p.b_mn ? a->K : a->N;
   if (int rc = make_tmap(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a->a, a_inner, a_outer, a->lda, 128, 128)) return rc;
   if (int rc = make_tmap(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a->b, b_inner, b_outer, a->ldb, 128, 128)) return rc;
+  CUtensorMap td = ta;   // placeholder where the kernel variant does not use it
+  if (C::bulk_store) {
+    static_assert(!C::bulk_store || C::phases == 1, "one box per warp");
+    if (int rc = make_tmap(&td, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.d, a->N, a->M, p.ldd * 2, C::phase_row_bytes, 32)) return rc;
+  }
   constexpr int TM = CTA2 ? 2 * BM : BM;
   p.tiles_m = int((a->M + TM - 1) / TM);
   p.tiles_n = int((a->N + BN_ - 1) / BN_);
@@ -822,9 +907,9 @@ static int launch_gemm(const tg_gemm_args* a, GemmParams p, cudaStream_t st) {
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    TG_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, ta, tb, p));
+    TG_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, ta, tb, td, p));
   } else {
-    kern<<<grid, C::threads, C::smem_bytes, st>>>(ta, tb, p);
+    kern<<<grid, C::threads, C::smem_bytes, st>>>(ta, tb, td, p);
   }
   TG_CUDA_CHECK(cudaGetLastError());
   return TG_OK;
