@@ -949,8 +949,11 @@ struct SplitPlan {
   int64_t bytes;     // workspace the split needs
 };
 
-// The smallest S in {1, 2, 4, 8} that fills at least 85 % of the SM slots of the last wave, among
-// those that divide the block count and leave every range at least 8 blocks; else the best of them.
+// S in {1, 2, 4, 8} (dividing the block count, every range at least 8 blocks) with the lowest
+// modelled time, in units of one contraction block on one SM: waves x (blocks per item + ~3 for an
+// item's ramp and stores), plus for S > 1 the reduce pass over S float32 slices at ~4 MB per unit.
+// A 2048 x 6144 weight gradient is 512 tiles = 3.5 waves of 256 blocks; cut in two it is 6.9 waves
+// of 128 (measured 6 % faster with the reduce); 2048 x 8192 (4.6 waves) is left whole.
 static SplitPlan plan_split(const tg_gemm_args* a, int bn) {
   SplitPlan pl = {1, 0};
   if (a->K % BK != 0) return pl;
@@ -960,11 +963,11 @@ static SplitPlan plan_split(const tg_gemm_args* a, int bn) {
   if (sms <= 0) return pl;
   double best = 0.0;
   for (int S = 1; S <= 8; S *= 2) {
-    if (nkb % S != 0 || nkb / S < 8) break;
-    const int64_t items = tiles * S;
-    const double eff = double(items) / double(((items + sms - 1) / sms) * sms);
-    if (eff > best + 0.02) { best = eff; pl.S = S; }
-    if (eff >= 0.85) break;
+    if (nkb % S != 0 || (S > 1 && nkb / S < 8)) break;
+    const int64_t waves = (tiles * S + sms - 1) / sms;
+    double cost = double(waves) * (double(nkb / S) + 3.0);
+    if (S > 1) cost += double(4 * S + 2) * double(a->M) * double(a->N) / 4.0e6;
+    if (S == 1 || cost < best * 0.98) { best = cost; pl.S = S; }
   }
   if (pl.S > 1) pl.bytes = int64_t(pl.S) * a->M * a->N * int64_t(sizeof(float));
   return pl;
