@@ -273,10 +273,10 @@ def main():
         "bound": "tensor", "kernel": "gemm_fp8_blockscaled_kernel", "achieved": achieved, "peak": fp8_peak,
         "unit": "TFLOP/s", "frac": achieved / fp8_peak,
         # DRAM bytes per launch: the ncu capture of the 8192-token forward GEMM (dram read + write
-        # 79.5 MB for 206.2 GFLOP, profiles/gemm_fp8_blockscaled_fwd_8192x2048x6144.md) scaled by FLOPs
+        # 77.2 MB for 206.2 GFLOP, profiles/gemm_fp8_blockscaled_fwd_8192x2048x6144.md) scaled by FLOPs
         # to the mean timed launch; the operands and the output of one launch are 0.25 - 0.6 GB
-        "traffic": (g_flops / max(len(gemm_events), 1)) * (79.5e6 / 206.2e9),
-        "traffic_note": "scaled from an ncu capture of a smaller launch of the same kernel by FLOPs; tensor-bound kernel, DRAM 7 % busy",
+        "traffic": (g_flops / max(len(gemm_events), 1)) * (77.2e6 / 206.2e9),
+        "traffic_note": "scaled from an ncu capture of a smaller launch of the same kernel by FLOPs; tensor-bound kernel, DRAM 8 % busy",
         "peak_note": f"2 x {peaks['source']} sustained bf16 cuBLAS ({peaks['bf16_tflops_sustained']} TFLOP/s); no FP8 peak is measured on this pool",
         "frac_of_spec_4500": achieved / 4500.0,
         "gemm_launches_timed": len(gemm_events), "gemm_share_of_step": g_ms / ms_total,
