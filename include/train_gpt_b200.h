@@ -72,6 +72,23 @@ int tg_quantize_colwise(const void* x, void* q, float* scales,
 int tg_quantize_rowcol(const void* x, void* q_row, float* s_row, void* q_col, float* s_col,
                        int64_t rows, int64_t cols, void* stream);
 
+/* tg_quantize_rowcol of an MLP activation that is computed on the fly instead of being read:
+ * the squared ReLU of model.py:72 (`jax.nn.relu(h) ** 2`) or the GELU the benchmark's training
+ * configuration names, and their cotangents for the backward pass.  `x` is the pre-activation (the
+ * up-projection's output); the *_BWD variants also read `gate`, the gradient arriving at the
+ * activation's output, and quantise gate * act'(x).  The value is computed in float32 and rounded
+ * to bf16 once before the quantisation rule of fp8.py:43-46 is applied, so the outputs equal
+ * tg_quantize_rowcol of the bf16 tensor an elementwise kernel would have written.
+ *   x, gate [rows, cols] bf16 (gate ignored, may be NULL, for the forward variants), cols % 128 == 0
+ *   outputs as tg_quantize_rowcol                                                           */
+#define TG_ACT_NONE 0
+#define TG_ACT_RELU2 1
+#define TG_ACT_GELU 2
+#define TG_ACT_RELU2_BWD 3
+#define TG_ACT_GELU_BWD 4
+int tg_act_quantize_rowcol(const void* x, const void* gate, int act, void* q_row, float* s_row,
+                           void* q_col, float* s_col, int64_t rows, int64_t cols, void* stream);
+
 /* Tiles of 128 x 128, one scale per tile: the weight granularity the benchmark
  * configurations name (the reference itself uses tg_quantize_colwise's).  Same scale
  * rule, fp8.py:43-46.

@@ -150,3 +150,24 @@ def test_loss_gradient_restatement_against_finite_differences():
     p[np.arange(6), tg] -= 1
     smooth = p * (1 - np.tanh(xs / 15.0) ** 2) / 6
     assert np.allclose(g, smooth, rtol=0.05, atol=2e-3)
+
+
+def test_activation_oracle_known_answers_and_derivatives():
+    """model.py:72 (`jax.nn.relu(h) ** 2`) worked by hand, its cotangent, and the GELU restatement
+    against central differences of its own float64 forward."""
+    from oracle import act_oracle as ao
+    h = np.array([-3.0, -0.0, 0.0, 0.5, 1.5, 3.0, 255.0], np.float32).astype(fo.BF16)
+    assert np.array_equal(ao.relu2(h).astype(np.float32), [0, 0, 0, 0.25, 2.25, 9, 65024.0])   # 255^2 = 65025 -> bf16
+    g = np.array([1, 1, 1, -2, 0.5, 3, 1], np.float32).astype(fo.BF16)
+    assert np.array_equal(ao.relu2_bwd(h, g).astype(np.float32), [0, 0, 0, -2, 1.5, 18, 510])
+    x = np.linspace(-6, 6, 97).astype(np.float32).astype(fo.BF16)
+    y = ao.gelu(x).astype(np.float32)
+    xf = x.astype(np.float64)
+    assert abs(y[48]) == 0 and np.all(y[xf > 5] == x.astype(np.float32)[xf > 5]) and np.all(np.abs(y[xf < -5.5]) < 1e-6)
+    from scipy.special import erf
+    f = lambda t: t * 0.5 * (1 + erf(t / np.sqrt(2)))
+    num = (f(xf + 1e-6) - f(xf - 1e-6)) / 2e-6
+    d = ao.gelu_bwd(x, np.ones_like(x)).astype(np.float64)
+    assert np.allclose(d, num, rtol=2 ** -7, atol=2 ** -9)
+    for name in ao.ACTS:
+        assert ao.apply(name, x, x).dtype == fo.BF16

@@ -17,6 +17,7 @@ TG_OK, TG_ERR_SHAPE, TG_ERR_ALIGN, TG_ERR_ARCH, TG_ERR_CUDA, TG_ERR_TOO_LARGE = 
 TG_NORM_FUSED, TG_NORM_PURE = 0, 1
 TG_MAJOR_K, TG_MAJOR_MN = 0, 1
 TG_OUT_BF16, TG_OUT_F32 = 0, 1
+TG_ACT = {"relu2": 1, "gelu": 2, "relu2_bwd": 3, "gelu_bwd": 4}
 
 _p, _i64, _f, _i = C.c_void_p, C.c_int64, C.c_float, C.c_int
 
@@ -40,6 +41,7 @@ SYMBOLS = {
     "tg_quantize_rowwise": (_i, [_p, _p, _p, _i64, _i64, _p]),
     "tg_quantize_colwise": (_i, [_p, _p, _p, _i64, _i64, _p]),
     "tg_quantize_rowcol": (_i, [_p, _p, _p, _p, _p, _i64, _i64, _p]),
+    "tg_act_quantize_rowcol": (_i, [_p, _p, _i, _p, _p, _p, _p, _i64, _i64, _p]),
     "tg_quantize_block128": (_i, [_p, _p, _p, _i64, _i64, _p]),
     "tg_selftest_quantise_division": (_i, [_p, _p]),
     "tg_rmsnorm_fwd": (_i, [_p, _p, _f, _p, _p, _i64, _i64, _i, _p]),

@@ -55,14 +55,44 @@ constexpr int kColThreads = 256;
 constexpr int kColHalfWarps = kColThreads / 16;           // 16
 constexpr int kColRowsPerThread = kTile / kColHalfWarps;  // 8
 
+// Activation folded into the load (ACT != TG_ACT_NONE): the tile that is quantised is
+//   relu2      bf16( max(x,0)^2 )                         model.py:72, `jax.nn.relu(h) ** 2`
+//   gelu       bf16( x/2 (1 + erf(x/sqrt 2)) )            the activation BASELINE's training configuration names
+//   relu2_bwd  bf16( gate * 2 max(x,0) )                  the cotangent of relu2 for upstream gradient `gate`
+//   gelu_bwd   bf16( gate * (Phi(x) + x phi(x)) )
+// each computed in float32 from the bf16 input(s) and rounded to bf16 ONCE, which is what the
+// unfused composition (an elementwise bf16 kernel, then the quantiser) would have handed over.
+// The MLP's activation and its gradient are then never written to memory.
+template <int ACT>
+__device__ __forceinline__ float act_value(float x, float gate) {
+  if (ACT == TG_ACT_RELU2) { const float r = fmaxf(x, 0.f); return r * r; }
+  if (ACT == TG_ACT_RELU2_BWD) return gate * (2.f * fmaxf(x, 0.f));
+  if (ACT == TG_ACT_GELU) return x * 0.5f * (1.f + erff(x * 0.70710678118654752440f));
+  if (ACT == TG_ACT_GELU_BWD) {
+    const float cdf = 0.5f * (1.f + erff(x * 0.70710678118654752440f));
+    const float pdf = expf(-0.5f * x * x) * 0.39894228040143267794f;
+    return gate * (cdf + x * pdf);
+  }
+  return x;
+}
+template <int ACT>
+__device__ __forceinline__ uint32_t act_pair(uint32_t x2, uint32_t g2) {
+  return pack_bf16x2(act_value<ACT>(bf16lo(x2), bf16lo(g2)), act_value<ACT>(bf16hi(x2), bf16hi(g2)));
+}
+template <int ACT>
+__device__ __forceinline__ uint4 act_apply(uint4 x, uint4 g) {
+  return make_uint4(act_pair<ACT>(x.x, g.x), act_pair<ACT>(x.y, g.y), act_pair<ACT>(x.z, g.z), act_pair<ACT>(x.w, g.w));
+}
+
 // WITH_ROWS: the same pass also emits the 1 x 128 (row-wise) quantisation of the panel -- a
 // half-warp spans exactly one row tile -- so a tensor that needs both forms (an upstream
 // gradient: row-wise for dgrad, column-wise for wgrad) is read from HBM once, not twice.
-template <bool WITH_ROWS>
+template <bool WITH_ROWS, int ACT = TG_ACT_NONE>
 __global__ void __launch_bounds__(kColThreads, 3)
 quantize_colwise_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
                         float* __restrict__ scales, uint8_t* __restrict__ q_row,
-                        float* __restrict__ s_row, int64_t rows, int64_t cols) {
+                        float* __restrict__ s_row, int64_t rows, int64_t cols,
+                        const __nv_bfloat16* __restrict__ gate = nullptr) {
   __shared__ float s_max[kColThreads / 32][kColPanelCols];
   __shared__ __align__(16) float s_scale[kColPanelCols], s_rcp[kColPanelCols];
   const int cx = threadIdx.x & 15, hw = threadIdx.x >> 4;
@@ -76,6 +106,12 @@ quantize_colwise_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict
   for (int r = 0; r < kColRowsPerThread; ++r) {
     const int64_t row = row0 + r * kColHalfWarps;
     w[r] = (col_ok && row < rows) ? ld_nc_v4(x + row * cols + col0) : make_uint4(0, 0, 0, 0);
+    if constexpr (ACT != TG_ACT_NONE) {
+      uint4 g = make_uint4(0, 0, 0, 0);
+      if constexpr (ACT == TG_ACT_RELU2_BWD || ACT == TG_ACT_GELU_BWD)
+        if (col_ok && row < rows) g = ld_nc_v4(gate + row * cols + col0);
+      w[r] = act_apply<ACT>(w[r], g);   // rows past the end stay zero: every variant maps (0, 0) to 0
+    }
   }
   if constexpr (WITH_ROWS) {   // cols % 128 == 0 here: every lane holds real columns
     // the 8 row tiles of a half-warp: one exchange leaves lane j with the amax of row j % 8
@@ -255,6 +291,35 @@ extern "C" int tg_quantize_rowcol(const void* x, void* q_row, float* s_row, void
                                   static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(q_col), s_col, static_cast<uint8_t*>(q_row), s_row, rows,
       cols);
+  TG_CUDA_CHECK(cudaGetLastError());
+  return TG_OK;
+}
+
+extern "C" int tg_act_quantize_rowcol(const void* x, const void* gate, int act, void* q_row, float* s_row, void* q_col,
+                                      float* s_col, int64_t rows, int64_t cols, void* stream) {
+  if (rows < 0 || cols < 0 || cols % kTile != 0) return TG_ERR_SHAPE;
+  const bool bwd = act == TG_ACT_RELU2_BWD || act == TG_ACT_GELU_BWD;
+  if (act != TG_ACT_RELU2 && act != TG_ACT_GELU && !bwd) return TG_ERR_SHAPE;
+  if (rows == 0 || cols == 0) return TG_OK;
+  if (bwd && gate == nullptr) return TG_ERR_SHAPE;
+  if (!aligned16(x) || (bwd && !aligned16(gate)) || !aligned16(q_row) || !aligned16(q_col) || !aligned16(s_col) ||
+      (reinterpret_cast<uintptr_t>(s_row) & 3u))
+    return TG_ERR_ALIGN;
+  if (int rc = check_arch()) return rc;
+  const int64_t gx = cols / kColPanelCols, gy = (rows + kTile - 1) / kTile;
+  if (gy > 65535) return TG_ERR_TOO_LARGE;
+  const dim3 grid{unsigned(gx), unsigned(gy)};
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
+  const __nv_bfloat16* gp = static_cast<const __nv_bfloat16*>(gate);
+  uint8_t* qc = static_cast<uint8_t*>(q_col);
+  uint8_t* qr = static_cast<uint8_t*>(q_row);
+  switch (act) {
+    case TG_ACT_RELU2: quantize_colwise_kernel<true, TG_ACT_RELU2><<<grid, kColThreads, 0, st>>>(xp, qc, s_col, qr, s_row, rows, cols, gp); break;
+    case TG_ACT_GELU: quantize_colwise_kernel<true, TG_ACT_GELU><<<grid, kColThreads, 0, st>>>(xp, qc, s_col, qr, s_row, rows, cols, gp); break;
+    case TG_ACT_RELU2_BWD: quantize_colwise_kernel<true, TG_ACT_RELU2_BWD><<<grid, kColThreads, 0, st>>>(xp, qc, s_col, qr, s_row, rows, cols, gp); break;
+    default: quantize_colwise_kernel<true, TG_ACT_GELU_BWD><<<grid, kColThreads, 0, st>>>(xp, qc, s_col, qr, s_row, rows, cols, gp); break;
+  }
   TG_CUDA_CHECK(cudaGetLastError());
   return TG_OK;
 }

@@ -84,6 +84,36 @@ def quantize_rowcol(x: torch.Tensor):
     return q_row, s_row, q_col, s_col
 
 
+def act_quantize_rowcol(x: torch.Tensor, act: str, gate: torch.Tensor | None = None):
+    """quantize_rowcol of an MLP activation computed on the fly from the pre-activation `x`:
+    act "relu2" (model.py:72) or "gelu"; "relu2_bwd" / "gelu_bwd" quantise gate * act'(x), the
+    gradient at the pre-activation for upstream gradient `gate`.  The activation (or its gradient)
+    is rounded to bf16 once and never written to memory.  Returns (q_row, s_row, q_col, s_col)."""
+    if act not in _lib.TG_ACT:
+        raise ValueError(f"unknown activation {act!r}; use one of {sorted(_lib.TG_ACT)}")
+    x = _need(x, torch.bfloat16, "x")
+    if x.dim() != 2:
+        raise ValueError("act_quantize_rowcol takes a 2-D tensor")
+    bwd = act.endswith("_bwd")
+    if bwd:
+        if gate is None:
+            raise ValueError(f"{act} needs the upstream gradient `gate`")
+        gate = _need(gate, torch.bfloat16, "gate")
+        if gate.shape != x.shape:
+            raise ValueError(f"gate shape {tuple(gate.shape)} != x shape {tuple(x.shape)}")
+    R, Cc = x.shape
+    if Cc % TILE:
+        raise ValueError(f"K={Cc} not divisible by block_k={TILE}")
+    q_row = torch.empty((R, Cc), dtype=F8, device=x.device)
+    s_row = torch.empty((R, Cc // TILE), dtype=torch.float32, device=x.device)
+    q_col = torch.empty((R, Cc), dtype=F8, device=x.device)
+    s_col = torch.empty((_cdiv(R, TILE), Cc), dtype=torch.float32, device=x.device)
+    _lib.check(_lib.load().tg_act_quantize_rowcol(_ptr(x), _ptr(gate) if bwd else 0, _lib.TG_ACT[act], _ptr(q_row),
+                                                  _ptr(s_row), _ptr(q_col), _ptr(s_col), R, Cc, _stream()),
+               "tg_act_quantize_rowcol")
+    return q_row, s_row, q_col, s_col
+
+
 def quantize_block128(x: torch.Tensor):
     """128x128 tiles.  x (R, C) bf16 -> q (R, C) e4m3, scales (ceil(R/128), C/128) f32."""
     x = _need(x, torch.bfloat16, "x")

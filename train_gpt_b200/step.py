@@ -47,6 +47,7 @@ class StepConfig:
     logit_cap: float = 15.0         # config.py:19
     activation: str = "gelu"        # "gelu" (BASELINE configuration 3) or "relu2" (model.py:72)
     mm: str = "fp8"
+    mlp: str = "fused"              # "fused": activation and its gradient folded into the quantisers (FP8 mm only); "unfused"
     norm: str = "fused"
     loss: str = "fused"             # "fused": one CUDA pass each way over the logits; "torch": op by op (CPU tests)
     optimizer: str = "fused"        # "fused": optim.ClippedAdamW (CUDA kernels); "torch": torch.optim.AdamW + tensor-op clip
@@ -78,6 +79,43 @@ class _NormQuant(torch.autograd.Function):
             return None, None, None
         dx, dgamma = ops.rmsnorm_bwd(x, gamma, gy.contiguous(), ctx.eps)
         return dx, dgamma, None
+
+
+class _FusedMLP(torch.autograd.Function):
+    """model.py:72 -- `mm(act(mm(h, w_up)), w_down)` -- with both GEMMs and their FP8 backward as in
+    fp8.block_scaled_matmul(weight_tile=(128, 128), backward="fp8"), except that the activation is
+    never materialised: the down-projection's operand is quantised straight from the up-projection's
+    output (ops.act_quantize_rowcol), and in the backward pass the gradient at the pre-activation is
+    quantised straight from the down-projection's dgrad output and the saved pre-activation.  Saves
+    one bf16 write + read of the (tokens, d_ff) activation each way and two elementwise launches."""
+
+    @staticmethod
+    def forward(ctx, h, hq, w_up, w_down, act):
+        d = h.shape[-1]
+        h2d = h.reshape(-1, d)
+        a_q, a_s = hq.rowwise() if hq is not None else ops.quantize_rowwise(h2d)
+        wu_q, wu_s = ops.quantize_block128(w_up)
+        u = ops.gemm_fwd(a_q, a_s, wu_q, wu_s, (128, 128))                       # pre-activation, bf16
+        r_q, r_s, c_q, c_s = ops.act_quantize_rowcol(u, act)                     # act(u): row form now, column form for wgrad
+        wd_q, wd_s = ops.quantize_block128(w_down)
+        y = ops.gemm_fwd(r_q, r_s, wd_q, wd_s, (128, 128))
+        ctx.save_for_backward(h, u)
+        ctx.stash = (hq, act, c_q, c_s, wu_q, wu_s, wd_q, wd_s)
+        return y.reshape(*h.shape[:-1], w_down.shape[1])
+
+    @staticmethod
+    def backward(ctx, g):
+        h, u = ctx.saved_tensors
+        hq, act, c_q, c_s, wu_q, wu_s, wd_q, wd_s = ctx.stash
+        g2d = g.reshape(-1, g.shape[-1]).contiguous()
+        g_q, g_s, g_qc, g_sc = ops.quantize_rowcol(g2d)
+        da = ops.gemm_dgrad(g_q, g_s, wd_q, wd_s, (128, 128))                    # gradient at act(u)
+        dw_down = ops.gemm_wgrad(c_q, c_s, g_qc, g_sc)
+        du_q, du_s, du_qc, du_sc = ops.act_quantize_rowcol(u, act + "_bwd", da)  # da * act'(u), quantised, never stored
+        dh = ops.gemm_dgrad(du_q, du_s, wu_q, wu_s, (128, 128))
+        x_qc, x_sc = hq.colwise() if hq is not None else ops.quantize_colwise(h.reshape(-1, h.shape[-1]))
+        dw_up = ops.gemm_wgrad(x_qc, x_sc, du_qc, du_sc)
+        return dh.reshape(h.shape), None, dw_up, dw_down, None
 
 
 class GPT:
@@ -157,7 +195,10 @@ class GPT:
             o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True)
             x = x + self._mm(o.transpose(1, 2).reshape(B, T, -1), lp["wo"])         # model.py:68
             h, hq = self._norm(x, lp["norm2"])                                      # model.py:77
-            x = x + self._mm(self._act(self._mm(h, lp["w_up"], hq)), lp["w_down"])
+            if c.mm == "fp8" and c.mlp == "fused":
+                x = x + _FusedMLP.apply(h, hq, lp["w_up"], lp["w_down"], c.activation)
+            else:
+                x = x + self._mm(self._act(self._mm(h, lp["w_up"], hq)), lp["w_down"])
         x, _ = self._norm(x, self.final_norm)                                       # model.py:93
         return x @ self.unembed                                                     # stays bf16 (bench_fp8_norm.py:86)
 
