@@ -34,7 +34,33 @@ struct Softcap {
     return round_bf16(tanhf(a));
   }
   __device__ __forceinline__ float z_of_tanh(float t) const { return round_bf16(__fmul_rn(c, t)); }
+  // The quotient of tanh_of alone: bf16(x / c) as a float
+  __device__ __forceinline__ float quotient(float x) const {
+    const float q0 = __fmul_rn(x, r);
+    return round_bf16(__fmaf_rn(-__fmaf_rn(q0, c, -x), r, q0));
+  }
 };
+
+// bf16(tanh(a)) for a bf16 argument needs no evaluation outside 2^-6 <= |a| < 4: below, tanh(a)
+// differs from a by less than a^2/3 <= 2^-13.6 relative, far inside half a bf16 ulp (>= 2^-10), so
+// the result is a itself; from 4 on, 1 - tanh(a) <= 6.8e-4 < 2^-9, so it rounds to +-1.  The 1024
+// arguments in between (8 binades x 128 mantissas) are tabulated per thread block with the same
+// tanhf the direct form used, which makes the table path bit-identical to it.
+constexpr uint32_t kTanhLo = (127u - 6u) << 7;   // bf16 magnitude bits of 2^-6
+constexpr uint32_t kTanhHi = (127u + 2u) << 7;   // ... of 4.0
+constexpr int kTanhEntries = int(kTanhHi - kTanhLo);
+
+__device__ __forceinline__ void tanh_table_fill(uint16_t* table) {
+  for (int i = threadIdx.x; i < kTanhEntries; i += blockDim.x)
+    table[i] = uint16_t(__float_as_uint(round_bf16(tanhf(__uint_as_float((kTanhLo + uint32_t(i)) << 16)))) >> 16);
+}
+// a: a bf16 value held in a float
+__device__ __forceinline__ float tanh_bf16(float a, const uint16_t* table) {
+  const uint32_t bits = __float_as_uint(a), mag = (bits >> 16) & 0x7fffu;
+  if (mag < kTanhLo || mag > 0x7f80u) return a;                                   // tiny (or NaN): tanh(a) rounds to a
+  if (mag >= kTanhHi) return __uint_as_float((bits & 0x80000000u) | 0x3f800000u);  // +-1
+  return __uint_as_float((bits & 0x80000000u) | (uint32_t(table[mag - kTanhLo]) << 16));
+}
 
 // (m, s) <- combine with (m2, s2): s counts exp(z - m)
 __device__ __forceinline__ void lse_merge(float& m, float& s, float m2, float s2) {
@@ -48,6 +74,9 @@ softcap_ce_fwd_kernel(const __nv_bfloat16* __restrict__ logits, const int32_t* _
                       __nv_bfloat16* __restrict__ tanh_out, float* __restrict__ lse_out, float* __restrict__ nll_out,
                       int vocab, int64_t ld, int64_t ld_t) {
   __shared__ float s_m[kLossThreads / 32], s_s[kLossThreads / 32];
+  __shared__ uint16_t s_tanh[kTanhEntries];
+  tanh_table_fill(s_tanh);
+  __syncthreads();
   const int64_t row = blockIdx.x;
   const __nv_bfloat16* p = logits + row * ld;
   const Softcap sc(cap);
@@ -60,7 +89,7 @@ softcap_ce_fwd_kernel(const __nv_bfloat16* __restrict__ logits, const int32_t* _
     uint32_t* tp = &to.x;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const float t0 = sc.tanh_of(bf16lo(xi[j])), t1 = sc.tanh_of(bf16hi(xi[j]));
+      const float t0 = tanh_bf16(sc.quotient(bf16lo(xi[j])), s_tanh), t1 = tanh_bf16(sc.quotient(bf16hi(xi[j])), s_tanh);
       tp[j] = pack_bf16x2(t0, t1);   // exact: both are bf16 values already
       z[2 * j] = sc.z_of_tanh(t0);
       z[2 * j + 1] = sc.z_of_tanh(t1);
