@@ -99,3 +99,17 @@ def test_rejects_bad_arguments():
         ops.act_quantize_rowcol(x, "gelu_bwd")                      # no gate
     with pytest.raises(ValueError):
         ops.act_quantize_rowcol(torch.zeros((4, 100), dtype=torch.bfloat16, device="cuda"), "relu2")
+
+
+def test_gelu_every_finite_bf16_argument():
+    XX
+    (x/2 below 2^-11, a table up to 4, x from 4 on, erff for the negative tail) gives the bytes and
+    scales of torch's elementwise GELU followed by tg_quantize_rowcol."""
+    from train_gpt_b200 import ops
+    bits = np.concatenate([np.arange(0, 0x7F80), np.arange(0x8000, 0xFF80)]).astype(np.uint16)
+    x = to_torch_bf16(bits.view(BF16).reshape(510, 128))
+    out = ops.act_quantize_rowcol(x, "gelu")
+    ref = ops.quantize_rowcol(torch.nn.functional.gelu(x).contiguous())
+    assert torch.equal(out[1], ref[1]), "row-tile scales"
+    assert (out[0].view(torch.uint8) == ref[0].view(torch.uint8)).float().mean().item() >= 0.9995
+    assert (out[3] == ref[3]).float().mean().item() >= 0.99

@@ -83,6 +83,13 @@ def bench_quant(rows, cols, warmup, iters):
     _report("quantize_block128", m, b, bytes_=(3.0 + 4.0 / 16384) * E, shape=[rows, cols])
     m, b = _time(lambda i: ops.quantize_rowcol(xs[i]), n, warmup, iters, batch=10)
     _report("quantize_rowcol", m, b, bytes_=(2.0 + 2 * 1.03125) * E, shape=[rows, cols])
+    # the MLP activation (or its gradient) computed inside the same pass
+    gs = [(torch.randn(rows, cols, device="cuda") * 0.05).to(torch.bfloat16) for _ in range(n)]
+    for act in ("relu2", "gelu"):
+        m, b = _time(lambda i: ops.act_quantize_rowcol(xs[i], act), n, warmup, iters, batch=10)
+        _report(f"act_quantize_rowcol[{act}]", m, b, bytes_=(2.0 + 2 * 1.03125) * E, shape=[rows, cols])
+        m, b = _time(lambda i: ops.act_quantize_rowcol(xs[i], act + "_bwd", gs[i]), n, warmup, iters, batch=10)
+        _report(f"act_quantize_rowcol[{act}_bwd]", m, b, bytes_=(4.0 + 2 * 1.03125) * E, shape=[rows, cols])
 
 
 def bench_loss(rows, vocab, warmup, iters):
