@@ -102,9 +102,10 @@ def test_rejects_bad_arguments():
 
 
 def test_gelu_every_finite_bf16_argument():
-    XX
-    (x/2 below 2^-11, a table up to 4, x from 4 on, erff for the negative tail) gives the bytes and
-    scales of torch's elementwise GELU followed by tg_quantize_rowcol."""
+    """All 65280 finite bf16 values, 128 consecutive bit patterns per tile: the bytes and scales of
+    torch's elementwise GELU followed by tg_quantize_rowcol.  (A range split with a shared-memory
+    table for the erf, bit-identical on this test, measured SLOWER than evaluating erff per element
+    -- 1.5 against 2.0 TB/s: random 2-byte table reads conflict in the banks -- and was dropped.)"""
     from train_gpt_b200 import ops
     bits = np.concatenate([np.arange(0, 0x7F80), np.arange(0x8000, 0xFF80)]).astype(np.uint16)
     x = to_torch_bf16(bits.view(BF16).reshape(510, 128))
