@@ -57,7 +57,7 @@ constexpr int kColRowsPerThread = kTile / kColHalfWarps;  // 8
 
 // Activation folded into the load (ACT != TG_ACT_NONE): the tile that is quantised is
 //   relu2      bf16( max(x,0)^2 )                         model.py:72, `jax.nn.relu(h) ** 2`
-//   gelu       bf16( x/2 (1 + erf(x/sqrt 2)) )            the activation BASELINE's training configuration names
+//   gelu       bf16( x/2 (1 + erf(x/sqrt 2)) )            the activation the benchmark's training configuration names
 //   relu2_bwd  bf16( gate * 2 max(x,0) )                  the cotangent of relu2 for upstream gradient `gate`
 //   gelu_bwd   bf16( gate * (Phi(x) + x phi(x)) )
 // each computed in float32 from the bf16 input(s) and rounded to bf16 ONCE, which is what the

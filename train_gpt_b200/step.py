@@ -14,7 +14,7 @@ layer and the norms run on this package's kernels through the reference's `mm` /
          "torch_reference"  kernels.py:30-33 written with torch ops: the comparator the loss-curve
                     parity test and the CPU (gloo) tests of the gradient exchange run against
 
-Differences from model.py that BASELINE.json's configuration 3 asks for are switches: GELU
+Differences from model.py that the benchmark's training configuration asks for are switches: GELU
 (default there) or the reference's squared ReLU (model.py:72); learned positions, separate
 q/k/v, untied head, tanh logit cap 15 and the 0.02 / 0.02/sqrt(2L) init follow model.py.
 No per-block rematerialisation (the reference's `use_remat` trades compute for memory; 180 GB
@@ -45,7 +45,7 @@ class StepConfig:
     init_std: float = 0.02          # config.py:16
     rms_eps: float = 1e-5           # config.py:17
     logit_cap: float = 15.0         # config.py:19
-    activation: str = "gelu"        # "gelu" (BASELINE configuration 3) or "relu2" (model.py:72)
+    activation: str = "gelu"        # "gelu" (the benchmark's training configuration) or "relu2" (model.py:72)
     mm: str = "fp8"
     mlp: str = "fused"              # "fused": activation and its gradient folded into the quantisers (FP8 mm only); "unfused"
     norm: str = "fused"
@@ -327,7 +327,7 @@ def step_flops(cfg: StepConfig, tokens: int) -> float:
 
 def bench_train_step(world: int, rank: int, device, dist, steps: int = 5, warmup: int = 3, batch_per_gpu: int = 32,
                      cfg: StepConfig = StepConfig(), graph: bool = True):
-    """Tokens/s of the data-parallel step (BASELINE configuration 3): batch sharded by rank,
+    """Tokens/s of the data-parallel step (the benchmark's training configuration): batch sharded by rank,
     weights replicated, gradients all-reduced per layer bucket over NCCL."""
     batches = [synthetic_batch(cfg, batch_per_gpu, device, seed=1000 * rank + i) for i in range(2)]
     graph_error = None
@@ -400,7 +400,7 @@ def kernel_breakdown(steps: int = 2, batch_per_gpu: int = 32, cfg: StepConfig = 
 
 if __name__ == "__main__":
     import argparse
-    ap = argparse.ArgumentParser(description="Training step of BASELINE configuration 3 on one GPU")
+    ap = argparse.ArgumentParser(description="Training step of the benchmark's training configuration on one GPU")
     ap.add_argument("--kernel-breakdown", action="store_true", help="device time per kernel (torch profiler)")
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--no-graph", action="store_true")
