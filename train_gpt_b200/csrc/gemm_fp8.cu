@@ -99,7 +99,14 @@ struct Cfg {
   static constexpr bool bulk_store = !OUT_F32 && !CTA2;
   static constexpr int warp_out_bytes = 32 * phase_row_bytes;
   static constexpr int out_bytes = promo_warps * warp_out_bytes;
-  static constexpr int sb_bytes = SB_GRAN == 1 ? promo_warps * 2 * cols_per_warp * 4 : 0;  // float[warps][2][cols_per_warp]
+  // per-column scales: float[warps][2][cols_per_warp column scales + 32 row scales], double-buffered
+  static constexpr int sc_slot = cols_per_warp + 32;
+  static constexpr int sb_bytes = SB_GRAN == 1 ? promo_warps * 2 * sc_slot * 4 : 0;
+  // 64-column warps with per-column scales read TMEM in the MMA fragment layout (a thread holds 4 rows
+  // x 16 columns instead of 1 x 64): a column scale is then shared by 8 lanes instead of all 32, and
+  // the block's 64 of them cost 8 conflict-free 8-byte reads per thread instead of 16 broadcasts of 16
+  // bytes, which a warp is served a quarter at a time (64 -> 16 shared-memory wavefronts per warp)
+  static constexpr bool frag = SB_GRAN == 1 && cols_per_warp == 64 && !CTA2;
   static constexpr int misc_bytes = 512;                      // barriers, TMEM pointer, abort flag
   static constexpr int stages_fit = (kSmemLimit - 1024 - out_bytes - sb_bytes - misc_bytes) / stage_bytes;
   static constexpr int stages = stages_fit > 6 ? 6 : stages_fit;
@@ -302,6 +309,23 @@ __device__ __forceinline__ void tmem_wait_ld16(uint32_t (&v)[16]) {
         "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15])
       :
       : "memory");
+}
+
+// 16 lanes x 16 consecutive columns of 32-bit, in the fragment layout of an MMA accumulator: thread
+// t (g = t / 4, j = t % 4) gets, for k = 0, 1:  v[4k], v[4k+1] <- lane base + g,     columns 8k + 2j, 8k + 2j + 1
+//                                               v[4k+2], v[4k+3] <- lane base + g + 8, same columns
+__device__ __forceinline__ void tmem_ld_frag16(uint32_t taddr, uint32_t* v) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.16x256b.x2.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void st_shared_b32(uint32_t addr, uint32_t x) {
+  asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(x) : "memory");
+}
+__device__ __forceinline__ void st_shared_v2(uint32_t addr, uint32_t x, uint32_t y) {
+  asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(x), "r"(y) : "memory");
 }
 
 // ---- CTA-pair (cta_group::2) variants ---------------------------------------------------
@@ -578,7 +602,9 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const int cg = pw >> 2;                    // column group
     const int r = quarter * 32 + lane;         // row inside the tile
     const int c0 = cg * kCols;                 // first column inside the tile
-    float* sb_stage = reinterpret_cast<float*>(smem + C::off_sb) + pw * (2 * kCols);  // warp-private, double-buffered
+    float* sb_stage = reinterpret_cast<float*>(smem + C::off_sb) + pw * (2 * C::sc_slot);  // warp-private, double-buffered
+    constexpr bool kFrag = C::frag;
+    const int fg = lane >> 2, fj = lane & 3;     // fragment coordinates: rows fg + 8 i, column pairs 8 k + 2 fj
     const uint32_t out_base = sbase + C::off_out + uint32_t(pw) * C::warp_out_bytes + uint32_t(lane) * C::phase_row_bytes;
     // TMA swizzle of this row: 16-byte chunk index XOR address bits 7.. (128B: 3 bits, 64B: 2, 32B: 1)
     const int swz = C::phase_row_bytes == 128 ? (lane & 7) : C::phase_row_bytes == 64 ? ((lane >> 1) & 3) : ((lane >> 2) & 1);
@@ -671,10 +697,11 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
           sb_v.x = __shfl_sync(0xffffffffu, sb_grp, kl);
         }
-        float* stage = sb_stage + (it & 1u) * kCols;
+        float* stage = sb_stage + (it & 1u) * C::sc_slot;
         if (SB_GRAN == 1) {
           if (kPerLane == 2) *reinterpret_cast<float2*>(stage + 2 * lane) = sb_v;
           else stage[lane] = sb_v.x;
+          if (kFrag) stage[kCols + lane] = sa_v;   // row 32 * quarter + lane
           __syncwarp();
         }
         // After an abort the remaining iterations only keep the loop counters in step.
@@ -697,6 +724,34 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
           __syncwarp();
           if (lane == 0) mbar_arrive(tempty_bar(tb));
           promote<SB_GRAN, 32>(acc + 16, v, stage + 32, sa_v, s_scalar);
+        } else if (kFrag) {
+          // acc[(4 q + i) * 2 + k] holds rows fg + 8 i, columns 16 q + 8 k + 2 fj (+1)
+          float sa_r[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) sa_r[i] = stage[kCols + fg + 8 * i];
+          uint32_t v[16];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            tmem_ld_frag16(taddr + 16 * q, v);                     // rows fg, fg + 8
+            tmem_ld_frag16(taddr + (16u << 16) + 16 * q, v + 8);   // rows fg + 16, fg + 24
+            tmem_wait_ld16(v);
+            if (q == 3) {
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(tempty_bar(tb));
+            }
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+              const float2 sb2 = *reinterpret_cast<const float2*>(stage + 16 * q + 8 * k + 2 * fj);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const int o = 8 * (i >> 1) + 4 * k + 2 * (i & 1);
+                const float2 pv = make_float2(__uint_as_float(v[o]), __uint_as_float(v[o + 1]));
+                float2& a = acc[(4 * q + i) * 2 + k];
+                a = __ffma2_rn(__fmul2_rn(pv, sb2), make_float2(sa_r[i], sa_r[i]), a);
+              }
+            }
+          }
         } else if (kCols > 32) {
           // 64 columns in four 16-column pieces; the buffer goes back after the last load lands
           uint32_t v[16];
@@ -743,6 +798,19 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
         // staging rows comes only before they are overwritten, one whole tile later.
         if (lane == 0) tma_store_wait_read();
         __syncwarp();
+        if (kFrag) {
+          const uint32_t wb = sbase + C::off_out + uint32_t(pw) * C::warp_out_bytes;
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+              for (int k = 0; k < 2; ++k) {   // row fg + 8 i (row & 7 == fg & 7), 16-byte chunk 2 q + k, 4 fj bytes in
+                const float2 a = acc[(4 * q + i) * 2 + k];
+                st_shared_b32(wb + uint32_t(fg + 8 * i) * PRB + (uint32_t((2 * q + k) ^ (fg & 7)) << 4) + 4u * fj,
+                              pack_bf16x2(a.x, a.y));
+              }
+        } else
 #pragma unroll
         for (int c = 0; c < PRB / 16; ++c) {   // 8 bf16 per 16-byte chunk
           const int j = 4 * c;
@@ -759,7 +827,19 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
       for (int ph = 0; ph < C::phases; ++ph) {
         __syncwarp();  // the previous read-back of these staging rows is complete
-        if (OUT_F32) {
+        if (kFrag && OUT_F32) {
+          const uint32_t wb = sbase + C::off_out + uint32_t(pw) * C::warp_out_bytes;
+#pragma unroll
+          for (int qq = 0; qq < 2; ++qq)     // this phase's 32 columns are pieces 2 ph, 2 ph + 1
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+              for (int k = 0; k < 2; ++k) {   // column 16 qq + 8 k + 2 fj of the phase: chunk of 4 floats, 8-byte half
+                const float2 a = acc[(4 * (2 * ph + qq) + i) * 2 + k];
+                st_shared_v2(wb + uint32_t(fg + 8 * i) * PRB + (uint32_t((4 * qq + 2 * k + (fj >> 1)) ^ (fg & 7)) << 4) + 8u * (fj & 1),
+                             __float_as_uint(a.x), __float_as_uint(a.y));
+              }
+        } else if (OUT_F32) {
 #pragma unroll
           for (int c = 0; c < PRB / 16; ++c) {   // 4 floats per 16-byte chunk
             const int j = ph * (C::phase_cols / 2) + 2 * c;
