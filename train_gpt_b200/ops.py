@@ -66,6 +66,9 @@ def quantize_colwise(x: torch.Tensor):
     return q, s
 
 
+last_gemm_kernel_launches = 0   # kernels the most recent gemm_* call launched (1, or 2 with the split-contraction reduce)
+
+
 def quantize_rowcol(x: torch.Tensor):
     """Row-wise (1x128) and column-wise (128x1) quantisation of a 2-D tensor in one pass.
     Returns (q_row, s_row, q_col, s_col), bit-identical to the two separate kernels."""
@@ -289,6 +292,8 @@ def gemm_blockscaled(a, b, sa, sb, *, M, N, K, a_major, b_major, sa_strides, sb_
             ws = torch.empty((need,), dtype=torch.uint8, device=a.device)
             args.workspace, args.workspace_bytes = _ptr(ws), need
     _lib.check(lib.tg_gemm_fp8_blockscaled(C.byref(args), _stream()), "tg_gemm_fp8_blockscaled")
+    global last_gemm_kernel_launches
+    last_gemm_kernel_launches = 2 if ws is not None else 1      # a split contraction adds the reduce kernel
     return out
 
 
