@@ -729,16 +729,18 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
           float sa_r[4];
 #pragma unroll
           for (int i = 0; i < 4; ++i) sa_r[i] = stage[kCols + fg + 8 * i];
-          uint32_t v[16];
+          // two staging sets: the loads of piece q + 1 are in flight while piece q is promoted
+          uint32_t va[16], vb[16];
+          tmem_ld_frag16(taddr, va);
+          tmem_ld_frag16(taddr + (16u << 16), va + 8);
+          tmem_wait_ld16(va);
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
-            tmem_ld_frag16(taddr + 16 * q, v);                     // rows fg, fg + 8
-            tmem_ld_frag16(taddr + (16u << 16) + 16 * q, v + 8);   // rows fg + 16, fg + 24
-            tmem_wait_ld16(v);
-            if (q == 3) {
-              tc_fence_before();
-              __syncwarp();
-              if (lane == 0) mbar_arrive(tempty_bar(tb));
+            uint32_t (&cur)[16] = (q & 1) ? vb : va;
+            uint32_t (&nxt)[16] = (q & 1) ? va : vb;
+            if (q < 3) {
+              tmem_ld_frag16(taddr + 16 * (q + 1), nxt);
+              tmem_ld_frag16(taddr + (16u << 16) + 16 * (q + 1), nxt + 8);
             }
 #pragma unroll
             for (int k = 0; k < 2; ++k) {
@@ -746,10 +748,16 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
               for (int i = 0; i < 4; ++i) {
                 const int o = 8 * (i >> 1) + 4 * k + 2 * (i & 1);
-                const float2 pv = make_float2(__uint_as_float(v[o]), __uint_as_float(v[o + 1]));
+                const float2 pv = make_float2(__uint_as_float(cur[o]), __uint_as_float(cur[o + 1]));
                 float2& a = acc[(4 * q + i) * 2 + k];
                 a = __ffma2_rn(__fmul2_rn(pv, sb2), make_float2(sa_r[i], sa_r[i]), a);
               }
+            }
+            if (q < 3) tmem_wait_ld16(nxt);
+            if (q == 2) {        // every load of the buffer has landed
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(tempty_bar(tb));
             }
           }
         } else if (kCols > 32) {
