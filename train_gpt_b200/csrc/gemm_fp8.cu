@@ -42,13 +42,6 @@
 
 #include "common.cuh"
 
-#ifndef TG_REGSTEAL
-#define TG_REGSTEAL 1
-#endif
-#ifndef TG_SCALE_LD
-#define TG_SCALE_LD "ld.global.nc.f32"
-#endif
-
 namespace tg {
 
 constexpr int BM = 128;          // tile rows (TMEM lanes)
@@ -73,7 +66,7 @@ struct Cfg {
   // warpgroup drops to `service_regs` and each promotion warpgroup grows to `promo_regs`
   // (service_regs + 4 * promo_regs <= 5 * 96 per scheduler, so the growth never waits for
   // registers that nobody releases).
-  static constexpr bool regsteal = TG_REGSTEAL && BN == 256;
+  static constexpr bool regsteal = BN == 256;
   static constexpr int producer_warp = promo_warps;
   static constexpr int issuer_warp = promo_warps + 1;
   static constexpr int warps = promo_warps + (regsteal ? 4 : 2);
@@ -401,7 +394,7 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
 
 __device__ __forceinline__ float ldg_f32(const float* ptr) {
   float v;
-  asm volatile(TG_SCALE_LD " %0, [%1];" : "=f"(v) : "l"(ptr));
+  asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(ptr));   // L1-allocating: an activation scale's line serves 16-32 blocks
   return v;
 }
 
