@@ -121,14 +121,16 @@ def scaled_matmul(a_q, b_q_t, a_s, b_s, block_k: int = DEFAULT_BLOCK_K) -> np.nd
     (M, N) float32.  Inner sums are exact in float64 (an e4m3 product has 8
     significant bits; 128 of them span < 53 bits).
     """
-    a = np.asarray(a_q).astype(np.float64)
-    b = np.asarray(b_q_t).astype(np.float64)
-    M, K = a.shape
-    N = b.shape[0]
+    a_q = np.asarray(a_q)
+    b_q_t = np.asarray(b_q_t)
+    M, K = a_q.shape
+    N = b_q_t.shape[0]
     out = np.zeros((M, N), dtype=np.float64)
     for kb in range(K // block_k):
         sl = slice(kb * block_k, (kb + 1) * block_k)
-        part = a[:, sl] @ b[:, sl].T
+        # operands are widened one block at a time: the sampled full-size checks pass (N, K)
+        # arrays of 10^8 elements, whose float64 copy would not fit comfortably in host memory
+        part = a_q[:, sl].astype(np.float64) @ b_q_t[:, sl].astype(np.float64).T
         out += part * (a_s[:, kb].astype(np.float64)[:, None] * b_s[:, kb].astype(np.float64)[None, :])
     return out.astype(np.float32)
 
