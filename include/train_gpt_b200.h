@@ -105,6 +105,18 @@ int tg_quantize_block128(const void* x, void* q, float* scales,
  *   bare x*(1/s), [2] with one correction step (the shipped form -- must be 0), [3] with two. */
 int tg_selftest_quantise_division(uint64_t* counts, void* stream);
 
+/* No counterpart in the reference.  Every barrier wait inside tg_gemm_fp8_blockscaled is
+ * bounded: a wait that runs out raises a CTA-wide abort flag, stores its role code in the
+ * caller's status word, every other role leaves its own wait when it sees the flag, and the
+ * CTA frees its tensor memory and returns.  This runs exactly that sequence, with the GEMM's
+ * own wait routine and teardown, on a barrier that is never arrived at -- so that the give-up
+ * path is exercised without a fault and without hanging the device.
+ *   status  device uint32: receives the role code of the wait that ran out (5)
+ *   report  device uint32[4]: [0] 0 = the short wait gave up, [1] 2 = the long wait left early
+ *           on the abort flag, [2] 1 = an ordinary wait still succeeded, [3] 1 = teardown reached
+ *   limit_cycles  the short wait's clock64 limit, 1000 .. 50 000 000 (about 25 ms)          */
+int tg_selftest_bounded_wait(uint32_t* status, uint32_t* report, int64_t limit_cycles, void* stream);
+
 /* ---- RMSNorm ---------------------------------------------------------------------- */
 
 /* mode for the norm entry points */
@@ -174,7 +186,9 @@ int tg_rmsnorm_bwd_static(const void* x, const void* gamma, const void* g, float
  *   tanh_out bf16 [rows, ld_tanh] or NULL: bf16(tanh(bf16(logits / cap))), what the backward
  *            needs (cap * tanh_out, rounded to bf16, is the capped logits model.forward returns)
  *   lse, nll float32 [rows]: logsumexp of the capped logits, and lse - capped[target]
- *   vocab, ld, ld_tanh multiples of 8; pointers 16-byte aligned.                          */
+ *   ld, ld_tanh multiples of 8 (16-byte row pitch); pointers 16-byte aligned.  vocab itself
+ *   may be any positive size (train-gpt's default is 50257, config.py:8): the columns
+ *   between vocab and the row pitch are read but take no part and are never written.       */
 int tg_softcap_ce_fwd(const void* logits, const int32_t* targets, float cap, void* tanh_out, float* lse,
                       float* nll, int64_t rows, int64_t vocab, int64_t ld, int64_t ld_tanh, void* stream);
 

@@ -80,3 +80,22 @@ def test_launchers_validate_on_the_host(lib):
     args.sb_gran_n = 1
     args.N = 100
     assert lib.tg_gemm_fp8_blockscaled(ctypes.byref(args), None) == _lib.TG_ERR_SHAPE
+
+
+def test_nonzero_gemm_status_raises():
+    """A GEMM whose bounded device wait ran out leaves a role code in its status word; reading a
+    non-zero word raises and clears it.  (A host tensor stands in for the device word: no GPU.)"""
+    import torch
+    from train_gpt_b200 import ops
+    ok = torch.zeros(1, dtype=torch.int32)
+    ops.check_status(ok)                                        # zero: silent
+    for code in (1, 2, 3, 4, 5, 77):
+        word = torch.tensor([code], dtype=torch.int32)
+        with pytest.raises(RuntimeError, match=f"status {code}"):
+            ops.check_status(word)
+        assert int(word.item()) == 0                            # cleared for the next check
+    assert ops.status_error(0) is None
+    assert "promotion warps" in str(ops.status_error(5))
+    loss = torch.tensor(2.5)
+    assert float(ops.poison_if_failed(loss, ok)) == 2.5
+    assert torch.isnan(ops.poison_if_failed(loss, torch.tensor([3], dtype=torch.int32)))

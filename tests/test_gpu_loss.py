@@ -23,13 +23,15 @@ def _case(rows, vocab, seed, spread=6.0):
     return x, t
 
 
-@pytest.mark.parametrize("rows,vocab,spread", [(7, 512, 6.0), (33, 50304, 3.0), (4, 2056, 40.0)])
+@pytest.mark.parametrize("rows,vocab,spread", [(7, 512, 6.0), (33, 50304, 3.0), (4, 2056, 40.0),
+                                               (5, 50257, 3.0), (3, 12, 2.0), (2, 2049, 6.0)])   # 50257: train-gpt config.py:8
 def test_forward_matches_oracle(rows, vocab, spread):
     from train_gpt_b200 import ops
     x, t = _case(rows, vocab, rows + vocab, spread)
     nll, lse, th = ops.softcap_ce_fwd(to_torch_bf16(x), torch.from_numpy(t).cuda(), 15.0)
     z_ref, t_ref = lo.softcap(x, 15.0)
     _, nll_ref, lse_ref = lo.cross_entropy(z_ref, t)
+    assert th.shape == (rows, vocab)
     th_bits = from_torch_bf16(th).view(np.uint16).astype(np.int32)
     ref_bits = t_ref.view(np.uint16).astype(np.int32)
     assert np.abs(th_bits - ref_bits).max() <= 1
@@ -53,7 +55,7 @@ def test_every_finite_bf16_logit():
     assert np.allclose(lse.cpu().numpy(), lse_ref, rtol=2e-6) and np.allclose(nll.cpu().numpy(), nll_ref, rtol=2e-5, atol=2e-5)
 
 
-@pytest.mark.parametrize("rows,vocab", [(9, 512), (16, 50304)])
+@pytest.mark.parametrize("rows,vocab", [(9, 512), (16, 50304), (6, 50257), (5, 12)])
 def test_backward_matches_oracle(rows, vocab):
     from train_gpt_b200 import ops
     x, t = _case(rows, vocab, 3 * rows + vocab, 4.0)
@@ -61,8 +63,11 @@ def test_backward_matches_oracle(rows, vocab):
     _, lse, th = ops.softcap_ce_fwd(to_torch_bf16(x), tt, 15.0)
     gs = torch.tensor([0.75], dtype=torch.float32, device="cuda")
     d = ops.softcap_ce_bwd(th, tt, lse, gs, 15.0)
-    d_inplace = ops.softcap_ce_bwd(th.clone(), tt, lse, gs, 15.0, in_place=True)
-    assert torch.equal(d, d_inplace)
+    th2 = torch.full((rows, th.stride(0)), 7.0, dtype=torch.bfloat16, device="cuda")      # same row pitch, marked padding
+    th2[:, :vocab].copy_(th)
+    d_inplace = ops.softcap_ce_bwd(th2[:, :vocab], tt, lse, gs, 15.0, in_place=True)
+    assert torch.equal(d, d_inplace) and d.shape == (rows, vocab)
+    assert bool((th2[:, vocab:] == 7.0).all())                  # nothing is stored past the vocabulary
     ref = lo.softcap_cross_entropy_grad(x, t, 15.0, gscale=0.75)
     got = from_torch_bf16(d).astype(np.float64)
     rms = np.sqrt((ref ** 2).mean())
@@ -93,12 +98,28 @@ def test_autograd_function_matches_torch_ops():
 
 def test_rejects_bad_arguments():
     from train_gpt_b200 import ops
-    x = torch.zeros((2, 12), dtype=torch.bfloat16, device="cuda")
-    with pytest.raises(ValueError):
-        ops.softcap_ce_fwd(x, torch.zeros(2, dtype=torch.int32, device="cuda"), 15.0)     # vocab % 8
     with pytest.raises(TypeError):
         ops.softcap_ce_fwd(torch.zeros((2, 16), dtype=torch.bfloat16, device="cuda"),
                            torch.zeros(2, dtype=torch.int64, device="cuda"), 15.0)
     with pytest.raises(ValueError):
         ops.softcap_ce_fwd(torch.zeros((2, 16), dtype=torch.bfloat16, device="cuda"),
                            torch.zeros(2, dtype=torch.int32, device="cuda"), 0.0)          # cap must be positive
+
+
+def test_reference_default_vocabulary_through_autograd():
+    """vocab 50257 (train-gpt config.py:8, not a multiple of 8) through losses.capped_cross_entropy."""
+    from train_gpt_b200 import losses
+    torch.manual_seed(1)
+    logits = (torch.randn(2, 8, 50257, device="cuda") * 4).to(torch.bfloat16)
+    tg = torch.randint(0, 50257, (2, 8), device="cuda")
+    a = logits.clone().requires_grad_(True)
+    b = logits.clone().requires_grad_(True)
+    la = losses.capped_cross_entropy(a, tg, 15.0)
+    lb = torch.nn.functional.cross_entropy((15.0 * torch.tanh(b / 15.0)).float().view(-1, 50257), tg.view(-1))
+    la.backward()
+    lb.backward()
+    assert abs(float(la) - float(lb)) < 2e-5 * abs(float(lb))
+    ga, gb = a.grad.float(), b.grad.float()
+    assert ga.shape == gb.shape
+    rms = gb.pow(2).mean().sqrt()
+    assert bool(((ga - gb).abs() <= 2e-2 * gb.abs() + 1e-2 * rms).all())

@@ -72,3 +72,44 @@ def test_fused_mlp_follows_the_unfused_step(activation):
     else:
         assert torch.allclose(fused, plain, rtol=1e-3, atol=1e-4), (fused, plain)
         assert torch.allclose(fused_gn, plain_gn, rtol=1e-2, atol=1e-4), (fused_gn, plain_gn)
+
+
+def test_fp8_loss_curve_matches_bf16_at_the_training_configuration():
+    """The same 200-step comparison on the benchmark's training configuration itself: 24 layers, d_model 1024,
+    16 heads, MLP 4096 (GELU), vocabulary 50304, sequence 1024, batch 32 on one GPU, AdamW lr 3e-4 --
+    FP8 linears + fused norm (the step the benchmark times, graph-captured) against bf16 matmuls + the
+    torch restatement of the norm, same seed, same batches (train-gpt bench_fp8_norm.py:130-138 is this
+    2 x 2 comparison; test_overfit.py:33-45 the falling-loss check).  The token stream is the learnable
+    one: uniform tokens would hold both curves at ln(50304)."""
+    from train_gpt_b200.step import StepConfig, Trainer, synthetic_batch
+    steps, batch = 200, 32
+    base = StepConfig()
+    assert (base.n_layers, base.d_model, base.vocab_size, base.seq_len, base.d_ff) == (24, 1024, 50304, 1024, 4096)
+    batches = [synthetic_batch(base, batch, "cuda", seed=i, learnable=True) for i in range(steps)]
+
+    def run(cfg, graph):
+        tr = Trainer(cfg, torch.device("cuda", 0), world_size=1, seed=0, graph=graph)
+        losses, gnorms = [], []
+        for ids, tgt in batches:
+            loss, gn = tr.step(ids, tgt)
+            losses.append(float(loss))
+            gnorms.append(float(gn))
+        del tr
+        torch.cuda.empty_cache()
+        return torch.tensor(losses), torch.tensor(gnorms)
+
+    fp8, fp8_gn = run(StepConfig(mm="fp8", norm="fused"), graph=True)
+    ref, ref_gn = run(StepConfig(mm="bf16", norm="torch_reference", loss="torch", optimizer="torch"), graph=False)
+    assert torch.isfinite(fp8).all() and torch.isfinite(fp8_gn).all()
+    assert abs(float(ref[0]) - 10.83) < 0.2                                  # ln(50304) at initialisation (test_overfit.py:33-35)
+    assert float(ref[-50:].mean()) < float(ref[:5].mean()) - 1.0            # the curve actually falls
+    rel = ((_smooth(fp8) - _smooth(ref)).abs() / _smooth(ref)).max()
+    last = abs(float(fp8[-50:].mean()) - float(ref[-50:].mean())) / float(ref[-50:].mean())
+    gn_rel = ((_smooth(fp8_gn) - _smooth(ref_gn)).abs() / _smooth(ref_gn)).max()
+    raw = ((fp8 - ref).abs() / ref).max()
+    print(f"training configuration, 200 steps: loss {float(ref[0]):.3f} -> {float(ref[-50:].mean()):.3f} (bf16) / "
+          f"{float(fp8[-50:].mean()):.3f} (fp8); max relative deviation of the 20-step mean {float(rel):.4f}, "
+          f"of single steps {float(raw):.4f}, of the last-50 mean {last:.4f}; gradient norm {float(gn_rel):.4f}")
+    assert float(rel) < 0.01, float(rel)
+    assert last < 0.01, last
+    assert float(gn_rel) < 0.10, float(gn_rel)

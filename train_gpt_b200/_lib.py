@@ -44,6 +44,7 @@ SYMBOLS = {
     "tg_act_quantize_rowcol": (_i, [_p, _p, _i, _p, _p, _p, _p, _i64, _i64, _p]),
     "tg_quantize_block128": (_i, [_p, _p, _p, _i64, _i64, _p]),
     "tg_selftest_quantise_division": (_i, [_p, _p]),
+    "tg_selftest_bounded_wait": (_i, [_p, _p, _i64, _p]),
     "tg_rmsnorm_fwd": (_i, [_p, _p, _f, _p, _p, _i64, _i64, _i, _p]),
     "tg_rmsnorm_quant_fwd": (_i, [_p, _p, _f, _p, _p, _p, _p, _i64, _i64, _i, _p]),
     "tg_rmsnorm_bwd_scratch_bytes": (_i64, [_i64, _i64]),

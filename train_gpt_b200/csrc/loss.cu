@@ -94,7 +94,20 @@ softcap_ce_fwd_kernel(const __nv_bfloat16* __restrict__ logits, const int32_t* _
       z[2 * j] = sc.z_of_tanh(t0);
       z[2 * j + 1] = sc.z_of_tanh(t1);
     }
-    if (tanh_out != nullptr) *reinterpret_cast<uint4*>(tanh_out + row * ld_t + i) = to;
+    const int valid = vocab - i;        // < 8 only in the last piece of a vocabulary that is not a multiple of 8
+    if (valid < 8) {
+      // the piece was read whole (the row pitch is a multiple of 8 elements); columns past the
+      // vocabulary take no part in the softmax and are not written
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (j >= valid) z[j] = -INFINITY;
+      if (tanh_out != nullptr) {
+        const __nv_bfloat16* tv = reinterpret_cast<const __nv_bfloat16*>(&to);
+        for (int j = 0; j < valid; ++j) tanh_out[row * ld_t + i + j] = tv[j];
+      }
+    } else if (tanh_out != nullptr) {
+      *reinterpret_cast<uint4*>(tanh_out + row * ld_t + i) = to;
+    }
     float mx = z[0];
 #pragma unroll
     for (int j = 1; j < 8; ++j) mx = fmaxf(mx, z[j]);
@@ -149,7 +162,13 @@ softcap_ce_bwd_kernel(const __nv_bfloat16* tanh_in, const int32_t* __restrict__ 
       if (i + 2 * j + 1 == t) p1 -= 1.0f;
       op[j] = pack_bf16x2(p0 * g * __fmaf_rn(-t0, t0, 1.0f), p1 * g * __fmaf_rn(-t1, t1, 1.0f));
     }
-    *reinterpret_cast<uint4*>(d + row * ld_d + i) = o;
+    const int valid = vocab - i;
+    if (valid < 8) {                     // ragged last piece: nothing is stored past the vocabulary
+      const __nv_bfloat16* ov = reinterpret_cast<const __nv_bfloat16*>(&o);
+      for (int j = 0; j < valid; ++j) d[row * ld_d + i + j] = ov[j];
+    } else {
+      *reinterpret_cast<uint4*>(d + row * ld_d + i) = o;
+    }
   }
 }
 
@@ -159,7 +178,7 @@ using namespace tg;
 
 extern "C" int tg_softcap_ce_fwd(const void* logits, const int32_t* targets, float cap, void* tanh_out, float* lse,
                                  float* nll, int64_t rows, int64_t vocab, int64_t ld, int64_t ld_tanh, void* stream) {
-  if (rows < 0 || vocab <= 0 || vocab % 8 != 0 || ld % 8 != 0 || ld < vocab || vocab > INT32_MAX) return TG_ERR_SHAPE;
+  if (rows < 0 || vocab <= 0 || ld % 8 != 0 || ld < vocab || vocab > INT32_MAX) return TG_ERR_SHAPE;
   if (tanh_out != nullptr && (ld_tanh % 8 != 0 || ld_tanh < vocab)) return TG_ERR_SHAPE;
   if (!(cap > 0.0f)) return TG_ERR_SHAPE;
   if (rows > INT32_MAX) return TG_ERR_TOO_LARGE;
@@ -176,7 +195,7 @@ extern "C" int tg_softcap_ce_fwd(const void* logits, const int32_t* targets, flo
 extern "C" int tg_softcap_ce_bwd(const void* tanh_in, const int32_t* targets, const float* lse, const float* gscale,
                                  float cap, void* dlogits, int64_t rows, int64_t vocab, int64_t ld_tanh, int64_t ld_d,
                                  void* stream) {
-  if (rows < 0 || vocab <= 0 || vocab % 8 != 0 || ld_tanh % 8 != 0 || ld_d % 8 != 0 || ld_tanh < vocab || ld_d < vocab ||
+  if (rows < 0 || vocab <= 0 || ld_tanh % 8 != 0 || ld_d % 8 != 0 || ld_tanh < vocab || ld_d < vocab ||
       vocab > INT32_MAX)
     return TG_ERR_SHAPE;
   if (!(cap > 0.0f)) return TG_ERR_SHAPE;

@@ -30,14 +30,15 @@ class _SoftcapCE(torch.autograd.Function):
         th, t, lse = ctx.saved_tensors
         # the tanh buffer is this function's own: the gradient replaces it in place
         d = ops.softcap_ce_bwd(th, t, lse, g.to(torch.float32), ctx.cap, in_place=True)
-        return d.view(ctx.shape), None, None
+        return d.reshape(ctx.shape), None, None
 
 
 def capped_cross_entropy(logits: torch.Tensor, target_ids: torch.Tensor, cap: float) -> torch.Tensor:
     """Mean over tokens of -log_softmax(cap * tanh(logits / cap))[target] (model.py:97, losses.py:8-12).
 
     logits: (..., vocab) bf16, the unembedding GEMM's output BEFORE the cap; target_ids: (...)
-    integer.  vocab must be a multiple of 8.  Differentiable with respect to logits."""
+    integer.  Any vocabulary size (the reference's default 50257 is not a multiple of 8).
+    Differentiable with respect to logits."""
     if logits.shape[:-1] != target_ids.shape:
         raise ValueError(f"logits {tuple(logits.shape)} and target_ids {tuple(target_ids.shape)} do not match")
     return _SoftcapCE.apply(logits, target_ids, float(cap))

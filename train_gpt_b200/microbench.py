@@ -56,6 +56,9 @@ def _outlier_input(rows, cols, n, seed=0):
     return xs
 
 
+EMIT = True      # print one JSON line per kernel (the command-line mode); bench.py collects the dicts instead
+
+
 def _report(name, ms_med, ms_min, bytes_=None, flops=None, **extra):
     out = {"kernel": name, "ms_median": round(ms_med, 5), "ms_min": round(ms_min, 5)}
     if bytes_ is not None:
@@ -67,29 +70,34 @@ def _report(name, ms_med, ms_min, bytes_=None, flops=None, **extra):
         out["TFLOPs_median"] = round(flops / ms_med / 1e9, 1)
         out["TFLOPs_best"] = round(flops / ms_min / 1e9, 1)
     out.update(extra)
-    print(json.dumps(out), flush=True)
+    if EMIT:
+        print(json.dumps(out), flush=True)
     return out
 
 
-def bench_quant(rows, cols, warmup, iters):
+def bench_quant(rows, cols, warmup, iters, acts=True):
     E = rows * cols
     n = max(2, int(L2_BYTES * 2 // (E * 2)) + 1)
     xs = _outlier_input(rows, cols, n)
+    out = []
     m, b = _time(lambda i: ops.quantize_rowwise(xs[i]), n, warmup, iters, batch=10)
-    _report("quantize_rowwise", m, b, bytes_=3.03125 * E, shape=[rows, cols])
+    out.append(_report("quantize_rowwise", m, b, bytes_=3.03125 * E, shape=[rows, cols]))
     m, b = _time(lambda i: ops.quantize_colwise(xs[i]), n, warmup, iters, batch=10)
-    _report("quantize_colwise", m, b, bytes_=3.03125 * E, shape=[rows, cols])
+    out.append(_report("quantize_colwise", m, b, bytes_=3.03125 * E, shape=[rows, cols]))
     m, b = _time(lambda i: ops.quantize_block128(xs[i]), n, warmup, iters, batch=10)
-    _report("quantize_block128", m, b, bytes_=(3.0 + 4.0 / 16384) * E, shape=[rows, cols])
+    out.append(_report("quantize_block128", m, b, bytes_=(3.0 + 4.0 / 16384) * E, shape=[rows, cols]))
     m, b = _time(lambda i: ops.quantize_rowcol(xs[i]), n, warmup, iters, batch=10)
-    _report("quantize_rowcol", m, b, bytes_=(2.0 + 2 * 1.03125) * E, shape=[rows, cols])
+    out.append(_report("quantize_rowcol", m, b, bytes_=(2.0 + 2 * 1.03125) * E, shape=[rows, cols]))
+    if not acts:
+        return out
     # the MLP activation (or its gradient) computed inside the same pass
     gs = [(torch.randn(rows, cols, device="cuda") * 0.05).to(torch.bfloat16) for _ in range(n)]
     for act in ("relu2", "gelu"):
         m, b = _time(lambda i: ops.act_quantize_rowcol(xs[i], act), n, warmup, iters, batch=10)
-        _report(f"act_quantize_rowcol[{act}]", m, b, bytes_=(2.0 + 2 * 1.03125) * E, shape=[rows, cols])
+        out.append(_report(f"act_quantize_rowcol[{act}]", m, b, bytes_=(2.0 + 2 * 1.03125) * E, shape=[rows, cols]))
         m, b = _time(lambda i: ops.act_quantize_rowcol(xs[i], act + "_bwd", gs[i]), n, warmup, iters, batch=10)
-        _report(f"act_quantize_rowcol[{act}_bwd]", m, b, bytes_=(4.0 + 2 * 1.03125) * E, shape=[rows, cols])
+        out.append(_report(f"act_quantize_rowcol[{act}_bwd]", m, b, bytes_=(4.0 + 2 * 1.03125) * E, shape=[rows, cols]))
+    return out
 
 
 def bench_loss(rows, vocab, warmup, iters):
@@ -115,12 +123,14 @@ def bench_norm(rows, cols, warmup, iters):
     gs = [torch.randn(rows, cols, device="cuda").to(torch.bfloat16) for _ in range(n)]
     gamma = (1 + 0.1 * torch.randn(cols, device="cuda")).to(torch.bfloat16)
     eps = 1e-6
+    out = []
     m, b = _time(lambda i: ops.rmsnorm_quant_fwd(xs[i], gamma, eps), n, warmup, iters, batch=10)
-    _report("rmsnorm_quant_fwd", m, b, bytes_=3.03125 * E + 2 * cols, shape=[rows, cols])
+    out.append(_report("rmsnorm_quant_fwd", m, b, bytes_=3.03125 * E + 2 * cols, shape=[rows, cols]))
     m, b = _time(lambda i: ops.rmsnorm_fwd(xs[i], gamma, eps), n, warmup, iters, batch=10)
-    _report("rmsnorm_fwd", m, b, bytes_=4.0 * E + 2 * cols, shape=[rows, cols])
+    out.append(_report("rmsnorm_fwd", m, b, bytes_=4.0 * E + 2 * cols, shape=[rows, cols]))
     m, b = _time(lambda i: ops.rmsnorm_bwd(xs[i], gamma, gs[i], eps), n, warmup, iters, batch=10)
-    _report("rmsnorm_bwd", m, b, bytes_=6.0 * E + 4 * cols, shape=[rows, cols])
+    out.append(_report("rmsnorm_bwd", m, b, bytes_=6.0 * E + 4 * cols, shape=[rows, cols]))
+    return out
 
 
 def _gemm_case(M, N, K, mode, tile, warmup, iters, student_t=False):
@@ -159,6 +169,24 @@ def _gemm_case(M, N, K, mode, tile, warmup, iters, student_t=False):
                    weight_tile=f"{tile[0]}x{tile[1]}", pct_of_4500=round(2.0 * M * N * K / m / 1e9 / 45.0, 1))
 
 
+def bench_sweep(tile=(128, 128), warmup=5, iters=30):
+    """The shape sweep of the benchmark configurations (Student-t(3) activations): squares
+    M = N = K in {1024 .. 16384}, then skinny M in {16, 64, 256} with K = N = 8192, each as forward,
+    dgrad and wgrad.  A skinny case streams the 67 MB weight once, so it also reports that as GB/s."""
+    out = []
+    for n in (1024, 2048, 4096, 8192, 16384):
+        for mode in ("fwd", "dgrad", "wgrad"):
+            out.append(_gemm_case(n, n, n, mode, tile, warmup, max(5, iters // 3), student_t=True))
+    for m in (16, 64, 256):
+        for mode in ("fwd", "dgrad", "wgrad"):
+            r = _gemm_case(m, 8192, 8192, mode, tile, warmup, iters, student_t=True)
+            # fwd / dgrad read the e4m3 weight (K*N bytes); wgrad writes the bf16 gradient (2*K*N bytes)
+            stream = 8192 * 8192 * (2 if mode == "wgrad" else 1)
+            r["weight_stream_GBps"] = round(stream / r["ms_median"] / 1e6, 1)
+            out.append(r)
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("what", choices=["quant", "norm", "gemm", "loss", "sweep"])
@@ -184,13 +212,7 @@ def main():
         for mode in (["fwd", "dgrad", "wgrad"] if a.mode == "all" else [a.mode]):
             _gemm_case(a.m, a.n, a.k, mode, tile, a.warmup, a.iters)
     else:
-        # the shape sweep of the benchmark configurations: squares, then skinny M with K=N=8192
-        for n in (1024, 2048, 4096, 8192, 16384):
-            for mode in ("fwd", "dgrad", "wgrad"):
-                _gemm_case(n, n, n, mode, tile, a.warmup, max(5, a.iters // 3), student_t=True)
-        for m in (16, 64, 256):
-            for mode in ("fwd", "dgrad", "wgrad"):
-                _gemm_case(m, 8192, 8192, mode, tile, a.warmup, a.iters, student_t=True)
+        bench_sweep(tile, a.warmup, a.iters)
 
 
 if __name__ == "__main__":

@@ -139,6 +139,17 @@ def selftest_quantise_division(device="cuda"):
     return tuple(int(v) for v in counts.cpu())
 
 
+def selftest_bounded_wait(limit_cycles: int = 2_000_000, device="cuda"):
+    """Run the GEMM's give-up path (a barrier wait whose clock limit runs out -> abort flag -> every
+    role leaves -> tensor memory freed) on a barrier that is never arrived at.  Returns
+    (status code, [gave_up == 0, left_early == 2, ordinary_wait_ok == 1, teardown == 1])."""
+    status = torch.zeros((1,), dtype=torch.int32, device=device)
+    report = torch.zeros((4,), dtype=torch.int32, device=device)
+    _lib.check(_lib.load().tg_selftest_bounded_wait(_ptr(status), _ptr(report), int(limit_cycles), _stream()),
+               "tg_selftest_bounded_wait")
+    return int(status.item()), [int(v) for v in report.cpu()]
+
+
 # ---- RMSNorm ------------------------------------------------------------------------------
 
 def rmsnorm_fwd(x, gamma, eps: float, pure: bool = False, want_rnorm: bool = False):
@@ -209,25 +220,40 @@ def softcap_ce_fwd(logits, targets, cap: float, want_tanh: bool = True):
     if targets.numel() != rows:
         raise ValueError("one target per row")
     lib = _lib.load()
+    pitch = _cdiv(vocab, 8) * 8
+    if pitch != vocab:
+        # a vocabulary that is not a multiple of 8 (train-gpt's default 50257, config.py:8): the kernels
+        # want a 16-byte row pitch, so the rows move to a padded buffer; the pad columns are never used
+        padded = torch.empty((rows, pitch), dtype=torch.bfloat16, device=logits.device)
+        padded[:, :vocab].copy_(logits)
+        logits = padded
     nll = torch.empty((rows,), dtype=torch.float32, device=logits.device)
     lse = torch.empty((rows,), dtype=torch.float32, device=logits.device)
-    th = torch.empty_like(logits) if want_tanh else None
+    th = torch.empty((rows, pitch), dtype=torch.bfloat16, device=logits.device) if want_tanh else None
     _lib.check(lib.tg_softcap_ce_fwd(_ptr(logits), _ptr(targets), float(cap), _ptr(th), _ptr(lse), _ptr(nll),
-                                     rows, vocab, vocab, vocab, _stream()), "tg_softcap_ce_fwd")
+                                     rows, vocab, pitch, pitch, _stream()), "tg_softcap_ce_fwd")
+    if th is not None and pitch != vocab:
+        th = th[:, :vocab]                       # a view: the row pitch stays `pitch`
     return nll, lse, th
 
 
 def softcap_ce_bwd(th, targets, lse, gscale, cap: float, in_place: bool = False):
     """Gradient of mean(nll) w.r.t. the uncapped logits; `gscale` is a float32 device scalar
     (or None for 1).  in_place=True overwrites `th` with the gradient."""
-    th = _need(th, torch.bfloat16, "tanh")
+    if not th.is_cuda or th.dtype != torch.bfloat16 or th.dim() != 2 or th.stride(1) != 1:
+        raise TypeError("tanh must be a 2-D bf16 CUDA tensor with unit inner stride (as softcap_ce_fwd returns it)")
     rows, vocab = th.shape
-    d = th if in_place else torch.empty_like(th)
+    pitch = th.stride(0)                         # > vocab for a vocabulary that is not a multiple of 8
+    if in_place:
+        d, d_pitch = th, pitch
+    else:
+        d_pitch = _cdiv(vocab, 8) * 8
+        d = torch.empty((rows, d_pitch), dtype=torch.bfloat16, device=th.device)[:, :vocab]
     if gscale is not None:
         gscale = _need(gscale.reshape(1), torch.float32, "gscale")
     lib = _lib.load()
     _lib.check(lib.tg_softcap_ce_bwd(_ptr(th), _ptr(targets), _ptr(lse), _ptr(gscale), float(cap), _ptr(d),
-                                     rows, vocab, vocab, vocab, _stream()), "tg_softcap_ce_bwd")
+                                     rows, vocab, pitch, d_pitch, _stream()), "tg_softcap_ce_bwd")
     return d
 
 
@@ -267,6 +293,58 @@ def new_status(device) -> torch.Tensor:
     return torch.zeros((1,), dtype=torch.int32, device=device)
 
 
+# what the code a GEMM leaves in its status word says about which bounded wait ran out
+STATUS_ROLES = {
+    1: "the TMA producer waited for a free shared-memory stage",
+    2: "the MMA issuer waited for a free accumulator buffer",
+    3: "the MMA issuer waited for operands to land",
+    4: "the MMA issuer waited for its last instructions to retire",
+    5: "the promotion warps waited for an accumulator buffer to fill",
+}
+
+_status_words = {}
+
+
+def default_status(device) -> torch.Tensor:
+    """The status word every gemm_* call on `device` uses when the caller passes none: one word per
+    device, allocated once (so a captured CUDA graph keeps pointing at it)."""
+    dev = torch.device(device)
+    if dev.index is None:
+        dev = torch.device("cuda", torch.cuda.current_device())
+    word = _status_words.get(dev)
+    if word is None:
+        word = _status_words[dev] = new_status(dev)
+    return word
+
+
+def status_error(code: int):
+    """The exception for a non-zero GEMM status code, or None for 0."""
+    if code == 0:
+        return None
+    why = STATUS_ROLES.get(int(code), "unknown role")
+    return RuntimeError(f"block-scaled GEMM gave up on a bounded device wait (status {int(code)}: {why}); "
+                        "its output is incomplete")
+
+
+def check_status(status: torch.Tensor | None = None, device=None) -> None:
+    """Read a status word (the device's default one if none is given; this synchronises with the
+    work queued on it) and raise if a GEMM's bounded wait ran out since it was last zero.  The
+    word is cleared so that the next check reports only newer failures."""
+    word = status if status is not None else default_status(device if device is not None else "cuda")
+    code = int(word.item())
+    if code != 0:
+        word.zero_()
+        raise status_error(code)
+
+
+def poison_if_failed(value: torch.Tensor, status: torch.Tensor | None = None) -> torch.Tensor:
+    """`value` with NaN in place of every element if the status word is non-zero -- a device-side
+    select, no synchronisation, capturable in a CUDA graph.  The training step passes its loss through
+    this, so a GEMM that gave up surfaces as a NaN loss instead of a silently wrong one."""
+    word = status if status is not None else default_status(value.device)
+    return torch.where(word.reshape(()) != 0, torch.full_like(value, float("nan")), value)
+
+
 def gemm_blockscaled(a, b, sa, sb, *, M, N, K, a_major, b_major, sa_strides, sb_strides, sb_gran_n,
                      out_dtype=torch.bfloat16, status=None, out=None, split=True):
     """Raw call of tg_gemm_fp8_blockscaled; see include/train_gpt_b200.h for the argument
@@ -278,6 +356,8 @@ def gemm_blockscaled(a, b, sa, sb, *, M, N, K, a_major, b_major, sa_strides, sb_
             raise TypeError(f"{n} must be a 2-D e4m3 tensor with unit inner stride")
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    if status is None:
+        status = default_status(a.device)      # never NULL: a bounded wait that runs out must leave a trace
     args = GemmArgs(
         a=_ptr(a), b=_ptr(b), lda=a.stride(0), ldb=b.stride(0), a_major=a_major, b_major=b_major,
         sa=_ptr(sa), sa_stride_m=sa_strides[0], sa_stride_kb=sa_strides[1],

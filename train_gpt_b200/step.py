@@ -246,6 +246,8 @@ class Trainer:
         loss = self.model.loss(ids, targets)
         loss.backward()
         self.buckets.finish()
+        if torch.device(self.device).type == "cuda":
+            loss = ops.poison_if_failed(loss.detach())        # a GEMM whose bounded wait ran out -> NaN loss
         if self._fused_opt:
             gnorm = self.opt.global_norm(self.buckets.flat)                          # train.py:132
             self.opt.step(gnorm)                                                     # train.py:133-134
@@ -325,16 +327,17 @@ def step_flops(cfg: StepConfig, tokens: int) -> float:
     return 6.0 * cfg.n_layers * layer_params * tokens
 
 
-def bench_train_step(world: int, rank: int, device, dist, steps: int = 5, warmup: int = 3, batch_per_gpu: int = 32,
+def bench_train_step(world: int, rank: int, device, dist, steps: int = 20, warmup: int = 3, batch_per_gpu: int = 32,
                      cfg: StepConfig = StepConfig(), graph: bool = True):
     """Tokens/s of the data-parallel step (the benchmark's training configuration): batch sharded by rank,
     weights replicated, gradients all-reduced per layer bucket over NCCL."""
-    batches = [synthetic_batch(cfg, batch_per_gpu, device, seed=1000 * rank + i) for i in range(2)]
+    # a fresh batch every step (nothing to memorise: uniform tokens hold the loss near ln(vocab))
+    batches = [synthetic_batch(cfg, batch_per_gpu, device, seed=100003 * rank + i) for i in range(warmup + steps)]
     graph_error = None
     tr = Trainer(cfg, device, world_size=world, graph=graph)
     try:
         for i in range(warmup):
-            loss, _ = tr.step(*batches[i % 2])
+            loss, _ = tr.step(*batches[i])
     except RuntimeError as e:
         if not graph:
             raise
@@ -344,14 +347,14 @@ def bench_train_step(world: int, rank: int, device, dist, steps: int = 5, warmup
         torch.cuda.synchronize()
         tr = Trainer(cfg, device, world_size=world, graph=False)
         for i in range(warmup):
-            loss, _ = tr.step(*batches[i % 2])
+            loss, _ = tr.step(*batches[i])
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(steps):
-        loss, gnorm = tr.step(*batches[i % 2])
+        loss, gnorm = tr.step(*batches[warmup + i])
     e1.record()
     if world > 1:
         dist.barrier()
