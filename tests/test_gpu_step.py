@@ -79,13 +79,18 @@ def test_fp8_loss_curve_matches_bf16_at_the_training_configuration():
     16 heads, MLP 4096 (GELU), vocabulary 50304, sequence 1024, batch 32 on one GPU, AdamW lr 3e-4 --
     FP8 linears + fused norm (the step the benchmark times, graph-captured) against bf16 matmuls + the
     torch restatement of the norm, same seed, same batches (train-gpt bench_fp8_norm.py:130-138 is this
-    2 x 2 comparison; test_overfit.py:33-45 the falling-loss check).  The token stream is the learnable
-    one: uniform tokens would hold both curves at ln(50304)."""
+    2 x 2 comparison; test_overfit.py:33-45 the falling-loss check).
+
+    The token stream is the Zipf one (independent tokens with Zipf-like frequencies): uniform tokens would
+    hold both curves at ln(50304), and the bigram stream of the small-model test has, at this size and
+    learning rate, a sharp transition whose TIMING is chaotic -- two bf16 runs that differ only in which
+    AdamW implementation they use separate by more than 1 % there, so no FP8-vs-bf16 bar can be read off it.
+    On the Zipf stream the loss falls smoothly from ln(vocab) = 10.8 to the stream's entropy (8.69)."""
     from train_gpt_b200.step import StepConfig, Trainer, synthetic_batch
     steps, batch = 200, 32
     base = StepConfig()
     assert (base.n_layers, base.d_model, base.vocab_size, base.seq_len, base.d_ff) == (24, 1024, 50304, 1024, 4096)
-    batches = [synthetic_batch(base, batch, "cuda", seed=i, learnable=True) for i in range(steps)]
+    batches = [synthetic_batch(base, batch, "cuda", seed=i, learnable="zipf") for i in range(steps)]
 
     def run(cfg, graph):
         tr = Trainer(cfg, torch.device("cuda", 0), world_size=1, seed=0, graph=graph)
@@ -101,7 +106,7 @@ def test_fp8_loss_curve_matches_bf16_at_the_training_configuration():
     fp8, fp8_gn = run(StepConfig(mm="fp8", norm="fused"), graph=True)
     ref, ref_gn = run(StepConfig(mm="bf16", norm="torch_reference", loss="torch", optimizer="torch"), graph=False)
     assert torch.isfinite(fp8).all() and torch.isfinite(fp8_gn).all()
-    assert abs(float(ref[0]) - 10.83) < 0.2                                  # ln(50304) at initialisation (test_overfit.py:33-35)
+    assert abs(float(ref[0]) - 10.83) < 0.35                                 # about ln(50304) at initialisation (test_overfit.py:33-35)
     assert float(ref[-50:].mean()) < float(ref[:5].mean()) - 1.0            # the curve actually falls
     rel = ((_smooth(fp8) - _smooth(ref)).abs() / _smooth(ref)).max()
     last = abs(float(fp8[-50:].mean()) - float(ref[-50:].mean())) / float(ref[-50:].mean())
@@ -111,5 +116,6 @@ def test_fp8_loss_curve_matches_bf16_at_the_training_configuration():
           f"{float(fp8[-50:].mean()):.3f} (fp8); max relative deviation of the 20-step mean {float(rel):.4f}, "
           f"of single steps {float(raw):.4f}, of the last-50 mean {last:.4f}; gradient norm {float(gn_rel):.4f}")
     assert float(rel) < 0.01, float(rel)
+    assert float(raw) < 0.01, float(raw)                                     # unsmoothed, step by step, as well
     assert last < 0.01, last
     assert float(gn_rel) < 0.10, float(gn_rel)

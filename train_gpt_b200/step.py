@@ -301,13 +301,31 @@ class Trainer:
         return self._loss, self._gnorm
 
 
-def synthetic_batch(cfg: StepConfig, batch: int, device, seed: int, learnable: bool = False):
+_ZIPF_CACHE = {}
+
+
+def _zipf_table(vocab: int):
+    """Token probabilities proportional to 1 / (rank + 10), ranks assigned by a fixed random permutation."""
+    if vocab not in _ZIPF_CACHE:
+        g = torch.Generator().manual_seed(4321)
+        p = 1.0 / (torch.arange(vocab, dtype=torch.float64) + 10.0)
+        _ZIPF_CACHE[vocab] = (p / p.sum())[torch.randperm(vocab, generator=g)]
+    return _ZIPF_CACHE[vocab]
+
+
+def synthetic_batch(cfg: StepConfig, batch: int, device, seed: int, learnable=False):
     """Seeded tokens uniform over the vocabulary (data.py:10-11's random windows stand-in).
-    `learnable` draws sequences from a fixed random bigram map instead, so that a short run
-    has a falling loss curve to compare."""
+    `learnable` selects a stream a short run can learn, so that its loss curve falls:
+      True / "bigram"  sequences from a fixed random bigram map with 10 % noise (a sharp transition once
+                       the map is found: good for "does it train", chaotic in WHEN it falls);
+      "zipf"           independent tokens with Zipf-like frequencies (a smooth fall from ln(vocab) to the
+                       distribution's entropy: the stream loss-curve comparisons use)."""
     g = torch.Generator(device="cpu").manual_seed(seed)
     if not learnable:
         ids = torch.randint(0, cfg.vocab_size, (batch, cfg.seq_len + 1), generator=g)
+    elif learnable == "zipf":
+        ids = torch.multinomial(_zipf_table(cfg.vocab_size), batch * (cfg.seq_len + 1), replacement=True,
+                                generator=g).view(batch, cfg.seq_len + 1)
     else:
         table = torch.randint(0, cfg.vocab_size, (cfg.vocab_size,), generator=torch.Generator().manual_seed(1234))
         ids = torch.empty((batch, cfg.seq_len + 1), dtype=torch.long)
