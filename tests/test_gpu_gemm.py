@@ -226,3 +226,58 @@ def test_bounded_wait_gives_up_and_the_cta_tears_down():
                                 torch.ones(128, 4, dtype=torch.bfloat16, device="cuda"))
     assert bool((y.float() == 128.0).all())
     ops.check_status(device="cuda")                             # the real GEMMs' shared status word stayed 0
+
+
+@pytest.mark.parametrize("M,K,N", [(8, 1024, 1024), (16, 2048, 1536), (64, 1024, 2048), (136, 1024, 1152), (192, 1024, 1024),
+                                    (200, 1024, 1280), (256, 2048, 1024)])
+@pytest.mark.parametrize("tile", [(128, 1), (128, 128)])
+def test_few_tokens_run_transposed(M, K, N, tile):
+    """M <= 128 tokens against a wide weight: the library runs the problem with its operands swapped (the weight's
+    N on the MMA's 128 rows, the contraction cut across SMs, a transposing reduce at the end); the larger M here
+    sit just past that switch.  Forward and dgrad, bf16 and float32 outputs, against the oracle; without
+    workspace the same call takes the ordinary path."""
+    from train_gpt_b200 import fp8, ops
+    rng = np.random.default_rng(M * 5 + K + N)
+    a = normal_bf16(rng, (M, K), outlier_p=1e-3)
+    b = normal_bf16(rng, (K, N), std=0.02)
+    g = normal_bf16(rng, (M, N))
+    st = ops.new_status("cuda")
+    a_q, a_s = ops.quantize_rowwise(to_torch_bf16(a))
+    w_q, w_s = fp8.quantize_weight(to_torch_bf16(b), tile)
+    y = ops.gemm_fwd(a_q, a_s, w_q, w_s, tile, status=st)
+    if M <= 128:
+        assert ops.last_gemm_kernel_launches == 2          # the transposed path: GEMM + transposing reduce
+    ref = fo.block_scaled_matmul(a, b, weight_tile=tile)
+    _close(from_torch_bf16(y), ref)
+    y32 = ops.gemm_fwd(a_q, a_s, w_q, w_s, tile, out_dtype=torch.float32, status=st)
+    assert fo.rel_frobenius(from_torch_bf16(y32.to(torch.bfloat16)), ref) < 2e-3
+    # the ordinary path (no workspace) gives the same numbers up to float32 summation order
+    M_, N_ = y.shape
+    sb_str = (1, N) if tile == (128, 1) else (1, w_s.shape[1])
+    from train_gpt_b200 import _lib
+    y_plain = ops.gemm_blockscaled(a_q, w_q, a_s, w_s, M=M, N=N, K=K, a_major=_lib.TG_MAJOR_K, b_major=_lib.TG_MAJOR_MN,
+                                   sa_strides=(a_s.shape[1], 1), sb_strides=sb_str, sb_gran_n=1 if tile == (128, 1) else 128,
+                                   out_dtype=torch.float32, status=st, split=False)
+    assert torch.allclose(y32, y_plain, rtol=1e-5, atol=1e-5 * float(y_plain.abs().max()))
+    # dgrad: dx = g W^T, the weight quantised along N
+    g_q, g_s = ops.quantize_rowwise(to_torch_bf16(g))
+    wd_q, wd_s = ops.quantize_rowwise(to_torch_bf16(b)) if tile == (128, 1) else (w_q, w_s)
+    dx = ops.gemm_dgrad(g_q, g_s, wd_q, wd_s, tile, status=st)
+    da_ref, _ = fo.backward_fp8(a, b, g, weight_tile=tile)
+    _close(from_torch_bf16(dx), da_ref)
+    torch.cuda.synchronize()
+    _status_ok(st)
+
+
+def test_wider_inputs_are_taken_only_if_they_hold_bf16_values():
+    """The reference upcasts bf16 operands to float32 before quantising (fp8.py:66,68); here a float32
+    operand is accepted when it is such an upcast and refused (not silently rounded) otherwise."""
+    from train_gpt_b200 import fp8
+    a = torch.randn(8, 128, device="cuda").to(torch.bfloat16)
+    b = (0.02 * torch.randn(128, 16, device="cuda")).to(torch.bfloat16)
+    y = fp8.block_scaled_matmul(a, b)
+    assert torch.equal(fp8.block_scaled_matmul(a.float(), b.float()), y)
+    with pytest.raises(TypeError, match="bf16 cannot hold"):
+        fp8.block_scaled_matmul(a.float() + 1e-4, b)
+    with pytest.raises(TypeError, match="bf16 cannot hold"):
+        fp8._quantize_to_fp8(torch.full((2, 128), 1.0 + 2.0 ** -12, device="cuda"))

@@ -57,6 +57,7 @@ def test_static_scratch_matches_caller_scratch_twice_in_a_row():
     _call_pair(lib, 3000, 2048, seed=1)      # fills the built-in scratch with this call's partial sums
     _call_pair(lib, 777, 1024, seed=2)       # a different shape on top of the stale contents
     _call_pair(lib, 3000, 2048, seed=3)
+    _call_pair(lib, 96, 4096, seed=4)        # a row split over two warps (wider than 2048) still fits the 4 MiB for few rows
 
 
 def test_static_scratch_refuses_what_does_not_fit():

@@ -11,6 +11,8 @@
 // sum-of-squares pass and the normalise/quantise pass: x is read from HBM once.
 #include <cstdlib>
 
+#include <atomic>
+
 #include "common.cuh"
 
 namespace tg {
@@ -561,7 +563,7 @@ extern "C" int tg_rmsnorm_bwd_static(const void* x, const void* gamma, const voi
                                      void* dx, void* dgamma, int64_t rows, int64_t cols, void* stream) {
   // In host code `g_bwd_scratch` is only a handle for the runtime, not an address a kernel
   // can use; the device address is looked up once per device, with that device current.
-  static void* dev_ptr[64] = {};
+  static std::atomic<void*> dev_ptr[64] = {};   // written once per device; host threads may race to be first
   if (rows < 0 || cols <= 0 || cols % 8 != 0) return TG_ERR_SHAPE;
   const int64_t need = tg_rmsnorm_bwd_scratch_bytes(rows, cols);
   if (need > tg::kStaticBwdScratchBytes) {
@@ -574,10 +576,10 @@ extern "C" int tg_rmsnorm_bwd_static(const void* x, const void* gamma, const voi
   int dev = 0;
   TG_CUDA_CHECK(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return TG_ERR_SHAPE;
-  void* scratch = dev_ptr[dev];
+  void* scratch = dev_ptr[dev].load(std::memory_order_acquire);
   if (scratch == nullptr) {
     TG_CUDA_CHECK(cudaGetSymbolAddress(&scratch, tg::g_bwd_scratch));
-    dev_ptr[dev] = scratch;  // racing first calls on one device store the same value
+    dev_ptr[dev].store(scratch, std::memory_order_release);  // racing first calls on one device store the same value
   }
   return tg_rmsnorm_bwd(x, gamma, g, eps, dx, dgamma, scratch, rows, cols, stream);
 }

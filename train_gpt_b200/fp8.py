@@ -23,20 +23,35 @@ E4M3_MAX = 448.0        # fp8.py:26
 DEFAULT_BLOCK_K = 128   # fp8.py:27
 
 
+def _as_bf16(t: torch.Tensor, name: str) -> torch.Tensor:
+    """bf16 view of an operand.  The reference upcasts its bf16 operands to float32 before quantising
+    (fp8.py:66,68); these kernels take the bf16 directly.  A wider tensor is taken only if the narrowing
+    is exact, so that scales and bytes cannot silently differ from the reference's."""
+    if t.dtype == torch.bfloat16:
+        return t
+    if not t.is_floating_point():
+        raise TypeError(f"{name} must be a floating-point tensor, got {t.dtype}")
+    n = t.to(torch.bfloat16)
+    if not bool((n.to(t.dtype) == t).all()):
+        raise TypeError(f"{name} is {t.dtype} with values bf16 cannot hold: the sm_100a kernels quantise bf16 operands "
+                        "(as the reference's model does); cast explicitly if that rounding is intended")
+    return n
+
+
 def _check_block(block_k: int):
     if block_k != DEFAULT_BLOCK_K:
         raise ValueError(f"block_k={block_k} is not supported by the sm_100a kernels (only {DEFAULT_BLOCK_K})")
 
 
 def _quantize_to_fp8(x_f32: torch.Tensor, block_k: int = DEFAULT_BLOCK_K):
-    """fp8.py:39-47.  The reference only ever passes an upcast bf16 tensor (fp8.py:66,68);
-    a float32 argument is therefore narrowed back to bf16 (exact for such inputs)."""
+    """fp8.py:39-47.  The reference only ever passes an upcast bf16 tensor (fp8.py:66,68), and the
+    kernels read bf16: a float32 argument is accepted only if it holds bf16 values exactly (it is then
+    narrowed back without loss); anything else raises rather than being rounded silently."""
     K = x_f32.shape[-1]
     if K % block_k != 0:
         raise ValueError(f"K={K} not divisible by block_k={block_k}")
     _check_block(block_k)
-    x = x_f32 if x_f32.dtype == torch.bfloat16 else x_f32.to(torch.bfloat16)
-    return ops.quantize_rowwise(x)
+    return ops.quantize_rowwise(_as_bf16(x_f32, "x"))
 
 
 class QuantizedActivation:
@@ -90,12 +105,12 @@ def _fp8_forward(a, b, block_k=DEFAULT_BLOCK_K, weight_tile=(128, 1), a_quantize
     K, N = _validate(a, b, block_k)
     leading = a.shape[:-1]
     if a_quantized is None:
-        a_q, a_s = ops.quantize_rowwise(a.reshape(-1, K).to(torch.bfloat16))
+        a_q, a_s = ops.quantize_rowwise(_as_bf16(a.reshape(-1, K), "a"))
     elif isinstance(a_quantized, QuantizedActivation):
         a_q, a_s = a_quantized.rowwise()
     else:
         a_q, a_s = a_quantized[0].reshape(-1, K), a_quantized[1].reshape(-1, K // block_k)
-    b = b.to(torch.bfloat16)
+    b = _as_bf16(b, "b")
     pad = (-N) % 16 if tuple(weight_tile) == (128, 1) else 0
     if pad:
         # the TMA row pitch of the (K, N) weight must be a multiple of 16 bytes: widen with
