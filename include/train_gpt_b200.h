@@ -40,6 +40,15 @@ extern "C" {
 /* Library version (major*100 + minor). */
 int tg_version(void);
 
+/* No counterpart in the reference.  The GEMM is a persistent kernel: one 200 KB thread block per SM
+ * for as long as the launch lasts.  A collective that should run BESIDE it (the data-parallel
+ * gradient all-reduce overlapping the rest of the backward pass) finds no SM to start on until a
+ * GEMM ends, and a GEMM launched after it finds some SMs taken and runs a ragged second wave.
+ * Reserving n SMs makes every later GEMM launch of this process use at most (SM count - n) thread
+ * blocks.  0 (the default) uses them all; n is clamped to 0 .. 64.  Returns the previous value.
+ * Process-wide, host-side only, thread-safe; takes effect at the next launch.                  */
+int tg_set_gemm_reserved_sms(int n);
+
 /* Text of the last CUDA error a launcher of this library saw on the calling thread
  * ("" if none).  The pointer stays valid until the next failing call on that thread. */
 const char* tg_last_cuda_error(void);

@@ -33,6 +33,8 @@ def test_header_symbols_are_exported_and_bound(lib):
         assert n in _lib.SYMBOLS, f"{n} has no ctypes prototype"
     assert sorted(_lib.SYMBOLS) == names
     assert lib.tg_version() >= 100
+    assert lib.tg_set_gemm_reserved_sms(8) == 0 and lib.tg_set_gemm_reserved_sms(1000) == 8
+    assert lib.tg_set_gemm_reserved_sms(0) == 64          # clamped; back to the default
 
 
 def test_gemm_args_struct_matches_header_layout():

@@ -15,7 +15,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 FFI = os.path.join(ROOT, "train_gpt_b200", "xla_ffi")
 
 # entry points that are queries or self-tests, not kernels an XLA program would call
-NOT_BOUND = {"tg_version", "tg_last_cuda_error", "tg_selftest_quantise_division", "tg_selftest_bounded_wait",
+NOT_BOUND = {"tg_version", "tg_last_cuda_error", "tg_set_gemm_reserved_sms", "tg_selftest_quantise_division", "tg_selftest_bounded_wait",
              "tg_rmsnorm_bwd_static_max_scratch_bytes"}
 
 

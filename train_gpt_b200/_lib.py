@@ -38,6 +38,7 @@ class GemmArgs(C.Structure):
 SYMBOLS = {
     "tg_version": (_i, []),
     "tg_last_cuda_error": (C.c_char_p, []),
+    "tg_set_gemm_reserved_sms": (_i, [_i]),
     "tg_quantize_rowwise": (_i, [_p, _p, _p, _i64, _i64, _p]),
     "tg_quantize_colwise": (_i, [_p, _p, _p, _i64, _i64, _p]),
     "tg_quantize_rowcol": (_i, [_p, _p, _p, _p, _p, _i64, _i64, _p]),

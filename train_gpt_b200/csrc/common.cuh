@@ -19,6 +19,8 @@ int record_cuda_error(cudaError_t e, const char* where);
 // TG_OK if the current device is compute capability 10.x, else TG_ERR_ARCH.
 int check_arch();
 int sm_count();
+// SMs a persistent GEMM grid may occupy: sm_count() minus what tg_set_gemm_reserved_sms left for others.
+int gemm_sms();
 
 #define TG_CUDA_CHECK(expr)                                        \
   do {                                                             \

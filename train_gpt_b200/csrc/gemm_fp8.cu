@@ -833,7 +833,7 @@ static int launch_gemm(const tg_gemm_args* a, GemmParams p, cudaStream_t st) {
   p.band = p.tiles_m < kBandRows ? p.tiles_m : kBandRows;
   const int64_t n_items = int64_t(p.tiles_m) * p.tiles_n * p.ksplit;
   if (n_items > INT32_MAX || n_items * p.nkb > INT32_MAX) return TG_ERR_TOO_LARGE;
-  const int sms = sm_count();
+  const int sms = gemm_sms();
   const int grid = int(n_items < sms ? n_items : sms);
   // the attribute is per device: set it once for each device this instantiation runs on
   static bool attr_set[64] = {};
@@ -926,7 +926,7 @@ static SplitPlan plan_split(const tg_gemm_args* a, int bn) {
   if (a->K % BK != 0) return pl;
   const int64_t nkb = a->K / BK;
   const int64_t tiles = ((a->M + BM - 1) / BM) * ((a->N + bn - 1) / bn);
-  const int sms = sm_count();
+  const int sms = gemm_sms();
   if (sms <= 0) return pl;
   double best = 0.0;
   for (int S = 1; S <= 8; S *= 2) {
@@ -962,7 +962,7 @@ static SkinnyPlan plan_skinny(const tg_gemm_args* a) {
   SkinnyPlan pl = {false, 0, 1, 0, 0};
   if (a->M > 128 || a->M % 8 != 0 || a->N < 1024 || a->K % BK != 0 || a->K < 1024) return pl;
   if (a->a_major != TG_MAJOR_K) return pl;          // the activation must be [M][K]: it becomes the K-major B operand
-  const int sms = sm_count();
+  const int sms = gemm_sms();
   if (sms <= 0) return pl;
   pl.on = true;
   pl.bn = 128;

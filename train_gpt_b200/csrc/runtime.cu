@@ -2,6 +2,8 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <atomic>
+
 #include "common.cuh"
 
 namespace tg {
@@ -47,8 +49,21 @@ int sm_count() {
   return d.sms;
 }
 
+static std::atomic<int> g_reserved_sms{0};
+
+int gemm_sms() {
+  const int n = sm_count() - g_reserved_sms.load(std::memory_order_relaxed);
+  return n < 1 ? 1 : n;
+}
+
 }  // namespace tg
 
-extern "C" int tg_version(void) { return 100; }
+extern "C" int tg_version(void) { return 101; }
+
+extern "C" int tg_set_gemm_reserved_sms(int n) {
+  if (n < 0) n = 0;
+  if (n > 64) n = 64;
+  return tg::g_reserved_sms.exchange(n, std::memory_order_relaxed);
+}
 
 extern "C" const char* tg_last_cuda_error(void) { return tg::g_err; }

@@ -33,6 +33,7 @@ class GradBuckets:
         self._sizes: List[int] = []
         self._handles = []
         self._hooks = []
+        self._nccl = world_size > 1 and dist.is_initialized() and dist.get_backend(group) == "nccl"
         for bi, params in enumerate(buckets):
             params = [p for p in params if p.requires_grad]
             if not params:
@@ -63,7 +64,9 @@ class GradBuckets:
 
     def _launch(self, bi: int):
         if self.world_size > 1:
-            self._handles.append(dist.all_reduce(self.flat[bi], op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+            # NCCL averages inside the collective; gloo (the CPU tests) has no AVG: sum, then scale in finish()
+            op = dist.ReduceOp.AVG if (self.average and self._nccl) else dist.ReduceOp.SUM
+            self._handles.append(dist.all_reduce(self.flat[bi], op=op, group=self.group, async_op=True))
 
     def finish(self):
         """Wait for every bucket's exchange, turn sums into means, re-arm for the next step."""
@@ -74,7 +77,7 @@ class GradBuckets:
         for h in self._handles:
             h.wait()
         self._handles.clear()
-        if self.world_size > 1 and self.average:
+        if self.world_size > 1 and self.average and not self._nccl:
             for f in self.flat:
                 if f.numel():
                     f.mul_(1.0 / self.world_size)

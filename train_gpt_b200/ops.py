@@ -288,6 +288,12 @@ def adamw_step(p, g, m, v, step, lr, b1=0.9, b2=0.999, eps=1e-8, weight_decay=0.
 
 # ---- GEMM ---------------------------------------------------------------------------------
 
+def set_gemm_reserved_sms(n: int) -> int:
+    """Leave `n` SMs free of the persistent GEMM's thread blocks from the next launch on (for a collective
+    that overlaps the GEMMs: the data-parallel gradient all-reduce).  Returns the previous setting."""
+    return int(_lib.load().tg_set_gemm_reserved_sms(int(n)))
+
+
 def new_status(device) -> torch.Tensor:
     """A zeroed device word for the GEMM's bounded-wait status."""
     return torch.zeros((1,), dtype=torch.int32, device=device)

@@ -56,6 +56,11 @@ class StepConfig:
     clip_norm: float = 1.0
 
 
+# SMs kept free of GEMM thread blocks while gradients are exchanged.  Measured on 2 GPUs (ms per step, graph replay):
+# 0 -> 99.4, 8 -> 101.6, 16 -> 101.7, 32 -> 103.8: the all-reduce kernels themselves shrink (6.3 -> 2.8 ms summed over a
+# step) but they were hidden behind the backward pass anyway, and the GEMMs lose more than that.  So: none.
+RESERVED_SMS_DP = 0
+
 SMALL = dict(vocab_size=256, seq_len=128, d_model=128, n_layers=2, n_heads=4, head_dim=32, d_ff=512)  # config.py:32-40
 
 
@@ -226,8 +231,13 @@ class Trainer:
     state are restored after them, so a captured run follows the same trajectory as an eager one.
     """
 
-    def __init__(self, cfg: StepConfig, device, world_size: int = 1, seed: int = 0, graph: bool = False):
+    def __init__(self, cfg: StepConfig, device, world_size: int = 1, seed: int = 0, graph: bool = False,
+                 reserve_sms: int | None = None):
         self.cfg, self.device, self.world = cfg, device, world_size
+        # With more than one rank the bucket all-reduces run beside the backward pass's GEMMs, which are
+        # persistent kernels holding every SM: leave NCCL a few SMs to start on (see tg_set_gemm_reserved_sms).
+        if torch.device(device).type == "cuda":
+            ops.set_gemm_reserved_sms(RESERVED_SMS_DP if (reserve_sms is None and world_size > 1) else int(reserve_sms or 0))
         self.model = GPT(cfg, device, seed)                     # same seed on every rank: replicated weights
         self.buckets = GradBuckets(self.model.buckets(), world_size)
         on_gpu = torch.device(device).type == "cuda"
@@ -346,13 +356,13 @@ def step_flops(cfg: StepConfig, tokens: int) -> float:
 
 
 def bench_train_step(world: int, rank: int, device, dist, steps: int = 20, warmup: int = 3, batch_per_gpu: int = 32,
-                     cfg: StepConfig = StepConfig(), graph: bool = True):
+                     cfg: StepConfig = StepConfig(), graph: bool = True, reserve_sms: int | None = None):
     """Tokens/s of the data-parallel step (the benchmark's training configuration): batch sharded by rank,
     weights replicated, gradients all-reduced per layer bucket over NCCL."""
     # a fresh batch every step (nothing to memorise: uniform tokens hold the loss near ln(vocab))
     batches = [synthetic_batch(cfg, batch_per_gpu, device, seed=100003 * rank + i) for i in range(warmup + steps)]
     graph_error = None
-    tr = Trainer(cfg, device, world_size=world, graph=graph)
+    tr = Trainer(cfg, device, world_size=world, graph=graph, reserve_sms=reserve_sms)
     try:
         for i in range(warmup):
             loss, _ = tr.step(*batches[i])
@@ -363,7 +373,7 @@ def bench_train_step(world: int, rank: int, device, dist, steps: int = 20, warmu
         graph_error, graph = str(e).splitlines()[0][:200], False
         del tr
         torch.cuda.synchronize()
-        tr = Trainer(cfg, device, world_size=world, graph=False)
+        tr = Trainer(cfg, device, world_size=world, graph=False, reserve_sms=reserve_sms)
         for i in range(warmup):
             loss, _ = tr.step(*batches[i])
     if world > 1:
@@ -391,7 +401,7 @@ def bench_train_step(world: int, rank: int, device, dist, steps: int = 20, warmu
         "config": {"layers": cfg.n_layers, "d_model": cfg.d_model, "heads": cfg.n_heads, "d_ff": cfg.d_ff,
                    "vocab": cfg.vocab_size, "seq": cfg.seq_len, "batch_per_gpu": batch_per_gpu, "activation": cfg.activation,
                    "mm": cfg.mm, "norm": cfg.norm, "optimizer": "AdamW lr 3e-4", "parallelism": f"dp{world}", "cuda_graph": bool(graph), "cuda_graph_error": graph_error,
-                   "grad_bytes_allreduced": tr.buckets.bytes(), "data": "tokens uniform over the vocabulary (seeded)"},
+                   "grad_bytes_allreduced": tr.buckets.bytes(), "sms_reserved_for_nccl": ops.set_gemm_reserved_sms(0), "data": "tokens uniform over the vocabulary (seeded)"},
     }
 
 
