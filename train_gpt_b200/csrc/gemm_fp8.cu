@@ -15,24 +15,29 @@
 // time per issued instruction, which is what keeps the single-thread issue loop and the
 // barrier round trips off the critical path.
 //
-// Warp roles in the CTA (persistent, one CTA per SM, tiles round-robin):
+// Warp roles in the CTA (persistent, one CTA per SM; work items numbered in bands, see tile_coords):
 //   warps 0..P-1 promotion + epilogue (P = 16, or 12 for 192-column tiles); warp w may touch TMEM
 //                lanes 32*(w%4).. (a hardware rule) and owns accumulator columns (BN/4)*(w/4)..;
-//                four warps per scheduler hide each other's TMEM-load latency.  bf16 tiles leave
-//                through one bulk tensor store per warp (registers -> the warp's swizzled staging
-//                rows -> cp.async.bulk.tensor), waited for only when the rows are reused a tile
-//                later; float32 tiles use the warp's own 16-byte coalesced stores.
+//                four warps per scheduler hide each other's TMEM-load latency.  Tiles leave through
+//                bulk tensor stores (registers -> the warp's swizzled staging rows ->
+//                cp.async.bulk.tensor, one box per 128 bytes of row), waited for only when the rows
+//                are reused a tile later.
 //   warp P       TMA producer: A (one 128 x 128-byte box) and B (BN/128 boxes), 128B swizzle
 //   warp P+1     MMA issuer (owns the TMEM allocation): one lane-split barrier wait per block
 //   warps P+2,3  (256-column tiles only) idle padding of the producer's warpgroup, so that it can
 //                release registers to the promotion warpgroups with setmaxnreg: 96 -> 40 / 104.
-//                The 8 extra registers take the tile-boundary spills from 14 stores / 8 loads to
-//                3 / 7; their reloads miss the 28 KB of L1 left beside 214 KB of shared memory.
+//
+// The loops of all three roles carry their state (stage, buffer, phase, scale offsets) instead of
+// deriving it from a block counter, and the barriers live in static shared memory, so that a block
+// costs the promotion warps little more than its 32 packed FMAs and 4 TMEM loads: the first builds
+// spent four fifths of their instructions on address arithmetic and were bound by issue.
 //
 // Operand orientation is data, not code: the TMA box is 128 bytes x 128 rows for both
 // K-major and MN-major storage (only the coordinates swap), and the shared-memory operand
 // descriptors / instruction descriptor carry the major-ness, so dgrad and wgrad read the
-// same buffers the forward wrote, untransposed.
+// same buffers the forward wrote, untransposed.  Few output tiles with a long contraction are
+// cut along the contraction (plan_split); few rows against a wide weight run with the operands
+// swapped (plan_skinny).
 //
 // Every wait on an mbarrier is bounded: when the limit runs out the waiting role raises a
 // CTA-wide abort flag, stores a code in *status, and all roles fall through to the common
