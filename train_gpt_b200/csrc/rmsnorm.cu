@@ -385,21 +385,199 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   for (int i = threadIdx.x; i < cols; i += blockDim.x) partial[int64_t(blockIdx.x) * cols + i] = s_dyn[i];
 }
 
+// ---------------------------------------------------------------------------------------
+// Backward for rows that one warp can hold (cols <= 2048), staged through shared memory.
+// The register-resident kernel above keeps x, g and 8 column sums per 16-byte piece live at
+// once (246 registers at 2048 columns: one block of eight warps per SM, each idle while its
+// next row is in flight; it reached 55 % of the copy bandwidth).  Here each warp owns SLOTS
+// pairs of row-sized shared-memory slots and cp.async keeps SLOTS - 1 rows of x and g in flight
+// while one is processed:
+// x goes to registers once, g is read from shared memory in the column-sum pass and again in
+// the dx pass, gamma sits in shared memory widened to float.  Every lane reads only the
+// 16-byte pieces it fetched itself, so cp.async.wait_group is the only synchronisation.
+// The arithmetic per row is the same sequence as in rmsnorm_bwd_kernel: dx comes out
+// bit-identical; dgamma sums the same products in another (still fixed) order.
+// ---------------------------------------------------------------------------------------
+template <int NCHUNK, int WARPS, int SLOTS, bool FULL>
+__global__ void __launch_bounds__(WARPS * 32, 1)
+rmsnorm_bwd_staged_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma,
+                          const __nv_bfloat16* __restrict__ g, float eps, __nv_bfloat16* __restrict__ dx,
+                          float* __restrict__ partial, int64_t rows, int cols) {
+  constexpr int kRowBytes = NCHUNK * 512;
+  extern __shared__ float4 s_gamma[];   // [cols] floats in two planes, then [warps][SLOTS][x row | g row] bf16
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int col_base = lane * 8;
+  const uint32_t stage0 = uint32_t(__cvta_generic_to_shared(s_gamma)) + uint32_t(cols) * 4u;
+  const uint32_t slot0 = stage0 + uint32_t(warp) * uint32_t(SLOTS * 2 * kRowBytes) + uint32_t(lane) * 16u;
+  const float inv_d = __fdiv_rn(1.0f, float(cols));
+
+  const int pieces = cols / 8;
+  for (int i = threadIdx.x; i < pieces; i += blockDim.x) {
+    const uint4 gq = reinterpret_cast<const uint4*>(gamma)[i];
+    s_gamma[i] = make_float4(bf16lo(gq.x), bf16hi(gq.x), bf16lo(gq.y), bf16hi(gq.y));
+    s_gamma[pieces + i] = make_float4(bf16lo(gq.z), bf16hi(gq.z), bf16lo(gq.w), bf16hi(gq.w));
+  }
+  __syncthreads();
+
+  float acc[NCHUNK][8];
+#pragma unroll
+  for (int c = 0; c < NCHUNK; ++c)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[c][j] = 0.f;
+
+  const int64_t stride = int64_t(gridDim.x) * WARPS;
+  int64_t row = int64_t(blockIdx.x) * WARPS + warp;
+  auto prefetch = [&](int64_t r, int slot) {
+    if (r < rows) {
+      const uint32_t dst = slot0 + uint32_t(slot) * 2u * kRowBytes;
+#pragma unroll
+      for (int c = 0; c < NCHUNK; ++c) {
+        const int col = col_base + c * 256;
+        if (FULL || col < cols) {
+          cp_async16(dst + c * 512, x + r * cols + col);
+          cp_async16(dst + kRowBytes + c * 512, g + r * cols + col);
+        }
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");   // an empty group keeps the wait count uniform
+  };
+  // SLOTS - 1 rows are in flight while one is processed
+#pragma unroll
+  for (int d = 0; d < SLOTS - 1; ++d) prefetch(row + d * stride, d);
+  int slot = 0, slot_in = SLOTS - 1;
+  for (; row < rows; row += stride) {
+    const uint32_t xs = slot0 + uint32_t(slot) * 2u * kRowBytes, gs = xs + kRowBytes;
+    prefetch(row + (SLOTS - 1) * stride, slot_in);    // into the slot the previous iteration finished with
+    asm volatile("cp.async.wait_group %0;" ::"n"(SLOTS - 1) : "memory");
+    slot_in = slot;
+    if (++slot == SLOTS) slot = 0;
+
+    uint4 w[NCHUNK];
+    float part[NCHUNK];
+#pragma unroll
+    for (int c = 0; c < NCHUNK; ++c) {
+      w[c] = (FULL || col_base + c * 256 < cols) ? lds128(xs + c * 512) : make_uint4(0, 0, 0, 0);
+      part[c] = sumsq8(w[c]);
+    }
+    float ss = tree_sum(part);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float rn = __frsqrt_rn(__fdiv_rn(ss, float(cols)) + eps);
+
+    // column sums of g * normed, and gs * normed summed over the row
+    float dpart[NCHUNK];
+#pragma unroll
+    for (int c = 0; c < NCHUNK; ++c) {
+      float dsum = 0.f;
+      const int col = col_base + c * 256;
+      if (FULL || col < cols) {
+        const uint4 gv = lds128(gs + c * 512);
+        const float4 m0 = s_gamma[col >> 3], m1 = s_gamma[pieces + (col >> 3)];
+        const float mf[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+        const uint32_t xi[4] = {w[c].x, w[c].y, w[c].z, w[c].w};
+        const uint32_t gi[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float n0 = __fmul_rn(bf16lo(xi[j]), rn), n1 = __fmul_rn(bf16hi(xi[j]), rn);
+          const float g0 = bf16lo(gi[j]), g1 = bf16hi(gi[j]);
+          acc[c][2 * j] = fmaf(g0, n0, acc[c][2 * j]);
+          acc[c][2 * j + 1] = fmaf(g1, n1, acc[c][2 * j + 1]);
+          dsum = fmaf(__fmul_rn(g0, mf[2 * j]), n0, dsum);
+          dsum = fmaf(__fmul_rn(g1, mf[2 * j + 1]), n1, dsum);
+        }
+      }
+      dpart[c] = dsum;
+    }
+    float dsum = tree_sum(dpart);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) dsum += __shfl_xor_sync(0xffffffffu, dsum, o);
+    const float dot = __fmul_rn(dsum, inv_d);
+
+    // (no instruction: stops the compiler from keeping the 8 * NCHUNK normalised values of the pass
+    // above alive for the pass below, which costs more registers than recomputing them)
+#pragma unroll
+    for (int c = 0; c < NCHUNK; ++c) asm volatile("" : "+r"(w[c].x), "+r"(w[c].y), "+r"(w[c].z), "+r"(w[c].w));
+#pragma unroll
+    for (int c = 0; c < NCHUNK; ++c) {
+      const int col = col_base + c * 256;
+      if (!(FULL || col < cols)) continue;
+      const uint4 gv = lds128(gs + c * 512);
+      const float4 m0 = s_gamma[col >> 3], m1 = s_gamma[pieces + (col >> 3)];
+      const float mf[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+      const uint32_t xi[4] = {w[c].x, w[c].y, w[c].z, w[c].w};
+      const uint32_t gi[4] = {gv.x, gv.y, gv.z, gv.w};
+      uint4 o;
+      uint32_t* op = &o.x;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float n0 = __fmul_rn(bf16lo(xi[j]), rn), n1 = __fmul_rn(bf16hi(xi[j]), rn);
+        const float gs0 = __fmul_rn(bf16lo(gi[j]), mf[2 * j]);
+        const float gs1 = __fmul_rn(bf16hi(gi[j]), mf[2 * j + 1]);
+        // rnorm * (gs - normed*dot), the subtraction fused as kernels.py:114 allows XLA to
+        const float d0 = __fmul_rn(rn, fmaf(-n0, dot, gs0));
+        const float d1 = __fmul_rn(rn, fmaf(-n1, dot, gs1));
+        op[j] = pack_bf16x2(d0, d1);
+      }
+      *reinterpret_cast<uint4*>(dx + row * cols + col) = o;
+    }
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+
+  // combine the block's warps in warp order over the (now idle) staging area, then publish the
+  // block's row of partial column sums
+  __syncthreads();
+  float* s_sum = reinterpret_cast<float*>(s_gamma) + cols;
+  for (int i = threadIdx.x; i < cols; i += blockDim.x) s_sum[i] = 0.f;
+  __syncthreads();
+  for (int turn = 0; turn < WARPS; ++turn) {
+    if (warp == turn) {
+#pragma unroll
+      for (int c = 0; c < NCHUNK; ++c) {
+        const int col = col_base + c * 256;
+        if (FULL || col < cols) {
+          float4* dst = reinterpret_cast<float4*>(s_sum + col);
+          float4 a = dst[0], b = dst[1];
+          a.x += acc[c][0]; a.y += acc[c][1]; a.z += acc[c][2]; a.w += acc[c][3];
+          b.x += acc[c][4]; b.y += acc[c][5]; b.z += acc[c][6]; b.w += acc[c][7];
+          dst[0] = a; dst[1] = b;
+        }
+      }
+    }
+    __syncthreads();
+  }
+  for (int i = threadIdx.x; i < cols; i += blockDim.x) partial[int64_t(blockIdx.x) * cols + i] = s_sum[i];
+}
+
+// Column sums of the per-block partials.  A thread block owns 32 columns; its eight warps take the
+// partial rows b = warp, warp + 8, ... (four independent sums each, so a warp has four loads in
+// flight), and the eight results are added in warp order: the order of additions is fixed by
+// (n_blocks, cols) alone.  With one thread per column walking all rows the kernel was a chain of
+// ~n_blocks / 4 dependent L2 round trips on eight thread blocks: 13 us at 1024 columns.
 __global__ void __launch_bounds__(256)
 rmsnorm_dgamma_reduce_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ dgamma,
                              int n_blocks, int cols) {
-  const int col = blockIdx.x * blockDim.x + threadIdx.x;
-  if (col >= cols) return;
+  __shared__ float s_part[8][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int col = blockIdx.x * 32 + lane;
   float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-  int b = 0;
-  for (; b + 4 <= n_blocks; b += 4) {
-    s0 += partial[int64_t(b) * cols + col];
-    s1 += partial[int64_t(b + 1) * cols + col];
-    s2 += partial[int64_t(b + 2) * cols + col];
-    s3 += partial[int64_t(b + 3) * cols + col];
+  if (col < cols) {
+    int b = warp;
+    for (; b + 24 < n_blocks; b += 32) {
+      s0 += partial[int64_t(b) * cols + col];
+      s1 += partial[int64_t(b + 8) * cols + col];
+      s2 += partial[int64_t(b + 16) * cols + col];
+      s3 += partial[int64_t(b + 24) * cols + col];
+    }
+    for (; b < n_blocks; b += 8) s0 += partial[int64_t(b) * cols + col];
   }
-  for (; b < n_blocks; ++b) s0 += partial[int64_t(b) * cols + col];
-  dgamma[col] = __float2bfloat16_rn((s0 + s1) + (s2 + s3));
+  s_part[warp][lane] = (s0 + s1) + (s2 + s3);
+  __syncthreads();
+  if (warp == 0 && col < cols) {
+    float t = s_part[0][lane];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) t += s_part[w][lane];
+    dgamma[col] = __float2bfloat16_rn(t);
+  }
 }
 
 struct NormGeom {
@@ -432,7 +610,7 @@ static int launch_fwd(const void* x, const void* gamma, float eps, void* q, floa
                       float* rnorm, int64_t rows, int64_t cols, int mode, cudaStream_t st) {
   NormGeom g;
   if (!norm_geom(cols, &g)) return cols > 8192 ? TG_ERR_TOO_LARGE : TG_ERR_SHAPE;
-  if (QUANT && g.wpr == 1 && getenv("TG_NORM_UNSTAGED") == nullptr) {
+  if (QUANT && g.wpr == 1) {
     const size_t smem = size_t(cols) * 4 + size_t(kNormWarps) * 2 * g.nchunk * 512;
     const int blocks = norm_blocks(rows, 1, kStagedBlocksPerSm);
     int dev = 0;
@@ -479,6 +657,17 @@ static int launch_fwd(const void* x, const void* gamma, float eps, void* q, floa
 
 constexpr int kBwdBlocksPerSm = 2;
 
+// Rows one warp can hold run staged, one block per SM with 192 KB of row slots: 8 warps x 3 slots
+// at 2048 columns, 12 x 4 at 1024, 16 x 4 below; wider rows stay register-resident.
+static int bwd_staged_warps(const NormGeom& g) { return g.wpr != 1 ? 0 : g.nchunk >= 8 ? 8 : g.nchunk == 4 ? 12 : 16; }
+
+static int bwd_blocks(int64_t rows, const NormGeom& g) {
+  const int w = bwd_staged_warps(g);
+  if (w == 0) return norm_blocks(rows, g.wpr, kBwdBlocksPerSm);
+  const int64_t need = (rows + w - 1) / w, cap = sm_count();
+  return int(need < cap ? need : cap);
+}
+
 }  // namespace tg
 
 using namespace tg;
@@ -507,7 +696,7 @@ extern "C" int tg_rmsnorm_quant_fwd(const void* x, const void* gamma, float eps,
 extern "C" int64_t tg_rmsnorm_bwd_scratch_bytes(int64_t rows, int64_t cols) {
   NormGeom g;
   if (rows <= 0 || !norm_geom(cols, &g)) return 0;
-  return int64_t(norm_blocks(rows, g.wpr, kBwdBlocksPerSm)) * cols * int64_t(sizeof(float));
+  return int64_t(bwd_blocks(rows, g)) * cols * int64_t(sizeof(float));
 }
 
 extern "C" int tg_rmsnorm_bwd(const void* x, const void* gamma, const void* g, float eps, void* dx,
@@ -522,7 +711,37 @@ extern "C" int tg_rmsnorm_bwd(const void* x, const void* gamma, const void* g, f
     TG_CUDA_CHECK(cudaMemsetAsync(dgamma, 0, size_t(cols) * 2, st));
     return TG_OK;
   }
-  const int blocks = norm_blocks(rows, geo.wpr, kBwdBlocksPerSm);
+  const int blocks = bwd_blocks(rows, geo);
+  if (bwd_staged_warps(geo) != 0) {
+    int dev = 0;
+    TG_CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return TG_ERR_SHAPE;
+    const bool full = cols == int64_t(geo.nchunk) * 256;   // no ragged chunk: the column guards compile away
+#define TG_BWD_STAGED_CASE(NC, WARPS, SLOTS)                                                      \
+  if (geo.nchunk == NC) {                                                                         \
+    auto kern = full ? rmsnorm_bwd_staged_kernel<NC, WARPS, SLOTS, true>                          \
+                     : rmsnorm_bwd_staged_kernel<NC, WARPS, SLOTS, false>;                        \
+    constexpr int kStage = WARPS * SLOTS * 2 * NC * 512;                                          \
+    static_assert(NC * 256 * 4 + kStage <= 227 * 1024, "row slots exceed shared memory");         \
+    static bool attr_set[2][64] = {};                                                             \
+    if (!attr_set[full][dev]) {                                                                   \
+      TG_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,       \
+                                         NC * 256 * 4 + kStage));                                 \
+      attr_set[full][dev] = true;                                                                 \
+    }                                                                                             \
+    kern<<<blocks, WARPS * 32, size_t(cols) * 4 + size_t(kStage), st>>>(                          \
+        static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(gamma),           \
+        static_cast<const __nv_bfloat16*>(g), eps, static_cast<__nv_bfloat16*>(dx),               \
+        static_cast<float*>(scratch), rows, int(cols));                                           \
+  } else
+    TG_BWD_STAGED_CASE(1, 16, 4) TG_BWD_STAGED_CASE(2, 16, 4) TG_BWD_STAGED_CASE(4, 12, 4) TG_BWD_STAGED_CASE(8, 8, 3) { return TG_ERR_SHAPE; }
+#undef TG_BWD_STAGED_CASE
+    TG_CUDA_CHECK(cudaGetLastError());
+    rmsnorm_dgamma_reduce_kernel<<<int((cols + 31) / 32), 256, 0, st>>>(
+        static_cast<const float*>(scratch), static_cast<__nv_bfloat16*>(dgamma), blocks, int(cols));
+    TG_CUDA_CHECK(cudaGetLastError());
+    return TG_OK;
+  }
   const size_t smem = size_t(cols) * sizeof(float);
 #define TG_BWD_CASE(NC, W)                                                                      \
   if (geo.nchunk == NC && geo.wpr == W) {                                                       \
@@ -535,7 +754,7 @@ extern "C" int tg_rmsnorm_bwd(const void* x, const void* gamma, const void* g, f
   TG_BWD_CASE(8, 4) { return TG_ERR_SHAPE; }
 #undef TG_BWD_CASE
   TG_CUDA_CHECK(cudaGetLastError());
-  rmsnorm_dgamma_reduce_kernel<<<int((cols + 255) / 256), 256, 0, st>>>(
+  rmsnorm_dgamma_reduce_kernel<<<int((cols + 31) / 32), 256, 0, st>>>(
       static_cast<const float*>(scratch), static_cast<__nv_bfloat16*>(dgamma), blocks, int(cols));
   TG_CUDA_CHECK(cudaGetLastError());
   return TG_OK;
