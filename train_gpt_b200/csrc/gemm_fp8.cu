@@ -122,7 +122,13 @@ struct Cfg {
   static constexpr int off_sb = off_out + out_bytes;
   // (handing the wide accumulator over in two 128-column halves, each with its own barriers
   // and N=128 MMAs, was tried: 7 % slower -- A is read twice and twice as many MMAs issue)
-  static constexpr int n_bars = 2 * stages + 2 * tmem_bufs + 1;
+  // With one staging phase per tile and idle warps to spare, one of them issues the tile's bulk
+  // stores: the copy engine accepts a promotion warp's 4 KB box only after the boxes before it (a
+  // 64 KB tile takes it ~1000 cycles at the SM's write bandwidth), and the sixteen warps used to sit
+  // in that queue instead of draining the next tile's accumulators.
+  static constexpr bool store_warp_on = regsteal && phases == 1;
+  static constexpr int store_warp = promo_warps + 2;
+  static constexpr int n_bars = 2 * stages + 2 * tmem_bufs + 1 + 2;
   static constexpr int smem_bytes = off_sb + sb_bytes;       // dynamic shared memory
   static_assert(n_bars <= 24, "control block too small");
   static_assert(stages >= 3, "pipeline too shallow");
@@ -141,6 +147,10 @@ struct GemmParams {
   int a_mn, b_mn;       // 1 = MN-major storage
   int tiles_m, tiles_n;
   int band;             // tile rows per band of the tile numbering
+  // ceil(2^40 / d) for the three divisors of the item -> tile arithmetic (tiles per contraction range,
+  // tiles per band, rows of the last band), 0 = divide the slow way (the exactness bound x * d < 2^40
+  // does not hold); rows of a full band = `band`, its reciprocal in mg_band
+  unsigned long long mg_tiles, mg_per_band, mg_band, mg_last;
   int ksplit;           // the contraction is cut into this many equal ranges; range s of a tile is its own
                         // work item and writes its float32 partial sums to d + s * slice_elems
   long long slice_elems;
@@ -163,6 +173,11 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t sr
                ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(x), "r"(y), "r"(z)
                : "memory");
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void tma_store_3d_nocommit(const CUtensorMap* map, uint32_t src, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(x), "r"(y), "r"(z)
+               : "memory");
 }
 // returns once every bulk store this thread committed has finished READING shared memory
 __device__ __forceinline__ void tma_store_wait_read() {
@@ -337,12 +352,25 @@ __device__ __forceinline__ void promote(float2* acc, const uint32_t (&v)[NC], co
 // together are as few as possible, which is what keeps the operands' L2 lines alive between the
 // CTAs that share them.  (Row-major numbering made a 148-CTA wave touch every B panel of a
 // 24-tile-wide problem plus 7 A panels; in bands of 16 it touches 16 + 10.)
+// x / d through a multiplication by mg = ceil(2^40 / d): exact while x * d < 2^40 (the host checks
+// and passes 0 otherwise).  A 32-bit division by a run-time value costs ~20 dependent instructions,
+// and every role does three of them at each tile boundary.
+__device__ __forceinline__ int fast_div(int x, int d, unsigned long long mg) {
+  return mg != 0 ? int((static_cast<unsigned long long>(static_cast<unsigned>(x)) * mg) >> 40) : x / d;
+}
 __device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& tm, int& tn) {
   const int per_band = p.band * p.tiles_n;
-  const int b = tile / per_band, w = tile - b * per_band;
-  const int rows = min(p.band, p.tiles_m - b * p.band);
-  tn = w / rows;
+  const int b = fast_div(tile, per_band, p.mg_per_band), w = tile - b * per_band;
+  const int left = p.tiles_m - b * p.band;
+  const bool full = left >= p.band;
+  const int rows = full ? p.band : left;
+  tn = fast_div(w, rows, full ? p.mg_band : p.mg_last);
   tm = b * p.band + (w - tn * rows);
+}
+// work item -> (contraction range, tile)
+__device__ __forceinline__ void item_split(const GemmParams& p, int item, int n_tiles, int& ks, int& tile) {
+  ks = fast_div(item, n_tiles, p.mg_tiles);
+  tile = item - ks * n_tiles;
 }
 
 template <int BN_, int SB_GRAN, bool OUT_F32>
@@ -355,7 +383,7 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
   constexpr int kPromoWarps = C::promo_warps;
   // operand stages (1024-byte aligned for the 128-byte swizzle), output staging, scale staging
   extern __shared__ __align__(1024) uint8_t smem[];
-  // barriers, 8 bytes each: full[kStages], empty[kStages], tfull[kTmemBufs], tempty[kTmemBufs], drain
+  // barriers, 8 bytes each: full[kStages], empty[kStages], tfull[kTmemBufs], tempty[kTmemBufs], drain, staged, unstaged
   __shared__ __align__(16) uint64_t ctl_bars[24];
   __shared__ uint32_t ctl_tmem_ptr;
   __shared__ int ctl_abort;
@@ -364,6 +392,7 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const uint32_t full0 = bar0, empty0 = bar0 + 8u * kStages;
   const uint32_t tfull0 = bar0 + 16u * kStages, tempty0 = tfull0 + 8u * kTmemBufs;
   const uint32_t drain_bar = tempty0 + 8u * kTmemBufs;
+  const uint32_t staged_bar = drain_bar + 8u, unstaged_bar = drain_bar + 16u;   // the store warp's pair (see Cfg::store_warp_on)
   volatile uint32_t* tmem_ptr_smem = &ctl_tmem_ptr;
   volatile int* abort_flag = &ctl_abort;
   if ((sbase & 1023u) != 0) {   // the swizzled operand layout needs this alignment; never seen, but not assumed
@@ -388,6 +417,8 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
       mbar_init(tempty0 + 8u * b, kPromoWarps);
     }
     mbar_init(drain_bar, 1);
+    mbar_init(staged_bar, kPromoWarps);
+    mbar_init(unstaged_bar, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_a)) : "memory");
@@ -411,8 +442,8 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t s = 0, ph = 1;                 // the first pass over the stages finds them all free
       bool ok = true;
       for (int item = first_item; ok && item < n_items; item += item_step) {
-        const int ks = item / n_tiles, tile = item - ks * n_tiles;
-        int tm, tn;
+        int ks, tile, tm, tn;
+        item_split(p, item, n_tiles, ks, tile);
         tile_coords(p, tile, tm, tn);
         const int m0 = tm * BM, n0 = tn * BN;
         int k0 = ks * p.nkb * BK;
@@ -482,6 +513,28 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
         mbar_wait(drain_bar, 0u, abort_flag, p.status, 4u);
       }
       __syncwarp();
+    } else if (C::store_warp_on && warp == C::store_warp) {
+      // ------------------------------ tile store issuer -----------------------------------
+      // Per tile: wait until all promotion warps have staged their rows, hand the sixteen boxes to the
+      // copy engine, wait until it has read them, give the staging rows back.
+      uint32_t sph = 0;
+      for (int item = first_item; item < n_items; item += item_step) {
+        int ks, tile, tm, tn;
+        item_split(p, item, n_tiles, ks, tile);
+        tile_coords(p, tile, tm, tn);
+        if (!__all_sync(0xffffffffu, mbar_wait(staged_bar, sph, abort_flag, p.status, 7u))) break;
+        sph ^= 1u;
+        if (elect_one()) {
+#pragma unroll 1
+          for (int w = 0; w < kPromoWarps; ++w)
+            tma_store_3d_nocommit(&tmap_d, sbase + C::off_out + uint32_t(w) * C::warp_out_bytes, tn * BN + (w >> 2) * kCols,
+                                  tm * BM + (w & 3) * 32, ks);
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          tma_store_wait_read();
+          mbar_arrive(unstaged_bar);
+        }
+        __syncwarp();
+      }
     }
   } else {
     // ------------------------------ promotion + epilogue --------------------------------
@@ -504,7 +557,7 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // carried incrementally: the accumulator buffer's barrier addresses, TMEM address and phase
     // are toggled, the scale pointers are bumped, and rows / columns outside the problem read a
     // clamped (valid) address instead of being predicated off.
-    uint32_t buf = 0, bph = 0;
+    uint32_t buf = 0, bph = 0, uph = 0;
     const uint32_t tcol0 = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(c0);
 
     // Per-tile state is ONE register pair of scale offsets, set one tile ahead so that the first scale
@@ -535,9 +588,9 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
       return v;
     };
     auto open_tile = [&](int item) {
-      const int ks = item / n_tiles, tile = item - ks * n_tiles;
+      int ks, tile, tm, tn;
+      item_split(p, item, n_tiles, ks, tile);
       const uint32_t kb_off = uint32_t(ks) * uint32_t(p.nkb);
-      int tm, tn;
       tile_coords(p, tile, tm, tn);
       const int n0 = tn * BN;
       const int m = min(tm * BM + r, p.M - 1);       // rows past M: a valid scale, results never stored
@@ -691,11 +744,11 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
       // start the next tile's first scale loads before the stores of this one
       if (item + item_step < n_items) open_tile(item + item_step);
-      int tile_m0, tile_n0;
-      const int tile_ks = item / n_tiles;
-      {
-        int tm, tn;
-        tile_coords(p, item - tile_ks * n_tiles, tm, tn);
+      int tile_m0 = 0, tile_n0 = 0, tile_ks = 0;
+      if constexpr (!C::store_warp_on) {
+        int tile, tm, tn;
+        item_split(p, item, n_tiles, tile_ks, tile);
+        tile_coords(p, tile, tm, tn);
         tile_m0 = tm * BM;
         tile_n0 = tn * BN;
       }
@@ -708,9 +761,20 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
       // are clipped by the tensor map, whose third coordinate is the contraction slice.
       constexpr int PRB = C::phase_row_bytes;
       const uint32_t wb = sbase + C::off_out + uint32_t(pw) * C::warp_out_bytes;
+      if constexpr (C::store_warp_on) {
+        // the staging rows are free once the store warp's boxes of the tile before have been read
+        // (a whole tile ago: this does not wait in practice); first tile: nothing to wait for
+        if (item != first_item) {
+          ok = __all_sync(0xffffffffu, mbar_wait(unstaged_bar, uph, abort_flag, p.status, 8u));
+          if (!ok) break;
+          uph ^= 1u;
+        }
+      }
 #pragma unroll
       for (int ph = 0; ph < C::phases; ++ph) {
-        if (lane == 0) tma_store_wait_read();
+        if constexpr (!C::store_warp_on) {
+          if (lane == 0) tma_store_wait_read();
+        }
         __syncwarp();
         if (kFrag && OUT_F32) {
           // thread (fg, fj) holds rows fg + 8 i, columns 16 qq + 8 k + 2 fj (+1) of the phase: 16-byte chunk
@@ -752,14 +816,18 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the copy engine
         __syncwarp();
-        if (lane == 0) tma_store_3d(&tmap_d, wb, tile_n0 + c0 + ph * C::phase_cols, tile_m0 + quarter * 32, tile_ks);
+        if constexpr (C::store_warp_on) {
+          mbar_arrive_if(staged_bar, is_lane0);
+        } else {
+          if (lane == 0) tma_store_3d(&tmap_d, wb, tile_n0 + c0 + ph * C::phase_cols, tile_m0 + quarter * 32, tile_ks);
+        }
       }
     }
   }
 
   // ------------------------------ teardown ----------------------------------------------
   // the last bulk stores must have read their staging rows before the CTA's shared memory goes away
-  if (warp < C::promo_warps && lane == 0) tma_store_wait_read();
+  if (!C::store_warp_on && warp < C::promo_warps && lane == 0) tma_store_wait_read();
   tc_fence_before();
   __syncthreads();
   if (warp == C::issuer_warp) {
@@ -837,6 +905,20 @@ static int launch_gemm(const tg_gemm_args* a, GemmParams p, cudaStream_t st) {
   p.tiles_n = int((a->N + BN_ - 1) / BN_);
   p.band = p.tiles_m < kBandRows ? p.tiles_m : kBandRows;
   const int64_t n_items = int64_t(p.tiles_m) * p.tiles_n * p.ksplit;
+  {
+    // reciprocals for the kernel's item -> tile arithmetic: q = (x * ceil(2^40 / d)) >> 40 is x / d
+    // for every x <= x_max when x_max * d < 2^40
+    auto magic = [](int64_t x_max, int64_t d) -> unsigned long long {
+      if (d <= 0 || x_max >= (int64_t(1) << 31) || x_max * d >= (int64_t(1) << 40)) return 0ull;
+      return ((1ull << 40) + uint64_t(d) - 1) / uint64_t(d);
+    };
+    const int64_t n_tiles = int64_t(p.tiles_m) * p.tiles_n, per_band = int64_t(p.band) * p.tiles_n;
+    const int64_t last_rows = p.tiles_m % p.band;
+    p.mg_tiles = magic(n_items, n_tiles);
+    p.mg_per_band = magic(n_tiles, per_band);
+    p.mg_band = magic(per_band, p.band);
+    p.mg_last = last_rows > 0 ? magic(per_band, last_rows) : 0ull;
+  }
   if (n_items > INT32_MAX || n_items * p.nkb > INT32_MAX) return TG_ERR_TOO_LARGE;
   const int sms = gemm_sms();
   const int grid = int(n_items < sms ? n_items : sms);
