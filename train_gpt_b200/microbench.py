@@ -6,6 +6,8 @@ TFLOP/s for the GEMMs, against the algorithmic bytes / FLOPs of each.
     python -m train_gpt_b200.microbench norm   [--rows 32768 --cols 2048]
     python -m train_gpt_b200.microbench gemm   [--m 32768 --n 6144 --k 2048 --mode fwd|dgrad|wgrad --tile 128x128|128x1]
     python -m train_gpt_b200.microbench sweep  (square and skinny GEMM shapes)
+    python -m train_gpt_b200.microbench sustained [--m .. --n .. --k .. --mode all --seconds 2.5]
+                                               (one GEMM back to back for seconds: rate, SM clock, power)
 
 Timing: CUDA events on the launching stream, `--warmup` untimed launches, then `--iters`
 samples (ten back-to-back launches each for the streaming kernels, one for a GEMM); operands rotate through enough distinct buffers to exceed the
@@ -17,6 +19,8 @@ from __future__ import annotations
 import argparse
 import json
 import statistics
+import subprocess
+import time
 
 import torch
 
@@ -199,6 +203,89 @@ def _gemm_case(M, N, K, mode, tile, warmup, iters, student_t=False):
                    weight_tile=f"{tile[0]}x{tile[1]}", pct_of_4500=round(2.0 * M * N * K / m / 1e9 / 45.0, 1))
 
 
+def _gemm_fn(M, N, K, mode, tile):
+    """Quantised operands of one layer GEMM and a closure that launches it."""
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    w = (0.02 * torch.randn(K, N, device="cuda", generator=g)).to(torch.bfloat16)
+    gr = torch.randn(M, N, device="cuda", generator=g).to(torch.bfloat16)
+    st = ops.new_status("cuda")
+    if mode == "fwd":
+        a_q, a_s = ops.quantize_rowwise(x)
+        w_q, w_s = fp8.quantize_weight(w, tile)
+        return (lambda: ops.gemm_fwd(a_q, a_s, w_q, w_s, tile, status=st)), st
+    if mode == "dgrad":
+        g_q, g_s = ops.quantize_rowwise(gr)
+        w_q, w_s = ops.quantize_rowwise(w) if tile == (128, 1) else ops.quantize_block128(w)
+        return (lambda: ops.gemm_dgrad(g_q, g_s, w_q, w_s, tile, status=st)), st
+    x_q, x_s = ops.quantize_colwise(x)
+    g_q, g_s = ops.quantize_colwise(gr)
+    return (lambda: ops.gemm_wgrad(x_q, x_s, g_q, g_s, status=st)), st
+
+
+def _sample_while(fn, seconds):
+    """Runs fn back to back for `seconds` while nvidia-smi samples the GPU every 50 ms (reading only);
+    returns launches, ms per launch and the medians of SM clock and power over the last three quarters."""
+    dev = torch.cuda.current_device()
+    smi = subprocess.Popen(
+        ["nvidia-smi", "-i", str(dev), "--query-gpu=clocks.sm,power.draw,clocks_event_reasons.sw_power_cap,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.sw_thermal_slowdown", "--format=csv,noheader,nounits",
+         "-lms", "50"], stdout=subprocess.PIPE, text=True)
+    for _ in range(5):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0, n = time.time(), 0
+    e0.record()
+    while time.time() - t0 < seconds:
+        for _ in range(50):
+            fn()
+        n += 50
+        torch.cuda.synchronize()
+    e1.record()
+    e1.synchronize()
+    ms = e0.elapsed_time(e1) / n
+    smi.terminate()
+    rows = [l.split(", ") for l in smi.stdout.read().strip().splitlines() if l.count(",") >= 4]
+    rows = rows[len(rows) // 4:]
+    clk = [float(r[0]) for r in rows] or [0.0]
+    pw = [float(r[1]) for r in rows] or [0.0]
+    return dict(launches=n, ms_per_launch=round(ms, 4), sm_mhz_median=statistics.median(clk), sm_mhz_min=min(clk),
+                power_w_median=round(statistics.median(pw), 1), samples=len(rows),
+                sw_power_cap=sum(r[2].strip() == "Active" for r in rows),
+                slowdown=sum(r[3].strip() == "Active" or r[4].strip() == "Active" for r in rows))
+
+
+def bench_sustained(M, N, K, modes, tile, seconds):
+    """What a GEMM sustains once the board sits at its power limit: the same launch back to back for
+    `seconds`, with the SM clock and the power the board settled at, and a cuBLAS bf16 8192^3 loop for
+    scale.  `tensor_busy` is the rate over what 148 SMs x 16384 FLOP per cycle give at that clock."""
+    out = []
+    for mode in modes:
+        fn, st = _gemm_fn(M, N, K, mode, tile)
+        r = _sample_while(fn, seconds)
+        if int(st.item()) != 0:
+            raise RuntimeError(f"GEMM bounded wait expired, status {int(st.item())}")
+        r.update(kernel=f"gemm_{mode}", tokens=M, K=K, N=N)
+        r["TFLOPs"] = round(2.0 * M * N * K / r["ms_per_launch"] / 1e9, 1)
+        if r["sm_mhz_median"] > 0:
+            r["tensor_busy"] = round(r["TFLOPs"] * 1e12 / (148 * 16384 * r["sm_mhz_median"] * 1e6), 3)
+        out.append(r)
+        if EMIT:
+            print(json.dumps(r), flush=True)
+        time.sleep(1.0)
+    a = torch.randn(8192, 8192, device="cuda").to(torch.bfloat16)
+    r = _sample_while(lambda: torch.mm(a, a), seconds)
+    r.update(kernel="cublas_bf16_8192x8192x8192")
+    r["TFLOPs"] = round(2.0 * 8192 ** 3 / r["ms_per_launch"] / 1e9, 1)
+    if r["sm_mhz_median"] > 0:
+        r["tensor_busy"] = round(r["TFLOPs"] * 1e12 / (148 * 8192 * r["sm_mhz_median"] * 1e6), 3)
+    out.append(r)
+    if EMIT:
+        print(json.dumps(r), flush=True)
+    return out
+
+
 def bench_sweep(tile=(128, 128), warmup=5, iters=30):
     """The shape sweep of the benchmark configurations (Student-t(3) activations): squares
     M = N = K in {1024 .. 16384}, then skinny M in {16, 64, 256} with K = N = 8192, each as forward,
@@ -219,7 +306,7 @@ def bench_sweep(tile=(128, 128), warmup=5, iters=30):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["quant", "norm", "gemm", "loss", "sweep"])
+    ap.add_argument("what", choices=["quant", "norm", "gemm", "loss", "sweep", "sustained"])
     ap.add_argument("--vocab", type=int, default=50304)
     ap.add_argument("--rows", type=int, default=32768)
     ap.add_argument("--cols", type=int, default=2048)
@@ -230,6 +317,7 @@ def main():
     ap.add_argument("--tile", default="128x128", choices=["128x128", "128x1"])
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--iters", type=int, default=30)
+    ap.add_argument("--seconds", type=float, default=2.5)
     a = ap.parse_args()
     tile = (128, 128) if a.tile == "128x128" else (128, 1)
     if a.what == "quant":
@@ -241,6 +329,8 @@ def main():
     elif a.what == "gemm":
         for mode in (["fwd", "dgrad", "wgrad"] if a.mode == "all" else [a.mode]):
             _gemm_case(a.m, a.n, a.k, mode, tile, a.warmup, a.iters)
+    elif a.what == "sustained":
+        bench_sustained(a.m, a.n, a.k, ["fwd", "dgrad", "wgrad"] if a.mode == "all" else [a.mode], tile, a.seconds)
     else:
         bench_sweep(tile, a.warmup, a.iters)
 
