@@ -102,10 +102,17 @@ def test_rejects_bad_arguments():
 
 
 def test_gelu_every_finite_bf16_argument():
-    """All 65280 finite bf16 values, 128 consecutive bit patterns per tile: the bytes and scales of
-    torch's elementwise GELU followed by tg_quantize_rowcol.  (A range split with a shared-memory
-    table for the erf, bit-identical on this test, measured SLOWER than evaluating erff per element
-    -- 1.5 against 2.0 TB/s: random 2-byte table reads conflict in the banks -- and was dropped.)"""
+    """All 65280 finite bf16 values, 128 consecutive bit patterns (one binade) per row: the bytes and
+    scales of torch's elementwise GELU followed by tg_quantize_rowcol.  The kernel's erf is its own
+    (one ex2 and a polynomial, not libdevice's erff); both put it into the float32 form
+    x/2 (1 + erf), whose result has no correct digits left once 1 + erf cancels -- below x = -4 a
+    rounding error of erf is a relative error of 2^-9 and more in the result.  So: row-tile scales and
+    bytes as before, column scales equal for the three row groups above -4, and for the last group
+    (x from -4 down) equal for the columns whose largest element has digits, within a factor of 2.5
+    for the rest.
+    (A range split with a shared-memory table for the erf, bit-identical on this test, measured SLOWER
+    than evaluating the function per element -- 1.5 against 2.0 TB/s: random 2-byte table reads
+    conflict in the banks -- and was dropped.)"""
     from train_gpt_b200 import ops
     bits = np.concatenate([np.arange(0, 0x7F80), np.arange(0x8000, 0xFF80)]).astype(np.uint16)
     x = to_torch_bf16(bits.view(BF16).reshape(510, 128))
@@ -113,4 +120,8 @@ def test_gelu_every_finite_bf16_argument():
     ref = ops.quantize_rowcol(torch.nn.functional.gelu(x).contiguous())
     assert torch.equal(out[1], ref[1]), "row-tile scales"
     assert (out[0].view(torch.uint8) == ref[0].view(torch.uint8)).float().mean().item() >= 0.9995
-    assert (out[3] == ref[3]).float().mean().item() >= 0.99
+    assert float(x[383, 127]) > -4.0 and float(x[384, 0]) == -4.0            # the fourth group of 128 rows starts at -4
+    assert (out[3][:3] == ref[3][:3]).float().mean().item() >= 0.995
+    assert (out[3][3] == ref[3][3]).float().mean().item() >= 0.9
+    ratio = out[3][3] / ref[3][3]
+    assert float(ratio.min()) > 0.4 and float(ratio.max()) < 2.5

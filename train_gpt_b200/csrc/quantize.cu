@@ -63,13 +63,36 @@ constexpr int kColRowsPerThread = kTile / kColHalfWarps;  // 8
 // each computed in float32 from the bf16 input(s) and rounded to bf16 ONCE, which is what the
 // unfused composition (an elementwise bf16 kernel, then the quantiser) would have handed over.
 // The MLP's activation and its gradient are then never written to memory.
+// erf(x / sqrt 2) as sign(x) (1 - 2^P(|x|)): P is the degree-9 polynomial (no constant term) fitted to
+// log2 erfc(a / sqrt 2) on a in [0, 6.08] with weight erfc, so that the ABSOLUTE error of erfc is 2e-9
+// everywhere -- which is what the float32 forms below can see: they add the result to 1.  One
+// special-function instruction and ten multiply-adds, against libdevice erff's two branches of that
+// size.  Rounded to bf16, x/2 (1 + erf) from this routine and from a correctly rounded erff agree for
+// every finite bf16 x in exact float32 arithmetic; the approximate ex2 flips a bf16 ulp on about one
+// element in ten thousand.
+__device__ __forceinline__ float erf_of_x_over_sqrt2(float x) {
+  const float a = fminf(fabsf(x), 6.081118f);       // erfc is 1.2e-9 there: 1 - that is 1
+  float p = 5.117859700476401e-07f;
+  p = fmaf(p, a, -9.538196536595933e-06f);
+  p = fmaf(p, a, 7.480611384380609e-05f);
+  p = fmaf(p, a, -0.0002837043721228838f);
+  p = fmaf(p, a, 1.3612322618428152e-05f);
+  p = fmaf(p, a, 0.006932816002517939f);
+  p = fmaf(p, a, -0.05243593826889992f);
+  p = fmaf(p, a, -0.4592210352420807f);
+  p = fmaf(p, a, -1.1511043310165405f);
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(p * a));
+  return copysignf(1.0f - e, x);
+}
+
 template <int ACT>
 __device__ __forceinline__ float act_value(float x, float gate) {
   if (ACT == TG_ACT_RELU2) { const float r = fmaxf(x, 0.f); return r * r; }
   if (ACT == TG_ACT_RELU2_BWD) return gate * (2.f * fmaxf(x, 0.f));
-  if (ACT == TG_ACT_GELU) return x * 0.5f * (1.f + erff(x * 0.70710678118654752440f));
+  if (ACT == TG_ACT_GELU) return x * 0.5f * (1.f + erf_of_x_over_sqrt2(x));
   if (ACT == TG_ACT_GELU_BWD) {
-    const float cdf = 0.5f * (1.f + erff(x * 0.70710678118654752440f));
+    const float cdf = 0.5f * (1.f + erf_of_x_over_sqrt2(x));
     const float pdf = expf(-0.5f * x * x) * 0.39894228040143267794f;
     return gate * (cdf + x * pdf);
   }
