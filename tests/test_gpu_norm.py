@@ -89,7 +89,8 @@ def test_fused_equals_norm_then_quantise_kernels():
     assert torch.equal(q.view(torch.uint8), q2.view(torch.uint8)) and torch.equal(s, s2)
 
 
-@pytest.mark.parametrize("shape", [(5, 128), (3, 20, 256), (33, 768), (700, 1024), (3000, 2048), (17, 4096), (9, 8192)])
+@pytest.mark.parametrize("shape", [(5, 128), (3, 20, 256), (33, 768), (700, 1024), (40, 1280), (50, 1792), (3000, 2048),
+                                   (17, 4096), (9, 8192)])
 def test_backward(shape):
     from train_gpt_b200 import ops
     eps = 1e-5

@@ -211,6 +211,19 @@ def _wgrad_case(tag, x, g, seed, plans=(True,)):
         _report(f"{tag} wgrad cols [{plan}]", dw[midx][:, nidx].float().cpu().numpy(), ref_cols)
 
 
+# ---- ragged edges under the persistent schedule ----------------------------------------------
+
+def test_ragged_problem_with_several_tiles_per_thread_block():
+    """19237 tokens x (384 -> 640): 151 x 3 forward tiles (the last column tile half full, the last row tile
+    37 rows) on 148 thread blocks, so most blocks run several tiles and hand each one to the store warp
+    while they start the next; dgrad has 151 x 2 tiles, the weight gradient a ragged last token block."""
+    M, K, N = 19237, 384, 640
+    x, w, g = _normal((M, K), 11), _normal((K, N), 12, 0.02), _normal((M, N), 13)
+    _forward_case("ragged", x, w, seed=5)
+    _dgrad_case("ragged", g, w, seed=6)
+    _wgrad_case("ragged", x, g, seed=7, plans=(True, False))
+
+
 # ---- benchmark configuration 2: one decoder layer's linear set at 32768 tokens ---------------
 
 @pytest.mark.parametrize("K,N", LAYER_SHAPES)
