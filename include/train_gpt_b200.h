@@ -151,6 +151,17 @@ int tg_rmsnorm_quant_fwd(const void* x, const void* gamma, float eps, void* q, f
                          void* y, float* rnorm, int64_t rows, int64_t cols, int mode,
                          void* stream);
 
+/* No counterpart in the reference (XLA fuses the add into the norm's first pass by itself).
+ * The residual add of model.py:68 / :72 folded into the norm that follows it:
+ *   sum_out = bf16(x + res)  (one rounding, as the elementwise add), then
+ *   tg_rmsnorm_quant_fwd of sum_out: q / scales / y / rnorm as there.
+ *   x, res, sum_out [rows, cols] bf16 (sum_out may alias x or res); cols % 128 == 0, cols <= 2048
+ *   (wider rows: TG_ERR_TOO_LARGE -- add first, then tg_rmsnorm_quant_fwd).
+ *   q and scales may both be NULL (a norm without a quantised consumer); then y is required. */
+int tg_add_rmsnorm_quant_fwd(const void* x, const void* res, const void* gamma, float eps, void* sum_out,
+                             void* q, float* scales, void* y, float* rnorm, int64_t rows, int64_t cols,
+                             int mode, void* stream);
+
 /* Bytes of scratch tg_rmsnorm_bwd needs for a [rows, cols] problem (float32 partial
  * column sums, one row of `cols` per thread block). */
 int64_t tg_rmsnorm_bwd_scratch_bytes(int64_t rows, int64_t cols);
@@ -163,6 +174,14 @@ int64_t tg_rmsnorm_bwd_scratch_bytes(int64_t rows, int64_t cols);
  *   undefined on entry and exit.  Deterministic (no atomics).                         */
 int tg_rmsnorm_bwd(const void* x, const void* gamma, const void* g, float eps, void* dx,
                    void* dgamma, void* scratch, int64_t rows, int64_t cols, void* stream);
+
+/* No counterpart in the reference (autodiff adds the two gradients in a separate pass).
+ * tg_rmsnorm_bwd with the gradient fan-in of a residual junction folded in:
+ *   dx = bf16(addend + d loss / d x through the norm), one rounding; dgamma as tg_rmsnorm_bwd.
+ *   addend [rows, cols] bf16: the gradient arriving over the skip path (dx may alias it).
+ *   cols <= 2048 (wider rows: TG_ERR_TOO_LARGE -- tg_rmsnorm_bwd, then add). */
+int tg_rmsnorm_bwd_add(const void* x, const void* gamma, const void* g, const void* addend, float eps,
+                       void* dx, void* dgamma, void* scratch, int64_t rows, int64_t cols, void* stream);
 
 /* No counterpart in the reference.  The same backward as tg_rmsnorm_bwd for hosts that
  * cannot hand over a scratch buffer because they cannot allocate one: a custom-call

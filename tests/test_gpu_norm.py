@@ -106,6 +106,63 @@ def test_backward(shape):
     assert np.abs(dg - dg_ref).max() <= 2.0 ** -7 * np.sqrt(np.mean(dg_ref ** 2)) + 2.0 ** -7 * np.abs(dg_ref).max()
 
 
+@pytest.mark.parametrize("shape", [(5, 128), (3, 20, 256), (33, 768), (700, 1024), (40, 1280), (300, 2048)])
+@pytest.mark.parametrize("pure", [False, True])
+def test_residual_add_folded_into_the_norm(shape, pure):
+    """tg_add_rmsnorm_quant_fwd: the sum equals the elementwise bf16 add bit for bit, and every other output
+    equals tg_rmsnorm_quant_fwd of that sum bit for bit; without a quantised consumer only y is produced."""
+    from train_gpt_b200 import ops
+    eps = 1e-5
+    x, gamma = _inputs(shape, 23, eps)
+    res = normal_bf16(np.random.default_rng(5), shape, std=0.3)
+    xt, rt, gt = to_torch_bf16(x), to_torch_bf16(res), to_torch_bf16(gamma)
+    s, q, sc, y = ops.add_rmsnorm_quant_fwd(xt, rt, gt, eps, pure=pure)
+    s_ref = xt + rt
+    assert torch.equal(s.view(torch.int16), s_ref.view(torch.int16))
+    q2, sc2, y2, _ = ops.rmsnorm_quant_fwd(s_ref, gt, eps, pure=pure, want_y=True)
+    assert torch.equal(q.view(torch.uint8), q2.view(torch.uint8)) and torch.equal(sc, sc2)
+    assert torch.equal(y.view(torch.int16), y2.view(torch.int16))
+    s3, q3, sc3, y3 = ops.add_rmsnorm_quant_fwd(xt, rt, gt, eps, pure=pure, want_q=False)
+    assert q3 is None and sc3 is None and torch.equal(y3.view(torch.int16), y2.view(torch.int16))
+    assert torch.equal(s3.view(torch.int16), s_ref.view(torch.int16))
+    with pytest.raises(ValueError):
+        ops.add_rmsnorm_quant_fwd(xt, rt, gt, eps, want_q=False, want_y=False)
+
+
+def test_residual_add_rejects_wide_rows():
+    from train_gpt_b200 import ops
+    x = torch.zeros((4, 4096), dtype=torch.bfloat16, device="cuda")
+    g = torch.ones((4096,), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ValueError):
+        ops.add_rmsnorm_quant_fwd(x, x, g, 1e-5)
+    with pytest.raises(ValueError):
+        ops.rmsnorm_bwd(x, g, x, 1e-5, addend=x)
+
+
+@pytest.mark.parametrize("shape", [(5, 128), (3, 20, 256), (33, 768), (700, 1024), (40, 1280), (3000, 2048)])
+def test_backward_with_the_skip_gradient_added(shape):
+    """tg_rmsnorm_bwd_add: dgamma bit-equal to tg_rmsnorm_bwd; dx = bf16(addend + the unrounded input gradient),
+    i.e. within half a bf16 ulp (of the sum) plus the plain kernel's own tolerance of addend + oracle dx."""
+    from train_gpt_b200 import ops
+    eps = 1e-5
+    x, gamma = _inputs(shape, 17, eps)
+    gy = normal_bf16(np.random.default_rng(3), shape)
+    ad = normal_bf16(np.random.default_rng(4), shape, std=0.5)
+    xt, gt, gyt, adt = to_torch_bf16(x), to_torch_bf16(gamma), to_torch_bf16(gy), to_torch_bf16(ad)
+    dx_plain, dgamma_plain = ops.rmsnorm_bwd(xt, gt, gyt, eps)
+    dx, dgamma = ops.rmsnorm_bwd(xt, gt, gyt, eps, addend=adt)
+    assert torch.equal(dgamma.view(torch.int16), dgamma_plain.view(torch.int16))
+    dx_ref, _ = no.rms_norm_bwd(x, gamma, gy, eps)
+    want = ad.astype(np.float32) + dx_ref.astype(np.float32)
+    got = from_torch_bf16(dx).astype(np.float32)
+    b = dx_ref.astype(np.float32)
+    tol = np.abs(want) * 2.0 ** -8 + np.abs(b) * 2.0 ** -7 + np.sqrt(np.mean(b * b)) * 2.0 ** -14
+    assert (np.abs(got - want) <= tol).all()
+    # and against the two-launch composition on the device: the same value up to the extra rounding of dx
+    two = from_torch_bf16(adt + dx_plain).astype(np.float32)
+    assert (np.abs(got - two) <= np.abs(two) * 2.0 ** -7 + np.abs(b) * 2.0 ** -8 + 1e-30).all()
+
+
 def test_backward_matches_reference_vectors_and_autograd(golden):
     from train_gpt_b200 import kernels
     x = to_torch_bf16(np.asarray(golden["norm_x"]).view(BF16)).requires_grad_(True)

@@ -48,8 +48,10 @@ SYMBOLS = {
     "tg_selftest_bounded_wait": (_i, [_p, _p, _i64, _p]),
     "tg_rmsnorm_fwd": (_i, [_p, _p, _f, _p, _p, _i64, _i64, _i, _p]),
     "tg_rmsnorm_quant_fwd": (_i, [_p, _p, _f, _p, _p, _p, _p, _i64, _i64, _i, _p]),
+    "tg_add_rmsnorm_quant_fwd": (_i, [_p, _p, _p, _f, _p, _p, _p, _p, _p, _i64, _i64, _i, _p]),
     "tg_rmsnorm_bwd_scratch_bytes": (_i64, [_i64, _i64]),
     "tg_rmsnorm_bwd": (_i, [_p, _p, _p, _f, _p, _p, _p, _i64, _i64, _p]),
+    "tg_rmsnorm_bwd_add": (_i, [_p, _p, _p, _p, _f, _p, _p, _p, _i64, _i64, _p]),
     "tg_rmsnorm_bwd_static_max_scratch_bytes": (_i64, []),
     "tg_rmsnorm_bwd_static": (_i, [_p, _p, _p, _f, _p, _p, _i64, _i64, _p]),
     "tg_softcap_ce_fwd": (_i, [_p, _p, _f, _p, _p, _p, _i64, _i64, _i64, _i64, _p]),

@@ -169,14 +169,20 @@ __device__ __forceinline__ void sts128(uint32_t addr, const uint4& v) {
 constexpr int kStagedBlocksPerSm = 3;
 constexpr int kGroup = 8;   // chunks normalised, scaled and quantised together (their bf16 values stay in registers)
 
-template <int NCHUNK, bool PURE, bool FULL>
+// ADD: the row that is normalised is bf16(x + res) -- the residual add of model.py:68 / :72 folded into
+// the norm that follows it -- and is also written to `sum_out` (the new residual stream); `res` rows
+// are staged beside the x rows and the sum replaces the x row in shared memory before the first pass.
+// q may be NULL (ADD only: the final norm has no quantised consumer), then only y is produced.
+template <int NCHUNK, bool PURE, bool FULL, bool ADD = false>
 __global__ void __launch_bounds__(kNormWarps * 32, kStagedBlocksPerSm)
 rmsnorm_quant_staged_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma,
                             float eps, uint8_t* __restrict__ q, float* __restrict__ scales,
                             __nv_bfloat16* __restrict__ y, float* __restrict__ rnorm_out, int64_t rows,
-                            int cols) {
-  constexpr int kSlotBytes = NCHUNK * 512;
-  extern __shared__ float4 s_gamma[];   // [cols] floats, then [warps][2][NCHUNK * 256] bf16
+                            int cols, const __nv_bfloat16* __restrict__ res = nullptr,
+                            __nv_bfloat16* __restrict__ sum_out = nullptr) {
+  constexpr int kRowBytes = NCHUNK * 512;
+  constexpr int kSlotBytes = ADD ? 2 * kRowBytes : kRowBytes;     // x row (then: the sum), res row
+  extern __shared__ float4 s_gamma[];   // [cols] floats, then [warps][2][slot] bf16
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int col_base = lane * 8;
   const uint32_t slot0 = uint32_t(__cvta_generic_to_shared(s_gamma)) + uint32_t(cols) * 4u +
@@ -199,7 +205,10 @@ rmsnorm_quant_staged_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bflo
 #pragma unroll
       for (int c = 0; c < NCHUNK; ++c) {
         const int col = col_base + c * 256;
-        if (FULL || col < cols) cp_async16(slot0 + slot * kSlotBytes + c * 512, x + r * cols + col);
+        if (FULL || col < cols) {
+          cp_async16(slot0 + slot * kSlotBytes + c * 512, x + r * cols + col);
+          if (ADD) cp_async16(slot0 + slot * kSlotBytes + kRowBytes + c * 512, res + r * cols + col);
+        }
       }
     }
     asm volatile("cp.async.commit_group;" ::: "memory");   // an empty group keeps the wait count uniform
@@ -209,6 +218,27 @@ rmsnorm_quant_staged_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bflo
     const uint32_t base = slot0 + (it & 1) * kSlotBytes;
     prefetch(row + stride, (it & 1) ^ 1);
     asm volatile("cp.async.wait_group 1;" ::: "memory");
+
+    if (ADD) {
+      // the residual add, one rounding to bf16 as the elementwise add it replaces
+#pragma unroll
+      for (int c = 0; c < NCHUNK; ++c) {
+        const int col = col_base + c * 256;
+        if (FULL || col < cols) {
+          const uint4 a = lds128(base + c * 512), b = lds128(base + kRowBytes + c * 512);
+          const uint32_t ai[4] = {a.x, a.y, a.z, a.w}, bi[4] = {b.x, b.y, b.z, b.w};
+          uint4 o;
+          uint32_t* op = &o.x;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 t = __fadd2_rn(bf16x2_unpack(ai[j]), bf16x2_unpack(bi[j]));
+            op[j] = pack_bf16x2(t.x, t.y);
+          }
+          sts128(base + c * 512, o);
+          *reinterpret_cast<uint4*>(sum_out + row * cols + col) = o;
+        }
+      }
+    }
 
     // pass 1: sum of squares
     float part[NCHUNK];
@@ -261,8 +291,9 @@ rmsnorm_quant_staged_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bflo
       {
         const int j = lane & 15;
         const int col = (g * G + j) * 256 + (lane & 16) * 8;     // first column of the tile this lane computed
-        if (j < G && (FULL || col < cols)) scales[row * (cols / kTile) + col / kTile] = s_mine;
+        if (j < G && (FULL || col < cols) && (!ADD || q != nullptr)) scales[row * (cols / kTile) + col / kTile] = s_mine;
       }
+      if (ADD && q == nullptr) continue;
 #pragma unroll
       for (int u = 0; u < G; ++u) {
         const int col = col_base + (g * G + u) * 256;
@@ -398,11 +429,14 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
 // The arithmetic per row is the same sequence as in rmsnorm_bwd_kernel: dx comes out
 // bit-identical; dgamma sums the same products in another (still fixed) order.
 // ---------------------------------------------------------------------------------------
-template <int NCHUNK, int WARPS, int SLOTS, bool FULL>
+// ADD: dx = bf16(addend + the norm's input gradient) -- the gradient fan-in at a residual junction (the
+// skip path's gradient plus the branch's) folded into the kernel, one rounding instead of two.
+template <int NCHUNK, int WARPS, int SLOTS, bool FULL, bool ADD = false>
 __global__ void __launch_bounds__(WARPS * 32, 1)
 rmsnorm_bwd_staged_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma,
                           const __nv_bfloat16* __restrict__ g, float eps, __nv_bfloat16* __restrict__ dx,
-                          float* __restrict__ partial, int64_t rows, int cols) {
+                          float* __restrict__ partial, int64_t rows, int cols,
+                          const __nv_bfloat16* __restrict__ addend = nullptr) {
   constexpr int kRowBytes = NCHUNK * 512;
   extern __shared__ float4 s_gamma[];   // [cols] floats in two planes, then [warps][SLOTS][x row | g row] bf16
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -464,6 +498,16 @@ rmsnorm_bwd_staged_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat
     for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
     const float rn = __frsqrt_rn(__fdiv_rn(ss, float(cols)) + eps);
 
+    // (ADD) the addend's pieces are fetched here, ahead of the pass that uses them, when the row is
+    // narrow enough for the registers; wider rows fetch them where they are used
+    constexpr bool kAddEarly = ADD && NCHUNK <= 4;
+    uint4 ad[kAddEarly ? NCHUNK : 1];
+    if constexpr (kAddEarly) {
+#pragma unroll
+      for (int c = 0; c < NCHUNK; ++c)
+        ad[c] = (FULL || col_base + c * 256 < cols) ? ld_nc_v4(addend + row * cols + col_base + c * 256) : make_uint4(0, 0, 0, 0);
+    }
+
     // column sums of g * normed, and gs * normed summed over the row
     float dpart[NCHUNK];
 #pragma unroll
@@ -506,6 +550,9 @@ rmsnorm_bwd_staged_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat
       const float mf[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
       const uint32_t xi[4] = {w[c].x, w[c].y, w[c].z, w[c].w};
       const uint32_t gi[4] = {gv.x, gv.y, gv.z, gv.w};
+      uint4 av = make_uint4(0, 0, 0, 0);
+      if constexpr (ADD) av = kAddEarly ? ad[kAddEarly ? c : 0] : ld_nc_v4(addend + row * cols + col);
+      const uint32_t ai[4] = {av.x, av.y, av.z, av.w};
       uint4 o;
       uint32_t* op = &o.x;
 #pragma unroll
@@ -514,8 +561,12 @@ rmsnorm_bwd_staged_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat
         const float gs0 = __fmul_rn(bf16lo(gi[j]), mf[2 * j]);
         const float gs1 = __fmul_rn(bf16hi(gi[j]), mf[2 * j + 1]);
         // rnorm * (gs - normed*dot), the subtraction fused as kernels.py:114 allows XLA to
-        const float d0 = __fmul_rn(rn, fmaf(-n0, dot, gs0));
-        const float d1 = __fmul_rn(rn, fmaf(-n1, dot, gs1));
+        float d0 = __fmul_rn(rn, fmaf(-n0, dot, gs0));
+        float d1 = __fmul_rn(rn, fmaf(-n1, dot, gs1));
+        if constexpr (ADD) {
+          d0 = __fadd_rn(d0, bf16lo(ai[j]));
+          d1 = __fadd_rn(d1, bf16hi(ai[j]));
+        }
         op[j] = pack_bf16x2(d0, d1);
       }
       *reinterpret_cast<uint4*>(dx + row * cols + col) = o;
@@ -631,7 +682,7 @@ static int launch_fwd(const void* x, const void* gamma, float eps, void* q, floa
     kern<<<blocks, kNormWarps * 32, smem, st>>>(                                                 \
         static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(gamma), eps,     \
         static_cast<uint8_t*>(q), scales, static_cast<__nv_bfloat16*>(y), rnorm, rows,           \
-        int(cols));                                                                              \
+        int(cols), nullptr, nullptr);                                                            \
   } else
     TG_STAGED_CASE(1) TG_STAGED_CASE(2) TG_STAGED_CASE(4) TG_STAGED_CASE(8) { return TG_ERR_SHAPE; }
 #undef TG_STAGED_CASE
@@ -693,18 +744,61 @@ extern "C" int tg_rmsnorm_quant_fwd(const void* x, const void* gamma, float eps,
                           static_cast<cudaStream_t>(stream));
 }
 
+extern "C" int tg_add_rmsnorm_quant_fwd(const void* x, const void* res, const void* gamma, float eps, void* sum_out,
+                                        void* q, float* scales, void* y, float* rnorm, int64_t rows, int64_t cols,
+                                        int mode, void* stream) {
+  if (rows < 0 || cols <= 0 || cols % kTile != 0 || (mode != TG_NORM_FUSED && mode != TG_NORM_PURE)) return TG_ERR_SHAPE;
+  if (x == nullptr || res == nullptr || sum_out == nullptr || (q == nullptr) != (scales == nullptr)) return TG_ERR_SHAPE;
+  if (q == nullptr && y == nullptr) return TG_ERR_SHAPE;
+  if (rows == 0) return TG_OK;
+  if (!aligned16(x) || !aligned16(res) || !aligned16(gamma) || !aligned16(q) || !aligned16(y) || !aligned16(sum_out)) return TG_ERR_ALIGN;
+  if (int rc = check_arch()) return rc;
+  NormGeom g;
+  if (!norm_geom(cols, &g)) return cols > 8192 ? TG_ERR_TOO_LARGE : TG_ERR_SHAPE;
+  if (g.wpr != 1) return TG_ERR_TOO_LARGE;      // rows one warp holds (cols <= 2048): the staged kernel
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t smem = size_t(cols) * 4 + size_t(kNormWarps) * 2 * 2 * g.nchunk * 512;
+  const int blocks = norm_blocks(rows, 1, kStagedBlocksPerSm);
+  int dev = 0;
+  TG_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return TG_ERR_SHAPE;
+#define TG_ADD_CASE(NC)                                                                          \
+  if (g.nchunk == NC) {                                                                          \
+    const bool full = cols == NC * 256;                                                          \
+    auto kern = mode == TG_NORM_PURE                                                             \
+                    ? (full ? rmsnorm_quant_staged_kernel<NC, true, true, true> : rmsnorm_quant_staged_kernel<NC, true, false, true>)   \
+                    : (full ? rmsnorm_quant_staged_kernel<NC, false, true, true> : rmsnorm_quant_staged_kernel<NC, false, false, true>); \
+    static bool attr_set[4][64] = {};                                                            \
+    if (!attr_set[(mode == TG_NORM_PURE) * 2 + full][dev]) {                                     \
+      TG_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,      \
+                                         int(2048 * 4 + kNormWarps * 2 * 2 * NC * 512)));        \
+      attr_set[(mode == TG_NORM_PURE) * 2 + full][dev] = true;                                   \
+    }                                                                                            \
+    kern<<<blocks, kNormWarps * 32, smem, st>>>(                                                 \
+        static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(gamma), eps,     \
+        static_cast<uint8_t*>(q), scales, static_cast<__nv_bfloat16*>(y), rnorm, rows,           \
+        int(cols), static_cast<const __nv_bfloat16*>(res), static_cast<__nv_bfloat16*>(sum_out)); \
+  } else
+  TG_ADD_CASE(1) TG_ADD_CASE(2) TG_ADD_CASE(4) TG_ADD_CASE(8) { return TG_ERR_SHAPE; }
+#undef TG_ADD_CASE
+  TG_CUDA_CHECK(cudaGetLastError());
+  return TG_OK;
+}
+
 extern "C" int64_t tg_rmsnorm_bwd_scratch_bytes(int64_t rows, int64_t cols) {
   NormGeom g;
   if (rows <= 0 || !norm_geom(cols, &g)) return 0;
   return int64_t(bwd_blocks(rows, g)) * cols * int64_t(sizeof(float));
 }
 
-extern "C" int tg_rmsnorm_bwd(const void* x, const void* gamma, const void* g, float eps, void* dx,
-                              void* dgamma, void* scratch, int64_t rows, int64_t cols, void* stream) {
+static int rmsnorm_bwd_impl(const void* x, const void* gamma, const void* g, const void* addend, float eps, void* dx,
+                            void* dgamma, void* scratch, int64_t rows, int64_t cols, void* stream) {
   if (rows < 0 || cols <= 0 || cols % 8 != 0) return TG_ERR_SHAPE;
   NormGeom geo;
   if (!norm_geom(cols, &geo)) return cols > 8192 ? TG_ERR_TOO_LARGE : TG_ERR_SHAPE;
-  if (!aligned16(x) || !aligned16(gamma) || !aligned16(g) || !aligned16(dx) || !aligned16(scratch)) return TG_ERR_ALIGN;
+  if (addend != nullptr && bwd_staged_warps(geo) == 0) return TG_ERR_TOO_LARGE;   // the fused add exists for rows one warp holds
+  if (!aligned16(x) || !aligned16(gamma) || !aligned16(g) || !aligned16(dx) || !aligned16(scratch) || !aligned16(addend))
+    return TG_ERR_ALIGN;
   if (int rc = check_arch()) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (rows == 0) {
@@ -719,20 +813,23 @@ extern "C" int tg_rmsnorm_bwd(const void* x, const void* gamma, const void* g, f
     const bool full = cols == int64_t(geo.nchunk) * 256;   // no ragged chunk: the column guards compile away
 #define TG_BWD_STAGED_CASE(NC, WARPS, SLOTS)                                                      \
   if (geo.nchunk == NC) {                                                                         \
-    auto kern = full ? rmsnorm_bwd_staged_kernel<NC, WARPS, SLOTS, true>                          \
-                     : rmsnorm_bwd_staged_kernel<NC, WARPS, SLOTS, false>;                        \
+    const bool add = addend != nullptr;                                                           \
+    auto kern = add ? (full ? rmsnorm_bwd_staged_kernel<NC, WARPS, SLOTS, true, true>             \
+                            : rmsnorm_bwd_staged_kernel<NC, WARPS, SLOTS, false, true>)           \
+                    : (full ? rmsnorm_bwd_staged_kernel<NC, WARPS, SLOTS, true, false>            \
+                            : rmsnorm_bwd_staged_kernel<NC, WARPS, SLOTS, false, false>);         \
     constexpr int kStage = WARPS * SLOTS * 2 * NC * 512;                                          \
     static_assert(NC * 256 * 4 + kStage <= 227 * 1024, "row slots exceed shared memory");         \
-    static bool attr_set[2][64] = {};                                                             \
-    if (!attr_set[full][dev]) {                                                                   \
+    static bool attr_set[4][64] = {};                                                             \
+    if (!attr_set[add * 2 + full][dev]) {                                                         \
       TG_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,       \
                                          NC * 256 * 4 + kStage));                                 \
-      attr_set[full][dev] = true;                                                                 \
+      attr_set[add * 2 + full][dev] = true;                                                       \
     }                                                                                             \
     kern<<<blocks, WARPS * 32, size_t(cols) * 4 + size_t(kStage), st>>>(                          \
         static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(gamma),           \
         static_cast<const __nv_bfloat16*>(g), eps, static_cast<__nv_bfloat16*>(dx),               \
-        static_cast<float*>(scratch), rows, int(cols));                                           \
+        static_cast<float*>(scratch), rows, int(cols), static_cast<const __nv_bfloat16*>(addend)); \
   } else
     TG_BWD_STAGED_CASE(1, 16, 4) TG_BWD_STAGED_CASE(2, 16, 4) TG_BWD_STAGED_CASE(4, 12, 4) TG_BWD_STAGED_CASE(8, 8, 3) { return TG_ERR_SHAPE; }
 #undef TG_BWD_STAGED_CASE
@@ -758,6 +855,17 @@ extern "C" int tg_rmsnorm_bwd(const void* x, const void* gamma, const void* g, f
       static_cast<const float*>(scratch), static_cast<__nv_bfloat16*>(dgamma), blocks, int(cols));
   TG_CUDA_CHECK(cudaGetLastError());
   return TG_OK;
+}
+
+extern "C" int tg_rmsnorm_bwd(const void* x, const void* gamma, const void* g, float eps, void* dx,
+                              void* dgamma, void* scratch, int64_t rows, int64_t cols, void* stream) {
+  return rmsnorm_bwd_impl(x, gamma, g, nullptr, eps, dx, dgamma, scratch, rows, cols, stream);
+}
+
+extern "C" int tg_rmsnorm_bwd_add(const void* x, const void* gamma, const void* g, const void* addend, float eps,
+                                  void* dx, void* dgamma, void* scratch, int64_t rows, int64_t cols, void* stream) {
+  if (addend == nullptr) return TG_ERR_SHAPE;
+  return rmsnorm_bwd_impl(x, gamma, g, addend, eps, dx, dgamma, scratch, rows, cols, stream);
 }
 
 // ---------------------------------------------------------------------------------------

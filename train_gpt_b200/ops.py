@@ -187,8 +187,39 @@ def rmsnorm_quant_fwd(x, gamma, eps: float, pure: bool = False, want_y: bool = F
     return q, s, y, rn
 
 
-def rmsnorm_bwd(x, gamma, g, eps: float):
-    """kernels.py:104-118.  Returns (dx bf16 like x, dgamma bf16 (D,))."""
+ADD_NORM_MAX_COLS = 2048     # the widest row the fused add + norm kernels take (one warp holds a row)
+
+
+def add_rmsnorm_quant_fwd(x, res, gamma, eps: float, pure: bool = False, want_q: bool = True, want_y: bool = True):
+    """s = bf16(x + res) (the residual add of model.py:68 / :72), then norm + 1x128 quantise of s, one pass.
+    Returns (s, q or None, scales or None, y or None).  Rows wider than ADD_NORM_MAX_COLS: ValueError."""
+    x = _need(x, torch.bfloat16, "x")
+    res = _need(res, torch.bfloat16, "res")
+    gamma = _need(gamma, torch.bfloat16, "gamma")
+    D = x.shape[-1]
+    if res.shape != x.shape:
+        raise ValueError("x and res shapes differ")
+    if gamma.shape != (D,):
+        raise ValueError(f"scale shape {tuple(gamma.shape)} does not match last dim {D}")
+    if D % TILE or D > ADD_NORM_MAX_COLS:
+        raise ValueError(f"K={D} must be a multiple of {TILE} and at most {ADD_NORM_MAX_COLS}")
+    if not (want_q or want_y):
+        raise ValueError("nothing to compute: neither the quantised nor the bf16 output is wanted")
+    rows = x.numel() // D
+    s = torch.empty_like(x)
+    q = torch.empty(x.shape, dtype=F8, device=x.device) if want_q else None
+    sc = torch.empty((*x.shape[:-1], D // TILE), dtype=torch.float32, device=x.device) if want_q else None
+    y = torch.empty_like(x) if want_y else None
+    _lib.check(_lib.load().tg_add_rmsnorm_quant_fwd(_ptr(x), _ptr(res), _ptr(gamma), float(eps), _ptr(s), _ptr(q), _ptr(sc),
+                                                    _ptr(y), None, rows, D, TG_NORM_PURE if pure else TG_NORM_FUSED,
+                                                    _stream()), "tg_add_rmsnorm_quant_fwd")
+    return s, q, sc, y
+
+
+def rmsnorm_bwd(x, gamma, g, eps: float, addend=None):
+    """kernels.py:104-118.  Returns (dx bf16 like x, dgamma bf16 (D,)).  With `addend` (bf16 like x, rows of
+    at most ADD_NORM_MAX_COLS) dx = bf16(addend + the norm's input gradient): the gradient fan-in of a
+    residual junction in the same pass."""
     x = _need(x, torch.bfloat16, "x")
     gamma = _need(gamma, torch.bfloat16, "gamma")
     g = _need(g, torch.bfloat16, "g")
@@ -201,6 +232,15 @@ def rmsnorm_bwd(x, gamma, g, eps: float):
     dgamma = torch.empty((D,), dtype=torch.bfloat16, device=x.device)
     nbytes = lib.tg_rmsnorm_bwd_scratch_bytes(rows, D)
     scratch = torch.empty((max(nbytes, 16),), dtype=torch.uint8, device=x.device)
+    if addend is not None:
+        addend = _need(addend, torch.bfloat16, "addend")
+        if addend.shape != x.shape:
+            raise ValueError("addend and x shapes differ")
+        if D > ADD_NORM_MAX_COLS:
+            raise ValueError(f"the fused add takes rows of at most {ADD_NORM_MAX_COLS}")
+        _lib.check(lib.tg_rmsnorm_bwd_add(_ptr(x), _ptr(gamma), _ptr(g), _ptr(addend), float(eps), _ptr(dx), _ptr(dgamma),
+                                          _ptr(scratch), rows, D, _stream()), "tg_rmsnorm_bwd_add")
+        return dx, dgamma
     _lib.check(lib.tg_rmsnorm_bwd(_ptr(x), _ptr(gamma), _ptr(g), float(eps), _ptr(dx), _ptr(dgamma), _ptr(scratch),
                                   rows, D, _stream()), "tg_rmsnorm_bwd")
     return dx, dgamma

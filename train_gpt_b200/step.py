@@ -49,6 +49,8 @@ class StepConfig:
     mm: str = "fp8"
     mlp: str = "fused"              # "fused": activation and its gradient folded into the quantisers (FP8 mm only); "unfused"
     norm: str = "fused"
+    residual: str = "fused"         # "fused": the residual add runs inside the norm after it, its gradient fan-in inside that
+                                    # norm's backward (norm "fused", FP8 mm, d_model <= 2048); "separate": elementwise adds
     loss: str = "fused"             # "fused": one CUDA pass each way over the logits; "torch": op by op (CPU tests)
     optimizer: str = "fused"        # "fused": optim.ClippedAdamW (CUDA kernels); "torch": torch.optim.AdamW + tensor-op clip
     lr: float = 3e-4
@@ -84,6 +86,36 @@ class _NormQuant(torch.autograd.Function):
             return None, None, None
         dx, dgamma = ops.rmsnorm_bwd(x, gamma, gy.contiguous(), ctx.eps)
         return dx, dgamma, None
+
+
+class _AddNormQuant(torch.autograd.Function):
+    """model.py:68 / :72 followed by :76-77 -- `x = x + branch; h = rms_norm(x)` -- as one kernel
+    (ops.add_rmsnorm_quant_fwd): returns the new residual stream, the norm output and (optionally) its
+    quantised pair.  In the backward pass the gradient of the new stream (arriving over the skip path)
+    and the norm's input gradient are added inside the norm backward kernel, and that sum is the
+    gradient of both `x` and `branch`: neither the forward add nor the fan-in add is a launch."""
+
+    @staticmethod
+    def forward(ctx, x, branch, gamma, eps, want_q):
+        s, q, sc, h = ops.add_rmsnorm_quant_fwd(x, branch, gamma, eps, want_q=want_q, want_y=True)
+        ctx.save_for_backward(s, gamma)
+        ctx.eps = eps
+        ctx.set_materialize_grads(False)
+        if want_q:
+            ctx.mark_non_differentiable(q, sc)
+            return s, h, q, sc
+        return s, h
+
+    @staticmethod
+    def backward(ctx, g_s, g_h, *_):
+        s, gamma = ctx.saved_tensors
+        dgamma = None
+        if g_h is None:
+            d = g_s
+        else:
+            d, dgamma = ops.rmsnorm_bwd(s, gamma, g_h.contiguous(), ctx.eps,
+                                        addend=None if g_s is None else g_s.contiguous())
+        return d, d, dgamma, None, None
 
 
 class _FusedMLP(torch.autograd.Function):
@@ -192,20 +224,37 @@ class GPT:
         c = self.cfg
         B, T = ids.shape
         x = self.embed[ids] + self.pos[:T]                                          # model.py:83
+        # With `residual == "fused"` a branch's output is not added where model.py adds it: it waits in
+        # `branch` and the norm that follows does the add (same values: one bf16 rounding of x + branch).
+        fuse = c.residual == "fused" and c.norm == "fused" and c.mm != "bf16" and c.d_model <= ops.ADD_NORM_MAX_COLS
+        branch = None
+
+        def norm_after(x, branch, gamma, want_q=True):
+            """(new x, h, quantised h) for `x = x + branch; h = norm(x)`; branch None: no add pending."""
+            if branch is None:
+                h, hq = self._norm(x, gamma)
+                return x, h, hq
+            if not fuse:
+                x = x + branch
+                h, hq = self._norm(x, gamma)
+                return x, h, hq
+            out = _AddNormQuant.apply(x, branch, gamma, c.rms_eps, want_q)
+            return out[0], out[1], (fp8.QuantizedActivation(out[1], out[2], out[3]) if want_q else None)
+
         for lp in self.layers:
-            h, hq = self._norm(x, lp["norm1"])                                      # model.py:76
+            x, h, hq = norm_after(x, branch, lp["norm1"])                           # model.py:72 (layer before), :76
             q = self._mm(h, lp["wq"], hq).view(B, T, c.n_heads, c.head_dim)         # model.py:63-65
             k = self._mm(h, lp["wk"], hq).view(B, T, c.n_heads, c.head_dim)
             v = self._mm(h, lp["wv"], hq).view(B, T, c.n_heads, c.head_dim)
             o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True)
-            x = x + self._mm(o.transpose(1, 2).reshape(B, T, -1), lp["wo"])         # model.py:68
-            h, hq = self._norm(x, lp["norm2"])                                      # model.py:77
+            branch = self._mm(o.transpose(1, 2).reshape(B, T, -1), lp["wo"])
+            x, h, hq = norm_after(x, branch, lp["norm2"])                           # model.py:68, :77
             if c.mm == "fp8" and c.mlp == "fused":
-                x = x + _FusedMLP.apply(h, hq, lp["w_up"], lp["w_down"], c.activation)
+                branch = _FusedMLP.apply(h, hq, lp["w_up"], lp["w_down"], c.activation)
             else:
-                x = x + self._mm(self._act(self._mm(h, lp["w_up"], hq)), lp["w_down"])
-        x, _ = self._norm(x, self.final_norm)                                       # model.py:93
-        return x @ self.unembed                                                     # stays bf16 (bench_fp8_norm.py:86)
+                branch = self._mm(self._act(self._mm(h, lp["w_up"], hq)), lp["w_down"])
+        x, h, _ = norm_after(x, branch, self.final_norm, want_q=False)              # model.py:72, :93
+        return h @ self.unembed                                                     # stays bf16 (bench_fp8_norm.py:86)
 
     def forward(self, ids):
         logits = self.raw_logits(ids)

@@ -37,7 +37,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 FFI_TARGETS = (
     "TgQuantizeRowwise", "TgQuantizeColwise", "TgQuantizeBlock128", "TgQuantizeRowcol",
     "TgActQuantizeRowcol", "TgActQuantizeRowcolBwd",
-    "TgRmsnormFwd", "TgRmsnormQuantFwd", "TgRmsnormBwd", "TgRmsnormBwdStatic",
+    "TgRmsnormFwd", "TgRmsnormQuantFwd", "TgAddRmsnormQuantFwd", "TgRmsnormBwd", "TgRmsnormBwdAdd", "TgRmsnormBwdStatic",
     "TgSoftcapCeFwd", "TgSoftcapCeBwd", "TgSumsqBf16", "TgAdamwBf16",
     "TgGemmFwd", "TgGemmDgrad", "TgGemmWgrad",
 )

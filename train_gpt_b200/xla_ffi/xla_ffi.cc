@@ -121,6 +121,17 @@ ffi::Error RmsnormQuantFwd(cudaStream_t s, BF16 x, BF16 gamma, RF8 q, RF32 scale
                "tg_rmsnorm_quant_fwd");
 }
 
+// the residual add folded into the norm that follows it (model.py:68 / :72 then :76-77); rows of at most 2048
+ffi::Error AddRmsnormQuantFwd(cudaStream_t s, BF16 x, BF16 res, BF16 gamma, RBF16 sum, RF8 q, RF32 scales, RBF16 y, RF32 rnorm,
+                              float eps, int32_t mode) {
+  int64_t rows, cols;
+  RowsCols(x, &rows, &cols);
+  return Check(tg_add_rmsnorm_quant_fwd(x.untyped_data(), res.untyped_data(), gamma.untyped_data(), eps, sum->untyped_data(),
+                                        q->untyped_data(), scales->typed_data(), y->untyped_data(), rnorm->typed_data(), rows,
+                                        cols, mode, s),
+               "tg_add_rmsnorm_quant_fwd");
+}
+
 // scratch: a result buffer of tg_rmsnorm_bwd_scratch_bytes(rows, cols) bytes that XLA plans
 ffi::Error RmsnormBwd(cudaStream_t s, BF16 x, BF16 gamma, BF16 g, RBF16 dx, RBF16 dgamma, RU8 scratch, float eps) {
   int64_t rows, cols;
@@ -130,6 +141,17 @@ ffi::Error RmsnormBwd(cudaStream_t s, BF16 x, BF16 gamma, BF16 g, RBF16 dx, RBF1
   return Check(tg_rmsnorm_bwd(x.untyped_data(), gamma.untyped_data(), g.untyped_data(), eps, dx->untyped_data(),
                               dgamma->untyped_data(), scratch->untyped_data(), rows, cols, s),
                "tg_rmsnorm_bwd");
+}
+
+// the backward with the skip path's gradient added in the same pass; rows of at most 2048
+ffi::Error RmsnormBwdAdd(cudaStream_t s, BF16 x, BF16 gamma, BF16 g, BF16 addend, RBF16 dx, RBF16 dgamma, RU8 scratch, float eps) {
+  int64_t rows, cols;
+  RowsCols(x, &rows, &cols);
+  if (static_cast<int64_t>(scratch->element_count()) < tg_rmsnorm_bwd_scratch_bytes(rows, cols))
+    return ffi::Error(ffi::ErrorCode::kInvalidArgument, "TgRmsnormBwdAdd: scratch result smaller than tg_rmsnorm_bwd_scratch_bytes");
+  return Check(tg_rmsnorm_bwd_add(x.untyped_data(), gamma.untyped_data(), g.untyped_data(), addend.untyped_data(), eps,
+                                  dx->untyped_data(), dgamma->untyped_data(), scratch->untyped_data(), rows, cols, s),
+               "tg_rmsnorm_bwd_add");
 }
 
 // the same backward with the scratch inside the library (fixed 4 MiB array; see the header)
@@ -265,6 +287,12 @@ XLA_FFI_DEFINE_HANDLER_SYMBOL(TgRmsnormFwd, RmsnormFwd,
 XLA_FFI_DEFINE_HANDLER_SYMBOL(TgRmsnormQuantFwd, RmsnormQuantFwd,
                               ffi::Ffi::Bind().Ctx<Stream>().Arg<BF16>().Arg<BF16>().Ret<F8>().Ret<F32>().Ret<BF16>().Ret<F32>()
                                   .Attr<float>("eps").Attr<int32_t>("mode"));
+XLA_FFI_DEFINE_HANDLER_SYMBOL(TgAddRmsnormQuantFwd, AddRmsnormQuantFwd,
+                              ffi::Ffi::Bind().Ctx<Stream>().Arg<BF16>().Arg<BF16>().Arg<BF16>().Ret<BF16>().Ret<F8>().Ret<F32>()
+                                  .Ret<BF16>().Ret<F32>().Attr<float>("eps").Attr<int32_t>("mode"));
+XLA_FFI_DEFINE_HANDLER_SYMBOL(TgRmsnormBwdAdd, RmsnormBwdAdd,
+                              ffi::Ffi::Bind().Ctx<Stream>().Arg<BF16>().Arg<BF16>().Arg<BF16>().Arg<BF16>().Ret<BF16>().Ret<BF16>()
+                                  .Ret<U8>().Attr<float>("eps"));
 XLA_FFI_DEFINE_HANDLER_SYMBOL(TgRmsnormBwd, RmsnormBwd,
                               ffi::Ffi::Bind().Ctx<Stream>().Arg<BF16>().Arg<BF16>().Arg<BF16>().Ret<BF16>().Ret<BF16>().Ret<U8>()
                                   .Attr<float>("eps"));
