@@ -148,3 +148,25 @@ def test_rowcol_equals_the_two_separate_quantisers(shape):
     q2, s2 = ops.quantize_colwise(x)
     assert torch.equal(q_row.view(torch.uint8), q1.view(torch.uint8)) and torch.equal(s_row.view(torch.int32), s1.view(torch.int32))
     assert torch.equal(q_col.view(torch.uint8), q2.view(torch.uint8)) and torch.equal(s_col.view(torch.int32), s2.view(torch.int32))
+
+
+def test_rowcol_row_form_into_a_column_slice():
+    """tg_quantize_rowcol_ld: three tensors' row forms written side by side into one wide matrix equal the three
+    dense calls bit for bit, untouched columns stay untouched, and the column forms are the dense ones."""
+    from train_gpt_b200 import ops
+    rows, widths = 300, (256, 128, 384)
+    N = sum(widths)
+    big_q = torch.full((rows, N + 128), 0x55, dtype=torch.uint8, device="cuda").view(torch.float8_e4m3fn)
+    big_s = torch.full((rows, (N + 128) // 128), -7.0, dtype=torch.float32, device="cuda")
+    off = 0
+    for i, w in enumerate(widths):
+        x = to_torch_bf16(normal_bf16(np.random.default_rng(40 + i), (rows, w), outlier_p=0.01))
+        dense = ops.quantize_rowcol(x)
+        out = ops.quantize_rowcol(x, row_out=(big_q[:, off:off + w], big_s[:, off // 128:(off + w) // 128]))
+        assert torch.equal(big_q[:, off:off + w].view(torch.uint8), dense[0].view(torch.uint8))
+        assert torch.equal(big_s[:, off // 128:(off + w) // 128], dense[1])
+        assert torch.equal(out[2].view(torch.uint8), dense[2].view(torch.uint8)) and torch.equal(out[3], dense[3])
+        off += w
+    assert bool((big_q[:, N:].view(torch.uint8) == 0x55).all()) and bool((big_s[:, N // 128:] == -7.0).all())
+    with pytest.raises(TypeError):
+        ops.quantize_rowcol(x, row_out=(big_q[:, :128], big_s[:, :1]))          # wrong shape for this x

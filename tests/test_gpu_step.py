@@ -11,11 +11,11 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _run(mm, norm, steps, activation="gelu", graph=False, mlp="fused"):
+def _run(mm, norm, steps, activation="gelu", graph=False, mlp="fused", **more):
     from train_gpt_b200.step import StepConfig, Trainer, synthetic_batch
     cfg = StepConfig(vocab_size=512, seq_len=128, d_model=256, n_layers=2, n_heads=4, head_dim=64, d_ff=1024,
                      mm=mm, norm=norm, loss="torch" if mm == "bf16" else "fused",
-                     optimizer="torch" if mm == "bf16" else "fused", activation=activation, lr=1e-3, mlp=mlp)
+                     optimizer="torch" if mm == "bf16" else "fused", activation=activation, lr=1e-3, mlp=mlp, **more)
     tr = Trainer(cfg, torch.device("cuda", 0), world_size=1, seed=0, graph=graph)
     losses, gnorms = [], []
     for i in range(steps):
@@ -72,6 +72,20 @@ def test_fused_mlp_follows_the_unfused_step(activation):
     else:
         assert torch.allclose(fused, plain, rtol=1e-3, atol=1e-4), (fused, plain)
         assert torch.allclose(fused_gn, plain_gn, rtol=1e-2, atol=1e-4), (fused_gn, plain_gn)
+
+
+def test_folded_residual_adds_and_single_qkv_dgrad_follow_the_separate_step():
+    """`residual="fused"` moves each residual add into the norm after it (the same bf16 sum, so the forward pass
+    is bit-identical) and adds the skip gradient inside the norm backward with one rounding instead of two;
+    `qkv="fused"` lets one dgrad GEMM sum the three input gradients in float32 instead of two bf16 adds.  Both
+    change only rounding points of the backward pass: the first step's loss is identical, the trajectory and
+    the gradient norm stay within the bars of the graph test."""
+    base, base_gn = _run("fp8", "fused", 12, residual="separate", qkv="separate")
+    for kw in (dict(residual="fused", qkv="separate"), dict(residual="separate", qkv="fused"), dict(residual="fused", qkv="fused")):
+        got, got_gn = _run("fp8", "fused", 12, **kw)
+        assert float(got[0]) == float(base[0]), kw
+        assert torch.allclose(got, base, rtol=1e-3, atol=1e-4), (kw, got, base)
+        assert torch.allclose(got_gn, base_gn, rtol=1e-2, atol=1e-4), (kw, got_gn, base_gn)
 
 
 def test_fp8_loss_curve_matches_bf16_at_the_training_configuration():

@@ -115,7 +115,10 @@ __global__ void __launch_bounds__(kColThreads, 3)
 quantize_colwise_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
                         float* __restrict__ scales, uint8_t* __restrict__ q_row,
                         float* __restrict__ s_row, int64_t rows, int64_t cols,
-                        const __nv_bfloat16* __restrict__ gate = nullptr) {
+                        const __nv_bfloat16* __restrict__ gate = nullptr, int64_t q_row_ld = 0, int64_t s_row_ld = 0) {
+  // row pitches of the row-wise outputs (0: dense, cols and cols / 128): a caller may place the row form
+  // inside a wider matrix, e.g. three gradients side by side for one GEMM that contracts over all of them
+  if (WITH_ROWS && q_row_ld == 0) { q_row_ld = cols; s_row_ld = cols / kTile; }
   __shared__ float s_max[kColThreads / 32][kColPanelCols];
   __shared__ __align__(16) float s_scale[kColPanelCols], s_rcp[kColPanelCols];
   const int cx = threadIdx.x & 15, hw = threadIdx.x >> 4;
@@ -146,13 +149,13 @@ quantize_colwise_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict
     tile_scales_own<kColRowsPerThread>(exchange_tile_amax<kColRowsPerThread>(mr), sr, rr, s_mine, fin);
     {
       const int64_t row = row0 + int64_t(cx & 7) * kColHalfWarps;   // lane j of the half computed row r = j % 8
-      if (cx < kColRowsPerThread && row < rows) s_row[row * (cols / kTile) + blockIdx.x] = s_mine;
+      if (cx < kColRowsPerThread && row < rows) s_row[row * s_row_ld + blockIdx.x] = s_mine;
     }
 #pragma unroll
     for (int r = 0; r < kColRowsPerThread; ++r) {
       const int64_t row = row0 + r * kColHalfWarps;
       if (row < rows)
-        *reinterpret_cast<uint2*>(q_row + row * cols + col0) = fin ? quantize8_sr(w[r], sr[r], rr[r]) : quantize8(w[r], sr[r]);
+        *reinterpret_cast<uint2*>(q_row + row * q_row_ld + col0) = fin ? quantize8_sr(w[r], sr[r], rr[r]) : quantize8(w[r], sr[r]);
     }
   }
   uint32_t m2[4] = {0u, 0u, 0u, 0u};  // packed |.|-maxima of column pairs (0,1) (2,3) (4,5) (6,7)
@@ -300,11 +303,12 @@ extern "C" int tg_quantize_colwise(const void* x, void* q, float* scales, int64_
   return TG_OK;
 }
 
-extern "C" int tg_quantize_rowcol(const void* x, void* q_row, float* s_row, void* q_col, float* s_col,
-                                  int64_t rows, int64_t cols, void* stream) {
+extern "C" int tg_quantize_rowcol_ld(const void* x, void* q_row, int64_t q_row_ld, float* s_row, int64_t s_row_ld,
+                                     void* q_col, float* s_col, int64_t rows, int64_t cols, void* stream) {
   if (rows < 0 || cols < 0 || cols % kTile != 0) return TG_ERR_SHAPE;
+  if (q_row_ld < cols || q_row_ld % 16 != 0 || s_row_ld < cols / kTile) return TG_ERR_SHAPE;
   if (rows == 0 || cols == 0) return TG_OK;
-  if (!aligned16(x) || !aligned16(q_row) || !aligned16(q_col) || !aligned16(s_col) ||
+  if (!aligned16(x) || (reinterpret_cast<uintptr_t>(q_row) & 7u) || !aligned16(q_col) || !aligned16(s_col) ||
       (reinterpret_cast<uintptr_t>(s_row) & 3u))
     return TG_ERR_ALIGN;
   if (int rc = check_arch()) return rc;
@@ -313,9 +317,15 @@ extern "C" int tg_quantize_rowcol(const void* x, void* q_row, float* s_row, void
   quantize_colwise_kernel<true><<<dim3(unsigned(gx), unsigned(gy)), kColThreads, 0,
                                   static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(q_col), s_col, static_cast<uint8_t*>(q_row), s_row, rows,
-      cols);
+      cols, nullptr, q_row_ld, s_row_ld);
   TG_CUDA_CHECK(cudaGetLastError());
   return TG_OK;
+}
+
+extern "C" int tg_quantize_rowcol(const void* x, void* q_row, float* s_row, void* q_col, float* s_col,
+                                  int64_t rows, int64_t cols, void* stream) {
+  if (cols > 0 && !aligned16(q_row)) return TG_ERR_ALIGN;
+  return tg_quantize_rowcol_ld(x, q_row, cols < 16 ? 16 : cols, s_row, cols / kTile, q_col, s_col, rows, cols, stream);
 }
 
 extern "C" int tg_act_quantize_rowcol(const void* x, const void* gate, int act, void* q_row, float* s_row, void* q_col,

@@ -49,6 +49,7 @@ class StepConfig:
     mm: str = "fp8"
     mlp: str = "fused"              # "fused": activation and its gradient folded into the quantisers (FP8 mm only); "unfused"
     norm: str = "fused"
+    qkv: str = "fused"              # "fused": one dgrad GEMM contracts over the gradients of q, k and v (FP8 mm, norm "fused"); "separate"
     residual: str = "fused"         # "fused": the residual add runs inside the norm after it, its gradient fan-in inside that
                                     # norm's backward (norm "fused", FP8 mm, d_model <= 2048); "separate": elementwise adds
     loss: str = "fused"             # "fused": one CUDA pass each way over the logits; "torch": op by op (CPU tests)
@@ -116,6 +117,49 @@ class _AddNormQuant(torch.autograd.Function):
             d, dgamma = ops.rmsnorm_bwd(s, gamma, g_h.contiguous(), ctx.eps,
                                         addend=None if g_s is None else g_s.contiguous())
         return d, d, dgamma, None, None
+
+
+class _QKV(torch.autograd.Function):
+    """model.py:63-65 -- q, k, v = h wq, h wk, h wv -- with fp8.block_scaled_matmul's forward for each, and a
+    backward in which the input gradient dh = gq wq^T + gk wk^T + gv wv^T is ONE GEMM: the three gradients'
+    row-wise forms are written side by side into one (tokens, 3 d) matrix by the quantiser itself
+    (ops.quantize_rowcol(row_out=...)), the three quantised weights are concatenated the same way, and the
+    dgrad contracts over all 3 d columns -- the float32 accumulator does the two adds that autograd would
+    otherwise launch on (tokens, d) tensors.  Bytes and scales are those of the separate calls: a 1x128 tile
+    never straddles two of the tensors.  The weight gradients stay three GEMMs."""
+
+    @staticmethod
+    def forward(ctx, h, hq, wq, wk, wv):
+        a_q, a_s = hq.rowwise()
+        outs, wqs = [], []
+        for w in (wq, wk, wv):
+            w_q, w_s = ops.quantize_block128(w)
+            outs.append(ops.gemm_fwd(a_q, a_s, w_q, w_s, (128, 128)).reshape(*h.shape[:-1], w.shape[1]))
+            wqs.append((w_q, w_s))
+        ctx.save_for_backward(h)
+        ctx.stash = (hq, wqs)
+        return tuple(outs)
+
+    @staticmethod
+    def backward(ctx, *gs):
+        (h,) = ctx.saved_tensors
+        hq, wqs = ctx.stash
+        M = h.numel() // h.shape[-1]
+        widths = [w_q.shape[1] for w_q, _ in wqs]
+        N = sum(widths)
+        G_q = torch.empty((M, N), dtype=torch.float8_e4m3fn, device=h.device)
+        G_s = torch.empty((M, N // 128), dtype=torch.float32, device=h.device)
+        W_q = torch.cat([w_q.view(torch.uint8) for w_q, _ in wqs], dim=1).view(torch.float8_e4m3fn)
+        W_s = torch.cat([w_s for _, w_s in wqs], dim=1)
+        x_qc, x_sc = hq.colwise()
+        dws, off = [], 0
+        for g, n in zip(gs, widths):
+            g2d = g.reshape(M, n).contiguous()
+            _, _, g_qc, g_sc = ops.quantize_rowcol(g2d, row_out=(G_q[:, off:off + n], G_s[:, off // 128:(off + n) // 128]))
+            dws.append(ops.gemm_wgrad(x_qc, x_sc, g_qc, g_sc))
+            off += n
+        dh = ops.gemm_dgrad(G_q, G_s, W_q, W_s, (128, 128))
+        return (dh.reshape(h.shape), None, *dws)
 
 
 class _FusedMLP(torch.autograd.Function):
@@ -243,9 +287,11 @@ class GPT:
 
         for lp in self.layers:
             x, h, hq = norm_after(x, branch, lp["norm1"])                           # model.py:72 (layer before), :76
-            q = self._mm(h, lp["wq"], hq).view(B, T, c.n_heads, c.head_dim)         # model.py:63-65
-            k = self._mm(h, lp["wk"], hq).view(B, T, c.n_heads, c.head_dim)
-            v = self._mm(h, lp["wv"], hq).view(B, T, c.n_heads, c.head_dim)
+            if c.qkv == "fused" and c.mm == "fp8" and hq is not None:
+                q, k, v = _QKV.apply(h, hq, lp["wq"], lp["wk"], lp["wv"])           # model.py:63-65
+            else:
+                q, k, v = (self._mm(h, lp[n], hq) for n in ("wq", "wk", "wv"))
+            q, k, v = (t.view(B, T, c.n_heads, c.head_dim) for t in (q, k, v))
             o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True)
             branch = self._mm(o.transpose(1, 2).reshape(B, T, -1), lp["wo"])
             x, h, hq = norm_after(x, branch, lp["norm2"])                           # model.py:68, :77

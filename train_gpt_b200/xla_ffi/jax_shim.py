@@ -35,7 +35,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 
 # every handler xla_ffi.cc defines with XLA_FFI_DEFINE_HANDLER_SYMBOL
 FFI_TARGETS = (
-    "TgQuantizeRowwise", "TgQuantizeColwise", "TgQuantizeBlock128", "TgQuantizeRowcol",
+    "TgQuantizeRowwise", "TgQuantizeColwise", "TgQuantizeBlock128", "TgQuantizeRowcol", "TgQuantizeRowcolInto",
     "TgActQuantizeRowcol", "TgActQuantizeRowcolBwd",
     "TgRmsnormFwd", "TgRmsnormQuantFwd", "TgAddRmsnormQuantFwd", "TgRmsnormBwd", "TgRmsnormBwdAdd", "TgRmsnormBwdStatic",
     "TgSoftcapCeFwd", "TgSoftcapCeBwd", "TgSumsqBf16", "TgAdamwBf16",

@@ -76,6 +76,26 @@ ffi::Error QuantizeRowcol(cudaStream_t s, BF16 x, RF8 q_row, RF32 s_row, RF8 q_c
                "tg_quantize_rowcol");
 }
 
+// The row form goes into columns [col0, col0 + cols) of wider matrices that several calls fill side by side
+// (the gradients of q, k and v for the one dgrad GEMM that contracts over all of them).  XLA has no strided
+// results: the wide matrices come in as operands and go out as results aliased to them
+// (input_output_aliases={1: 0, 2: 1} on the JAX side), so every call writes its slice in place.
+ffi::Error QuantizeRowcolInto(cudaStream_t s, BF16 x, F8 wide_q_in, F32 wide_s_in, RF8 wide_q, RF32 wide_s, RF8 q_col,
+                              RF32 s_col, int64_t col0) {
+  auto d = x.dimensions();
+  auto wq = wide_q->dimensions();
+  auto ws = wide_s->dimensions();
+  if (d.size() != 2 || wq.size() != 2 || ws.size() != 2 || wq[0] != d[0] || ws[0] != d[0] || col0 < 0 || col0 % 128 != 0 ||
+      col0 + d[1] > wq[1] || (col0 + d[1]) / 128 > ws[1])
+    return ffi::Error(ffi::ErrorCode::kInvalidArgument, "TgQuantizeRowcolInto: the slice does not fit the wide matrices");
+  if (wide_q_in.untyped_data() != wide_q->untyped_data() || wide_s_in.untyped_data() != wide_s->untyped_data())
+    return ffi::Error(ffi::ErrorCode::kInvalidArgument, "TgQuantizeRowcolInto: declare input_output_aliases={1: 0, 2: 1}");
+  return Check(tg_quantize_rowcol_ld(x.untyped_data(), static_cast<uint8_t*>(wide_q->untyped_data()) + col0, wq[1],
+                                     wide_s->typed_data() + col0 / 128, ws[1], q_col->untyped_data(), s_col->typed_data(),
+                                     d[0], d[1], s),
+               "tg_quantize_rowcol_ld");
+}
+
 // act: TG_ACT_RELU2 / TG_ACT_GELU
 ffi::Error ActQuantizeRowcol(cudaStream_t s, BF16 x, RF8 q_row, RF32 s_row, RF8 q_col, RF32 s_col, int32_t act) {
   auto d = x.dimensions();
@@ -275,6 +295,9 @@ XLA_FFI_DEFINE_HANDLER_SYMBOL(TgQuantizeColwise, QuantizeColwise, TG_QUANT_BINDI
 XLA_FFI_DEFINE_HANDLER_SYMBOL(TgQuantizeBlock128, QuantizeBlock128, TG_QUANT_BINDING);
 XLA_FFI_DEFINE_HANDLER_SYMBOL(TgQuantizeRowcol, QuantizeRowcol,
                               ffi::Ffi::Bind().Ctx<Stream>().Arg<BF16>().Ret<F8>().Ret<F32>().Ret<F8>().Ret<F32>());
+XLA_FFI_DEFINE_HANDLER_SYMBOL(TgQuantizeRowcolInto, QuantizeRowcolInto,
+                              ffi::Ffi::Bind().Ctx<Stream>().Arg<BF16>().Arg<F8>().Arg<F32>().Ret<F8>().Ret<F32>().Ret<F8>().Ret<F32>()
+                                  .Attr<int64_t>("col0"));
 XLA_FFI_DEFINE_HANDLER_SYMBOL(TgActQuantizeRowcol, ActQuantizeRowcol,
                               ffi::Ffi::Bind().Ctx<Stream>().Arg<BF16>().Ret<F8>().Ret<F32>().Ret<F8>().Ret<F32>()
                                   .Attr<int32_t>("act"));
