@@ -98,9 +98,40 @@ __device__ __forceinline__ float act_value(float x, float gate) {
   }
   return x;
 }
+// The same erf for two arguments at once in packed f32x2 instructions (the kernel is bound by instruction
+// issue, and the polynomial is most of the activation's instructions); same operations in the same order
+// as the scalar routine, so the same bits.  (Used by the forward form, 0.201 -> 0.182 ms at 32768 x 4096; the
+// backward form, which also needs an expf per element, measured 2 % slower packed and stays scalar.)
+__device__ __forceinline__ float2 erf_of_x_over_sqrt2_pair(float2 x) {
+  const float2 a = make_float2(fminf(fabsf(x.x), 6.081118f), fminf(fabsf(x.y), 6.081118f));
+  auto c2 = [](float c) { return make_float2(c, c); };
+  float2 p = c2(5.117859700476401e-07f);
+  p = __ffma2_rn(p, a, c2(-9.538196536595933e-06f));
+  p = __ffma2_rn(p, a, c2(7.480611384380609e-05f));
+  p = __ffma2_rn(p, a, c2(-0.0002837043721228838f));
+  p = __ffma2_rn(p, a, c2(1.3612322618428152e-05f));
+  p = __ffma2_rn(p, a, c2(0.006932816002517939f));
+  p = __ffma2_rn(p, a, c2(-0.05243593826889992f));
+  p = __ffma2_rn(p, a, c2(-0.4592210352420807f));
+  p = __ffma2_rn(p, a, c2(-1.1511043310165405f));
+  const float2 t = __fmul2_rn(p, a);
+  float2 e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e.x) : "f"(t.x));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e.y) : "f"(t.y));
+  const float2 r = __ffma2_rn(e, c2(-1.0f), c2(1.0f));       // 1 - e, exact product
+  return make_float2(copysignf(r.x, x.x), copysignf(r.y, x.y));
+}
+
 template <int ACT>
 __device__ __forceinline__ uint32_t act_pair(uint32_t x2, uint32_t g2) {
-  return pack_bf16x2(act_value<ACT>(bf16lo(x2), bf16lo(g2)), act_value<ACT>(bf16hi(x2), bf16hi(g2)));
+  if constexpr (ACT == TG_ACT_GELU) {
+    const float2 x = bf16x2_unpack(x2);
+    const float2 one_plus = __fadd2_rn(make_float2(1.f, 1.f), erf_of_x_over_sqrt2_pair(x));
+    const float2 y = __fmul2_rn(__fmul2_rn(x, make_float2(0.5f, 0.5f)), one_plus);
+    return pack_bf16x2(y.x, y.y);
+  } else {
+    return pack_bf16x2(act_value<ACT>(bf16lo(x2), bf16lo(g2)), act_value<ACT>(bf16hi(x2), bf16hi(g2)));
+  }
 }
 template <int ACT>
 __device__ __forceinline__ uint4 act_apply(uint4 x, uint4 g) {
