@@ -120,8 +120,8 @@ class _AddNormQuant(torch.autograd.Function):
 
 
 class _QKV(torch.autograd.Function):
-    """model.py:63-65 -- q, k, v = h wq, h wk, h wv -- with fp8.block_scaled_matmul's forward for each, and a
-    backward in which the input gradient dh = gq wq^T + gk wk^T + gv wv^T is ONE GEMM: the three gradients'
+    """model.py:63-65 -- q, k, v = h wq, h wk, h wv -- as ONE forward GEMM over the three weights side by side
+    (the outputs are column slices of its result: three tensors, no copies), and a backward in which the input gradient dh = gq wq^T + gk wk^T + gv wv^T is ONE GEMM: the three gradients'
     row-wise forms are written side by side into one (tokens, 3 d) matrix by the quantiser itself
     (ops.quantize_rowcol(row_out=...)), the three quantised weights are concatenated the same way, and the
     dgrad contracts over all 3 d columns -- the float32 accumulator does the two adds that autograd would
@@ -131,26 +131,28 @@ class _QKV(torch.autograd.Function):
     @staticmethod
     def forward(ctx, h, hq, wq, wk, wv):
         a_q, a_s = hq.rowwise()
-        outs, wqs = [], []
-        for w in (wq, wk, wv):
-            w_q, w_s = ops.quantize_block128(w)
-            outs.append(ops.gemm_fwd(a_q, a_s, w_q, w_s, (128, 128)).reshape(*h.shape[:-1], w.shape[1]))
-            wqs.append((w_q, w_s))
+        widths = [w.shape[1] for w in (wq, wk, wv)]
+        # the three weights side by side, quantised as one matrix (128x128 tiles never straddle two of them):
+        # one forward GEMM with 3 d output columns instead of three with d (a (tokens, 1024) x (1024, 1024) launch
+        # has 8 contraction blocks per tile and 7 waves: it runs at two thirds of the rate of the wide one)
+        W_q, W_s = ops.quantize_block128(torch.cat((wq, wk, wv), dim=1))
+        qkv = ops.gemm_fwd(a_q, a_s, W_q, W_s, (128, 128))
         ctx.save_for_backward(h)
-        ctx.stash = (hq, wqs)
+        ctx.stash = (hq, W_q, W_s, widths)
+        outs, off = [], 0
+        for n in widths:                                            # column slices: views, no copies
+            outs.append(qkv[:, off:off + n].view(*h.shape[:-1], n))
+            off += n
         return tuple(outs)
 
     @staticmethod
     def backward(ctx, *gs):
         (h,) = ctx.saved_tensors
-        hq, wqs = ctx.stash
+        hq, W_q, W_s, widths = ctx.stash
         M = h.numel() // h.shape[-1]
-        widths = [w_q.shape[1] for w_q, _ in wqs]
         N = sum(widths)
         G_q = torch.empty((M, N), dtype=torch.float8_e4m3fn, device=h.device)
         G_s = torch.empty((M, N // 128), dtype=torch.float32, device=h.device)
-        W_q = torch.cat([w_q.view(torch.uint8) for w_q, _ in wqs], dim=1).view(torch.float8_e4m3fn)
-        W_s = torch.cat([w_s for _, w_s in wqs], dim=1)
         x_qc, x_sc = hq.colwise()
         dws, off = [], 0
         for g, n in zip(gs, widths):
