@@ -81,13 +81,16 @@ int tg_quantize_colwise(const void* x, void* q, float* scales,
 int tg_quantize_rowcol(const void* x, void* q_row, float* s_row, void* q_col, float* s_col,
                        int64_t rows, int64_t cols, void* stream);
 
-/* tg_quantize_rowcol with row pitches for the row-wise outputs: row r of q_row starts q_row_ld bytes
- * after row r-1 (q_row_ld >= cols, a multiple of 16), row r of s_row s_row_ld floats after row r-1
- * (>= cols/128).  Lets a caller lay several tensors' row forms side by side in one matrix -- the
- * gradients of q, k and v for the single GEMM that contracts over all three (model.py:63-65 in the
- * backward pass) -- without a copy.  q_row 8-byte aligned.  No counterpart in the reference. */
+/* tg_quantize_rowcol with row pitches for all four outputs: row r of q_row starts q_row_ld bytes after
+ * row r-1 (>= cols, a multiple of 16), row r of s_row s_row_ld floats after row r-1 (>= cols/128); likewise
+ * q_col_ld (bytes, >= cols, multiple of 16) and s_col_ld (floats, >= cols) for the column-wise pair.
+ * Lets a caller lay several tensors' quantised forms side by side in one matrix -- the gradients of q, k and
+ * v for the single dgrad GEMM that contracts over all three and the single wgrad GEMM that produces all
+ * three weight gradients (model.py:63-65 in the backward pass) -- without a copy.  q_row, q_col 8-byte
+ * aligned.  No counterpart in the reference. */
 int tg_quantize_rowcol_ld(const void* x, void* q_row, int64_t q_row_ld, float* s_row, int64_t s_row_ld,
-                          void* q_col, float* s_col, int64_t rows, int64_t cols, void* stream);
+                          void* q_col, int64_t q_col_ld, float* s_col, int64_t s_col_ld, int64_t rows,
+                          int64_t cols, void* stream);
 
 /* tg_quantize_rowcol of an MLP activation that is computed on the fly instead of being read:
  * the squared ReLU of model.py:72 (`jax.nn.relu(h) ** 2`) or the GELU the benchmark's training

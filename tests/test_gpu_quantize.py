@@ -150,23 +150,32 @@ def test_rowcol_equals_the_two_separate_quantisers(shape):
     assert torch.equal(q_col.view(torch.uint8), q2.view(torch.uint8)) and torch.equal(s_col.view(torch.int32), s2.view(torch.int32))
 
 
-def test_rowcol_row_form_into_a_column_slice():
-    """tg_quantize_rowcol_ld: three tensors' row forms written side by side into one wide matrix equal the three
-    dense calls bit for bit, untouched columns stay untouched, and the column forms are the dense ones."""
+def test_rowcol_forms_into_column_slices():
+    """tg_quantize_rowcol_ld: three tensors' row and column forms written side by side into wide matrices equal the
+    three dense calls bit for bit, and columns nobody owns stay untouched."""
     from train_gpt_b200 import ops
     rows, widths = 300, (256, 128, 384)
     N = sum(widths)
-    big_q = torch.full((rows, N + 128), 0x55, dtype=torch.uint8, device="cuda").view(torch.float8_e4m3fn)
+    f8 = torch.float8_e4m3fn
+    big_q = torch.full((rows, N + 128), 0x55, dtype=torch.uint8, device="cuda").view(f8)
     big_s = torch.full((rows, (N + 128) // 128), -7.0, dtype=torch.float32, device="cuda")
+    big_qc = torch.full((rows, N + 128), 0x55, dtype=torch.uint8, device="cuda").view(f8)
+    big_sc = torch.full(((rows + 127) // 128, N + 128), -7.0, dtype=torch.float32, device="cuda")
     off = 0
     for i, w in enumerate(widths):
         x = to_torch_bf16(normal_bf16(np.random.default_rng(40 + i), (rows, w), outlier_p=0.01))
         dense = ops.quantize_rowcol(x)
-        out = ops.quantize_rowcol(x, row_out=(big_q[:, off:off + w], big_s[:, off // 128:(off + w) // 128]))
+        ops.quantize_rowcol(x, row_out=(big_q[:, off:off + w], big_s[:, off // 128:(off + w) // 128]),
+                            col_out=(big_qc[:, off:off + w], big_sc[:, off:off + w]))
         assert torch.equal(big_q[:, off:off + w].view(torch.uint8), dense[0].view(torch.uint8))
         assert torch.equal(big_s[:, off // 128:(off + w) // 128], dense[1])
-        assert torch.equal(out[2].view(torch.uint8), dense[2].view(torch.uint8)) and torch.equal(out[3], dense[3])
+        assert torch.equal(big_qc[:, off:off + w].view(torch.uint8), dense[2].view(torch.uint8))
+        assert torch.equal(big_sc[:, off:off + w], dense[3])
+        only_rows = ops.quantize_rowcol(x, row_out=(big_q[:, off:off + w], big_s[:, off // 128:(off + w) // 128]))
+        assert torch.equal(only_rows[2].view(torch.uint8), dense[2].view(torch.uint8)) and torch.equal(only_rows[3], dense[3])
         off += w
-    assert bool((big_q[:, N:].view(torch.uint8) == 0x55).all()) and bool((big_s[:, N // 128:] == -7.0).all())
+    for t in (big_q, big_qc):
+        assert bool((t[:, N:].view(torch.uint8) == 0x55).all())
+    assert bool((big_s[:, N // 128:] == -7.0).all()) and bool((big_sc[:, N:] == -7.0).all())
     with pytest.raises(TypeError):
         ops.quantize_rowcol(x, row_out=(big_q[:, :128], big_s[:, :1]))          # wrong shape for this x

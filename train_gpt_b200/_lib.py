@@ -42,7 +42,7 @@ SYMBOLS = {
     "tg_quantize_rowwise": (_i, [_p, _p, _p, _i64, _i64, _p]),
     "tg_quantize_colwise": (_i, [_p, _p, _p, _i64, _i64, _p]),
     "tg_quantize_rowcol": (_i, [_p, _p, _p, _p, _p, _i64, _i64, _p]),
-    "tg_quantize_rowcol_ld": (_i, [_p, _p, _i64, _p, _i64, _p, _p, _i64, _i64, _p]),
+    "tg_quantize_rowcol_ld": (_i, [_p, _p, _i64, _p, _i64, _p, _i64, _p, _i64, _i64, _i64, _p]),
     "tg_act_quantize_rowcol": (_i, [_p, _p, _i, _p, _p, _p, _p, _i64, _i64, _p]),
     "tg_quantize_block128": (_i, [_p, _p, _p, _i64, _i64, _p]),
     "tg_selftest_quantise_division": (_i, [_p, _p]),

@@ -146,10 +146,12 @@ __global__ void __launch_bounds__(kColThreads, 3)
 quantize_colwise_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
                         float* __restrict__ scales, uint8_t* __restrict__ q_row,
                         float* __restrict__ s_row, int64_t rows, int64_t cols,
-                        const __nv_bfloat16* __restrict__ gate = nullptr, int64_t q_row_ld = 0, int64_t s_row_ld = 0) {
-  // row pitches of the row-wise outputs (0: dense, cols and cols / 128): a caller may place the row form
-  // inside a wider matrix, e.g. three gradients side by side for one GEMM that contracts over all of them
+                        const __nv_bfloat16* __restrict__ gate = nullptr, int64_t q_row_ld = 0, int64_t s_row_ld = 0,
+                        int64_t q_col_ld = 0, int64_t s_col_ld = 0) {
+  // row pitches of the outputs (0: dense): a caller may place either form inside a wider matrix, e.g. three
+  // gradients side by side for one GEMM that contracts over all of them or produces all their weight gradients
   if (WITH_ROWS && q_row_ld == 0) { q_row_ld = cols; s_row_ld = cols / kTile; }
+  if (q_col_ld == 0) { q_col_ld = cols; s_col_ld = cols; }
   __shared__ float s_max[kColThreads / 32][kColPanelCols];
   __shared__ __align__(16) float s_scale[kColPanelCols], s_rcp[kColPanelCols];
   const int cx = threadIdx.x & 15, hw = threadIdx.x >> 4;
@@ -219,7 +221,7 @@ quantize_colwise_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict
     s_scale[threadIdx.x] = sc;
     s_rcp[threadIdx.x] = __frcp_rn(sc);
     const int64_t col = int64_t(blockIdx.x) * kColPanelCols + threadIdx.x;
-    if (col < cols) scales[row_blk * cols + col] = sc;
+    if (col < cols) scales[row_blk * s_col_ld + col] = sc;
   }
   __syncthreads();
   if (!col_ok) return;
@@ -257,7 +259,7 @@ quantize_colwise_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict
       b2 = cvt_e4m3x2(__fdiv_rn(bf16lo(v.z), s[4]), __fdiv_rn(bf16hi(v.z), s[5]));
       b3 = cvt_e4m3x2(__fdiv_rn(bf16lo(v.w), s[6]), __fdiv_rn(bf16hi(v.w), s[7]));
     }
-    *reinterpret_cast<uint2*>(q + row * cols + col0) = make_uint2(__byte_perm(b0, b1, 0x5410), __byte_perm(b2, b3, 0x5410));
+    *reinterpret_cast<uint2*>(q + row * q_col_ld + col0) = make_uint2(__byte_perm(b0, b1, 0x5410), __byte_perm(b2, b3, 0x5410));
   }
 }
 
@@ -335,12 +337,14 @@ extern "C" int tg_quantize_colwise(const void* x, void* q, float* scales, int64_
 }
 
 extern "C" int tg_quantize_rowcol_ld(const void* x, void* q_row, int64_t q_row_ld, float* s_row, int64_t s_row_ld,
-                                     void* q_col, float* s_col, int64_t rows, int64_t cols, void* stream) {
+                                     void* q_col, int64_t q_col_ld, float* s_col, int64_t s_col_ld, int64_t rows,
+                                     int64_t cols, void* stream) {
   if (rows < 0 || cols < 0 || cols % kTile != 0) return TG_ERR_SHAPE;
   if (q_row_ld < cols || q_row_ld % 16 != 0 || s_row_ld < cols / kTile) return TG_ERR_SHAPE;
+  if (q_col_ld < cols || q_col_ld % 16 != 0 || s_col_ld < cols) return TG_ERR_SHAPE;
   if (rows == 0 || cols == 0) return TG_OK;
-  if (!aligned16(x) || (reinterpret_cast<uintptr_t>(q_row) & 7u) || !aligned16(q_col) || !aligned16(s_col) ||
-      (reinterpret_cast<uintptr_t>(s_row) & 3u))
+  if (!aligned16(x) || (reinterpret_cast<uintptr_t>(q_row) & 7u) || (reinterpret_cast<uintptr_t>(q_col) & 7u) ||
+      (reinterpret_cast<uintptr_t>(s_col) & 3u) || (reinterpret_cast<uintptr_t>(s_row) & 3u))
     return TG_ERR_ALIGN;
   if (int rc = check_arch()) return rc;
   const int64_t gx = cols / kColPanelCols, gy = (rows + kTile - 1) / kTile;
@@ -348,15 +352,16 @@ extern "C" int tg_quantize_rowcol_ld(const void* x, void* q_row, int64_t q_row_l
   quantize_colwise_kernel<true><<<dim3(unsigned(gx), unsigned(gy)), kColThreads, 0,
                                   static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(q_col), s_col, static_cast<uint8_t*>(q_row), s_row, rows,
-      cols, nullptr, q_row_ld, s_row_ld);
+      cols, nullptr, q_row_ld, s_row_ld, q_col_ld, s_col_ld);
   TG_CUDA_CHECK(cudaGetLastError());
   return TG_OK;
 }
 
 extern "C" int tg_quantize_rowcol(const void* x, void* q_row, float* s_row, void* q_col, float* s_col,
                                   int64_t rows, int64_t cols, void* stream) {
-  if (cols > 0 && !aligned16(q_row)) return TG_ERR_ALIGN;
-  return tg_quantize_rowcol_ld(x, q_row, cols < 16 ? 16 : cols, s_row, cols / kTile, q_col, s_col, rows, cols, stream);
+  if (cols > 0 && (!aligned16(q_row) || !aligned16(q_col) || !aligned16(s_col))) return TG_ERR_ALIGN;
+  const int64_t ld = cols < 16 ? 16 : cols;
+  return tg_quantize_rowcol_ld(x, q_row, ld, s_row, cols / kTile, q_col, ld, s_col, cols, rows, cols, stream);
 }
 
 extern "C" int tg_act_quantize_rowcol(const void* x, const void* gate, int act, void* q_row, float* s_row, void* q_col,

@@ -69,37 +69,46 @@ def quantize_colwise(x: torch.Tensor):
 last_gemm_kernel_launches = 0   # kernels the most recent gemm_* call launched (1, or 2 with the split-contraction reduce)
 
 
-def quantize_rowcol(x: torch.Tensor, row_out=None):
+def quantize_rowcol(x: torch.Tensor, row_out=None, col_out=None):
     """Row-wise (1x128) and column-wise (128x1) quantisation of a 2-D tensor in one pass.
     Returns (q_row, s_row, q_col, s_col), bit-identical to the two separate kernels.
-    `row_out` = (q, s): write the row form into these instead of fresh tensors -- column slices
-    `big_q[:, c0:c0 + cols]`, `big_s[:, c0 // 128:(c0 + cols) // 128]` of wider matrices (unit stride along a row,
-    any row pitch that is a multiple of 16 bytes): several tensors' row forms side by side for one GEMM."""
+    `row_out` = (q, s) / `col_out` = (q, s): write that form into these instead of fresh tensors -- column
+    slices `big_q[:, c0:c0 + cols]` and `big_s[:, c0 // 128:(c0 + cols) // 128]` (row form) or
+    `big_s[:, c0:c0 + cols]` (column form) of wider matrices, unit stride along a row, row pitch a multiple of
+    16 bytes: several tensors' forms side by side for one GEMM."""
     x = _need(x, torch.bfloat16, "x")
     if x.dim() != 2:
         raise ValueError("quantize_rowcol takes a 2-D tensor")
     R, Cc = x.shape
     if Cc % TILE:
         raise ValueError(f"K={Cc} not divisible by block_k={TILE}")
-    q_col = torch.empty((R, Cc), dtype=F8, device=x.device)
-    s_col = torch.empty((_cdiv(R, TILE), Cc), dtype=torch.float32, device=x.device)
-    if row_out is None:
-        q_row = torch.empty((R, Cc), dtype=F8, device=x.device)
-        s_row = torch.empty((R, Cc // TILE), dtype=torch.float32, device=x.device)
-        _lib.check(_lib.load().tg_quantize_rowcol(_ptr(x), _ptr(q_row), _ptr(s_row), _ptr(q_col), _ptr(s_col), R, Cc,
-                                                  _stream()), "tg_quantize_rowcol")
+    dense = row_out is None and col_out is None
+
+    def form(out, s_shape, what):
+        if out is None:
+            return (torch.empty((R, Cc), dtype=F8, device=x.device), torch.empty(s_shape, dtype=torch.float32, device=x.device))
+        q, sc = out
+        if (q.dtype != F8 or sc.dtype != torch.float32 or not q.is_cuda or not sc.is_cuda
+                or tuple(q.shape) != (R, Cc) or tuple(sc.shape) != s_shape):
+            raise TypeError(f"{what} must be an e4m3 {(R, Cc)} and a float32 {s_shape} CUDA tensor")
+        if q.stride(1) != 1 or sc.stride(1) != 1:
+            raise ValueError(f"{what} tensors must have unit stride along a row")
+        return q, sc
+
+    q_row, s_row = form(row_out, (R, Cc // TILE), "row_out")
+    q_col, s_col = form(col_out, (_cdiv(R, TILE), Cc), "col_out")
+    lib = _lib.load()
+    if dense:
+        _lib.check(lib.tg_quantize_rowcol(_ptr(x), _ptr(q_row), _ptr(s_row), _ptr(q_col), _ptr(s_col), R, Cc, _stream()),
+                   "tg_quantize_rowcol")
         return q_row, s_row, q_col, s_col
-    q_row, s_row = row_out
-    if (q_row.dtype != F8 or s_row.dtype != torch.float32 or not q_row.is_cuda or not s_row.is_cuda
-            or tuple(q_row.shape) != (R, Cc) or tuple(s_row.shape) != (R, Cc // TILE)):
-        raise TypeError("row_out must be an e4m3 (rows, cols) and a float32 (rows, cols / 128) CUDA tensor")
-    if R > 1 and (q_row.stride(1) != 1 or s_row.stride(1) != 1):
-        raise ValueError("row_out tensors must have unit stride along a row")
-    q_ld = q_row.stride(0) if R > 1 else max(Cc, 16)
-    s_ld = s_row.stride(0) if R > 1 else Cc // TILE
-    _lib.check(_lib.load().tg_quantize_rowcol_ld(_ptr(x), q_row.data_ptr(), q_ld,
-                                                 s_row.data_ptr(), s_ld, _ptr(q_col), _ptr(s_col), R, Cc, _stream()),
-               "tg_quantize_rowcol_ld")
+
+    def ld(t, least):                       # a one-row tensor's stride(0) is arbitrary
+        return max(t.stride(0), least) if t.shape[0] > 1 else least
+
+    _lib.check(lib.tg_quantize_rowcol_ld(_ptr(x), q_row.data_ptr(), ld(q_row, max(Cc, 16)), s_row.data_ptr(),
+                                         ld(s_row, Cc // TILE), q_col.data_ptr(), ld(q_col, max(Cc, 16)),
+                                         s_col.data_ptr(), ld(s_col, Cc), R, Cc, _stream()), "tg_quantize_rowcol_ld")
     return q_row, s_row, q_col, s_col
 
 

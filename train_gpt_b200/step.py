@@ -125,8 +125,9 @@ class _QKV(torch.autograd.Function):
     row-wise forms are written side by side into one (tokens, 3 d) matrix by the quantiser itself
     (ops.quantize_rowcol(row_out=...)), the three quantised weights are concatenated the same way, and the
     dgrad contracts over all 3 d columns -- the float32 accumulator does the two adds that autograd would
-    otherwise launch on (tokens, d) tensors.  Bytes and scales are those of the separate calls: a 1x128 tile
-    never straddles two of the tensors.  The weight gradients stay three GEMMs."""
+    otherwise launch on (tokens, d) tensors; the column forms go side by side the same way and ONE wgrad GEMM
+    produces the three weight gradients as column slices of its (d, 3 d) result.  Bytes and scales are those of
+    the separate calls: a tile never straddles two of the tensors."""
 
     @staticmethod
     def forward(ctx, h, hq, wq, wk, wv):
@@ -151,16 +152,24 @@ class _QKV(torch.autograd.Function):
         hq, W_q, W_s, widths = ctx.stash
         M = h.numel() // h.shape[-1]
         N = sum(widths)
-        G_q = torch.empty((M, N), dtype=torch.float8_e4m3fn, device=h.device)
+        f8 = torch.float8_e4m3fn
+        G_q = torch.empty((M, N), dtype=f8, device=h.device)                 # row forms side by side: the dgrad's operand
         G_s = torch.empty((M, N // 128), dtype=torch.float32, device=h.device)
-        x_qc, x_sc = hq.colwise()
-        dws, off = [], 0
+        Gc_q = torch.empty((M, N), dtype=f8, device=h.device)                # column forms side by side: the wgrad's
+        Gc_s = torch.empty(((M + 127) // 128, N), dtype=torch.float32, device=h.device)
+        off = 0
         for g, n in zip(gs, widths):
-            g2d = g.reshape(M, n).contiguous()
-            _, _, g_qc, g_sc = ops.quantize_rowcol(g2d, row_out=(G_q[:, off:off + n], G_s[:, off // 128:(off + n) // 128]))
-            dws.append(ops.gemm_wgrad(x_qc, x_sc, g_qc, g_sc))
+            ops.quantize_rowcol(g.reshape(M, n).contiguous(),
+                                row_out=(G_q[:, off:off + n], G_s[:, off // 128:(off + n) // 128]),
+                                col_out=(Gc_q[:, off:off + n], Gc_s[:, off:off + n]))
             off += n
         dh = ops.gemm_dgrad(G_q, G_s, W_q, W_s, (128, 128))
+        x_qc, x_sc = hq.colwise()
+        dW = ops.gemm_wgrad(x_qc, x_sc, Gc_q, Gc_s)                          # (d, 3 d): the three weight gradients
+        dws, off = [], 0
+        for n in widths:
+            dws.append(dW[:, off:off + n])
+            off += n
         return (dh.reshape(h.shape), None, *dws)
 
 

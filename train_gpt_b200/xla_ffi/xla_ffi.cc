@@ -76,23 +76,29 @@ ffi::Error QuantizeRowcol(cudaStream_t s, BF16 x, RF8 q_row, RF32 s_row, RF8 q_c
                "tg_quantize_rowcol");
 }
 
-// The row form goes into columns [col0, col0 + cols) of wider matrices that several calls fill side by side
-// (the gradients of q, k and v for the one dgrad GEMM that contracts over all of them).  XLA has no strided
-// results: the wide matrices come in as operands and go out as results aliased to them
-// (input_output_aliases={1: 0, 2: 1} on the JAX side), so every call writes its slice in place.
-ffi::Error QuantizeRowcolInto(cudaStream_t s, BF16 x, F8 wide_q_in, F32 wide_s_in, RF8 wide_q, RF32 wide_s, RF8 q_col,
-                              RF32 s_col, int64_t col0) {
+// Both forms go into columns [col0, col0 + cols) of wider matrices that several calls fill side by side (the
+// gradients of q, k and v for the one dgrad GEMM that contracts over all of them and the one wgrad GEMM that
+// produces all three weight gradients).  XLA has no strided results: the four wide matrices come in as operands
+// and go out as results aliased to them (input_output_aliases={1: 0, 2: 1, 3: 2, 4: 3} on the JAX side), so
+// every call writes its slices in place.
+ffi::Error QuantizeRowcolInto(cudaStream_t s, BF16 x, F8 wide_q_in, F32 wide_s_in, F8 wide_qc_in, F32 wide_sc_in, RF8 wide_q,
+                              RF32 wide_s, RF8 wide_qc, RF32 wide_sc, int64_t col0) {
   auto d = x.dimensions();
   auto wq = wide_q->dimensions();
   auto ws = wide_s->dimensions();
-  if (d.size() != 2 || wq.size() != 2 || ws.size() != 2 || wq[0] != d[0] || ws[0] != d[0] || col0 < 0 || col0 % 128 != 0 ||
-      col0 + d[1] > wq[1] || (col0 + d[1]) / 128 > ws[1])
+  auto wqc = wide_qc->dimensions();
+  auto wsc = wide_sc->dimensions();
+  if (d.size() != 2 || wq.size() != 2 || ws.size() != 2 || wqc.size() != 2 || wsc.size() != 2 || wq[0] != d[0] ||
+      ws[0] != d[0] || wqc[0] != d[0] || wsc[0] != (d[0] + 127) / 128 || col0 < 0 || col0 % 128 != 0 ||
+      col0 + d[1] > wq[1] || (col0 + d[1]) / 128 > ws[1] || col0 + d[1] > wqc[1] || col0 + d[1] > wsc[1])
     return ffi::Error(ffi::ErrorCode::kInvalidArgument, "TgQuantizeRowcolInto: the slice does not fit the wide matrices");
-  if (wide_q_in.untyped_data() != wide_q->untyped_data() || wide_s_in.untyped_data() != wide_s->untyped_data())
-    return ffi::Error(ffi::ErrorCode::kInvalidArgument, "TgQuantizeRowcolInto: declare input_output_aliases={1: 0, 2: 1}");
+  if (wide_q_in.untyped_data() != wide_q->untyped_data() || wide_s_in.untyped_data() != wide_s->untyped_data() ||
+      wide_qc_in.untyped_data() != wide_qc->untyped_data() || wide_sc_in.untyped_data() != wide_sc->untyped_data())
+    return ffi::Error(ffi::ErrorCode::kInvalidArgument, "TgQuantizeRowcolInto: declare input_output_aliases={1: 0, 2: 1, 3: 2, 4: 3}");
   return Check(tg_quantize_rowcol_ld(x.untyped_data(), static_cast<uint8_t*>(wide_q->untyped_data()) + col0, wq[1],
-                                     wide_s->typed_data() + col0 / 128, ws[1], q_col->untyped_data(), s_col->typed_data(),
-                                     d[0], d[1], s),
+                                     wide_s->typed_data() + col0 / 128, ws[1],
+                                     static_cast<uint8_t*>(wide_qc->untyped_data()) + col0, wqc[1],
+                                     wide_sc->typed_data() + col0, wsc[1], d[0], d[1], s),
                "tg_quantize_rowcol_ld");
 }
 
@@ -296,8 +302,8 @@ XLA_FFI_DEFINE_HANDLER_SYMBOL(TgQuantizeBlock128, QuantizeBlock128, TG_QUANT_BIN
 XLA_FFI_DEFINE_HANDLER_SYMBOL(TgQuantizeRowcol, QuantizeRowcol,
                               ffi::Ffi::Bind().Ctx<Stream>().Arg<BF16>().Ret<F8>().Ret<F32>().Ret<F8>().Ret<F32>());
 XLA_FFI_DEFINE_HANDLER_SYMBOL(TgQuantizeRowcolInto, QuantizeRowcolInto,
-                              ffi::Ffi::Bind().Ctx<Stream>().Arg<BF16>().Arg<F8>().Arg<F32>().Ret<F8>().Ret<F32>().Ret<F8>().Ret<F32>()
-                                  .Attr<int64_t>("col0"));
+                              ffi::Ffi::Bind().Ctx<Stream>().Arg<BF16>().Arg<F8>().Arg<F32>().Arg<F8>().Arg<F32>()
+                                  .Ret<F8>().Ret<F32>().Ret<F8>().Ret<F32>().Attr<int64_t>("col0"));
 XLA_FFI_DEFINE_HANDLER_SYMBOL(TgActQuantizeRowcol, ActQuantizeRowcol,
                               ffi::Ffi::Bind().Ctx<Stream>().Arg<BF16>().Ret<F8>().Ret<F32>().Ret<F8>().Ret<F32>()
                                   .Attr<int32_t>("act"));
