@@ -163,6 +163,12 @@ def bench_norm(rows, cols, warmup, iters):
     out.append(_report("rmsnorm_fwd", m, b, bytes_=4.0 * E + 2 * cols, shape=[rows, cols]))
     m, b = _time(lambda i: ops.rmsnorm_bwd(xs[i], gamma, gs[i], eps), n, warmup, iters, batch=10)
     out.append(_report("rmsnorm_bwd", m, b, bytes_=6.0 * E + 4 * cols, shape=[rows, cols]))
+    if cols <= ops.ADD_NORM_MAX_COLS:
+        # the residual add folded in: x, res read; sum, y, q (+ scales) written / x, g, addend read; dx written
+        m, b = _time(lambda i: ops.add_rmsnorm_quant_fwd(xs[i], gs[i], gamma, eps), n, warmup, iters, batch=10)
+        out.append(_report("add_rmsnorm_quant_fwd", m, b, bytes_=9.03125 * E + 2 * cols, shape=[rows, cols]))
+        m, b = _time(lambda i: ops.rmsnorm_bwd(xs[i], gamma, gs[i], eps, addend=gs[(i + 1) % n]), n, warmup, iters, batch=10)
+        out.append(_report("rmsnorm_bwd_add", m, b, bytes_=8.0 * E + 4 * cols, shape=[rows, cols]))
     return out
 
 
