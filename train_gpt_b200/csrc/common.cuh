@@ -112,13 +112,28 @@ __device__ __forceinline__ float2 bf16x2_unpack_neg(uint32_t w) {
   asm("mad.lo.u32 %0, %1, 65536, 0x80000000;" : "=r"(lo) : "r"(w));   // (w << 16) ^ sign bit, one FMA-pipe instruction
   return make_float2(__uint_as_float(lo), __uint_as_float((w & 0xffff0000u) ^ 0x80000000u));
 }
-// two bf16 values (one word) -> two e4m3 bytes (low 16 bits), finite scale s, nr = -RN(1/s)
-__device__ __forceinline__ uint32_t quantize2_sr(uint32_t w, float2 s2, float2 nr2) {
+// two bf16 values (one word) -> their quotients by the finite scales s2, nr2 = -RN(1/s2)
+__device__ __forceinline__ float2 quotient2_sr(uint32_t w, float2 s2, float2 nr2) {
   const float2 nx = bf16x2_unpack_neg(w);
   const float2 q0 = __fmul2_rn(nx, nr2);
   const float2 e = __ffma2_rn(q0, s2, nx);
-  const float2 q = __ffma2_rn(e, nr2, q0);
+  return __ffma2_rn(e, nr2, q0);
+}
+// two bf16 values (one word) -> two e4m3 bytes (low 16 bits)
+__device__ __forceinline__ uint32_t quantize2_sr(uint32_t w, float2 s2, float2 nr2) {
+  const float2 q = quotient2_sr(w, s2, nr2);
   return cvt_e4m3x2(q.x, q.y);
+}
+// four floats -> four e4m3 bytes in memory order.  The two 16-bit conversion results are joined inside one
+// asm block: handed out as separate 16-bit values they are each widened (a mask) and then permuted together.
+__device__ __forceinline__ uint32_t cvt_e4m3x4(float2 a, float2 b) {
+  uint32_t r;
+  asm("{\n\t.reg .b16 lo, hi;\n\t"
+      "cvt.rn.satfinite.e4m3x2.f32 lo, %2, %1;\n\t"
+      "cvt.rn.satfinite.e4m3x2.f32 hi, %4, %3;\n\t"
+      "mov.b32 %0, {lo, hi};\n\t}"
+      : "=r"(r) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return r;
 }
 
 // Quantise 8 values with a FINITE scale s and its reciprocal r = RN(1/s) that the caller
@@ -126,9 +141,8 @@ __device__ __forceinline__ uint32_t quantize2_sr(uint32_t w, float2 s2, float2 n
 // the 8 e4m3 bytes come back in memory order.
 __device__ __forceinline__ uint2 quantize8_sr(const uint4& w, float s, float r) {
   const float2 s2 = make_float2(s, s), nr2 = make_float2(-r, -r);
-  const uint32_t b0 = quantize2_sr(w.x, s2, nr2), b1 = quantize2_sr(w.y, s2, nr2);
-  const uint32_t b2 = quantize2_sr(w.z, s2, nr2), b3 = quantize2_sr(w.w, s2, nr2);
-  return make_uint2(__byte_perm(b0, b1, 0x5410), __byte_perm(b2, b3, 0x5410));
+  return make_uint2(cvt_e4m3x4(quotient2_sr(w.x, s2, nr2), quotient2_sr(w.y, s2, nr2)),
+                    cvt_e4m3x4(quotient2_sr(w.z, s2, nr2), quotient2_sr(w.w, s2, nr2)));
 }
 
 // Quantise 8 values with `scale` (any value: a NaN or Inf scale takes the IEEE division).
@@ -169,6 +183,21 @@ __device__ __forceinline__ void tile_scales(const float (&amax)[N], float (&s)[N
 // jnp.max wants.  One LOP3 + one VIMNMX.U16x2 per two values.
 constexpr uint32_t kAbsMask2 = 0x7fff7fffu;
 __device__ __forceinline__ uint32_t absmax2(uint32_t m, uint32_t w) { return __vmaxu2(m, w & kAbsMask2); }
+// Magnitude maximum of eight packed words through the packed bf16 max (NaN-propagating): seven instructions
+// on the FMA pipe, which the quantisers leave half idle, instead of eight masks and eight integer maxima on
+// the ALU pipe, which bounds them.  |.| is taken on the leaves only.  A NaN comes back as the canonical
+// 0x7FFF, still the largest pattern under the unsigned order above.
+__device__ __forceinline__ uint32_t absmax2_tree8(uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t e, uint32_t f,
+                                                  uint32_t g, uint32_t h) {
+  uint32_t r;
+  asm("{\n\t.reg .b32 t<8>;\n\t"
+      "abs.bf16x2 t0, %1;\n\tabs.bf16x2 t1, %2;\n\tabs.bf16x2 t2, %3;\n\tabs.bf16x2 t3, %4;\n\t"
+      "abs.bf16x2 t4, %5;\n\tabs.bf16x2 t5, %6;\n\tabs.bf16x2 t6, %7;\n\tabs.bf16x2 t7, %8;\n\t"
+      "max.NaN.bf16x2 t0, t0, t1;\n\tmax.NaN.bf16x2 t2, t2, t3;\n\tmax.NaN.bf16x2 t4, t4, t5;\n\tmax.NaN.bf16x2 t6, t6, t7;\n\t"
+      "max.NaN.bf16x2 t0, t0, t2;\n\tmax.NaN.bf16x2 t4, t4, t6;\n\tmax.NaN.bf16x2 %0, t0, t4;\n\t}"
+      : "=r"(r) : "r"(a), "r"(b), "r"(c), "r"(d), "r"(e), "r"(f), "r"(g), "r"(h));
+  return r;
+}
 __device__ __forceinline__ uint32_t absmax8(const uint4& w, uint32_t m = 0u) {
   return absmax2(absmax2(absmax2(absmax2(m, w.x), w.y), w.z), w.w);
 }

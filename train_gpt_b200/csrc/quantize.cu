@@ -149,38 +149,38 @@ __device__ __forceinline__ uint4 act_apply(uint4 x, uint4 g) {
   return make_uint4(act_pair<ACT>(x.x, g.x), act_pair<ACT>(x.y, g.y), act_pair<ACT>(x.z, g.z), act_pair<ACT>(x.w, g.w));
 }
 
-// WITH_ROWS: the same pass also emits the 1 x 128 (row-wise) quantisation of the panel -- a
-// half-warp spans exactly one row tile -- so a tensor that needs both forms (an upstream
-// gradient: row-wise for dgrad, column-wise for wgrad) is read from HBM once, not twice.
-template <bool WITH_ROWS, int ACT = TG_ACT_NONE>
-__global__ void __launch_bounds__(kColThreads, 3)
-quantize_colwise_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
-                        float* __restrict__ scales, uint8_t* __restrict__ q_row,
-                        float* __restrict__ s_row, int64_t rows, int64_t cols,
-                        const __nv_bfloat16* __restrict__ gate = nullptr, int64_t q_row_ld = 0, int64_t s_row_ld = 0,
-                        int64_t q_col_ld = 0, int64_t s_col_ld = 0) {
-  // row pitches of the outputs (0: dense): a caller may place either form inside a wider matrix, e.g. three
-  // gradients side by side for one GEMM that contracts over all of them or produces all their weight gradients
-  if (WITH_ROWS && q_row_ld == 0) { q_row_ld = cols; s_row_ld = cols / kTile; }
-  if (q_col_ld == 0) { q_col_ld = cols; s_col_ld = cols; }
-  __shared__ float s_max[kColThreads / 32][kColPanelCols];
-  __shared__ __align__(16) float s_scale[kColPanelCols], s_rcp[kColPanelCols];
+// FULL: the panel lies wholly inside the tensor (all 128 rows, all 128 columns), the case of every block of
+// a launch whose sizes are multiples of 128: no bounds predicate is evaluated and row addresses are
+// one 64-bit add apart.  (The kernel is bound by instruction issue; the per-opcode counters showed the
+// address arithmetic and the bounds branches of the general form to be a third of its instructions.)
+template <bool WITH_ROWS, int ACT, bool FULL>
+__device__ __forceinline__ void colwise_panel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
+                                              float* __restrict__ scales, uint8_t* __restrict__ q_row,
+                                              float* __restrict__ s_row, int64_t rows, int64_t cols,
+                                              const __nv_bfloat16* __restrict__ gate, int64_t q_row_ld, int64_t s_row_ld,
+                                              int64_t q_col_ld, int64_t s_col_ld, float (*s_max)[kColPanelCols],
+                                              float* s_scale, float* s_rcp) {
   const int cx = threadIdx.x & 15, hw = threadIdx.x >> 4;
   const int64_t col0 = int64_t(blockIdx.x) * kColPanelCols + cx * 8;
   const int64_t row_blk = blockIdx.y;
   const int64_t row0 = row_blk * kTile + hw;  // this thread's rows: row0 + 16 r
-  const bool col_ok = col0 < cols;            // cols % 8 == 0
+  const bool col_ok = FULL || col0 < cols;    // cols % 8 == 0
 
   uint4 w[kColRowsPerThread];
+  {
+    const __nv_bfloat16* xp = x + row0 * cols + col0;
+    const __nv_bfloat16* gp = gate + row0 * cols + col0;     // only dereferenced by the *_BWD variants
+    const int64_t step = int64_t(kColHalfWarps) * cols;
 #pragma unroll
-  for (int r = 0; r < kColRowsPerThread; ++r) {
-    const int64_t row = row0 + r * kColHalfWarps;
-    w[r] = (col_ok && row < rows) ? ld_nc_v4(x + row * cols + col0) : make_uint4(0, 0, 0, 0);
-    if constexpr (ACT != TG_ACT_NONE) {
-      uint4 g = make_uint4(0, 0, 0, 0);
-      if constexpr (ACT == TG_ACT_RELU2_BWD || ACT == TG_ACT_GELU_BWD)
-        if (col_ok && row < rows) g = ld_nc_v4(gate + row * cols + col0);
-      w[r] = act_apply<ACT>(w[r], g);   // rows past the end stay zero: every variant maps (0, 0) to 0
+    for (int r = 0; r < kColRowsPerThread; ++r, xp += step, gp += step) {
+      const bool ok = FULL || (col_ok && row0 + r * kColHalfWarps < rows);
+      w[r] = ok ? ld_nc_v4(xp) : make_uint4(0, 0, 0, 0);
+      if constexpr (ACT != TG_ACT_NONE) {
+        uint4 g = make_uint4(0, 0, 0, 0);
+        if constexpr (ACT == TG_ACT_RELU2_BWD || ACT == TG_ACT_GELU_BWD)
+          if (ok) g = ld_nc_v4(gp);
+        w[r] = act_apply<ACT>(w[r], g);   // rows past the end stay zero: every variant maps (0, 0) to 0
+      }
     }
   }
   if constexpr (WITH_ROWS) {   // cols % 128 == 0 here: every lane holds real columns
@@ -193,23 +193,27 @@ quantize_colwise_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict
     tile_scales_own<kColRowsPerThread>(exchange_tile_amax<kColRowsPerThread>(mr), sr, rr, s_mine, fin);
     {
       const int64_t row = row0 + int64_t(cx & 7) * kColHalfWarps;   // lane j of the half computed row r = j % 8
-      if (cx < kColRowsPerThread && row < rows) s_row[row * s_row_ld + blockIdx.x] = s_mine;
+      if (cx < kColRowsPerThread && (FULL || row < rows)) s_row[row * s_row_ld + blockIdx.x] = s_mine;
     }
+    uint8_t* qp = q_row + row0 * q_row_ld + col0;
+    const int64_t step = int64_t(kColHalfWarps) * q_row_ld;
+    // one branch around the whole loop, not one per row: a NaN or Inf anywhere in the warp's tiles is the rare case
+    if (fin) {
 #pragma unroll
-    for (int r = 0; r < kColRowsPerThread; ++r) {
-      const int64_t row = row0 + r * kColHalfWarps;
-      if (row < rows)
-        *reinterpret_cast<uint2*>(q_row + row * q_row_ld + col0) = fin ? quantize8_sr(w[r], sr[r], rr[r]) : quantize8(w[r], sr[r]);
+      for (int r = 0; r < kColRowsPerThread; ++r, qp += step)
+        if (FULL || row0 + r * kColHalfWarps < rows) *reinterpret_cast<uint2*>(qp) = quantize8_sr(w[r], sr[r], rr[r]);
+    } else {
+#pragma unroll
+      for (int r = 0; r < kColRowsPerThread; ++r, qp += step)
+        if (FULL || row0 + r * kColHalfWarps < rows) *reinterpret_cast<uint2*>(qp) = quantize8(w[r], sr[r]);
     }
   }
-  uint32_t m2[4] = {0u, 0u, 0u, 0u};  // packed |.|-maxima of column pairs (0,1) (2,3) (4,5) (6,7)
-#pragma unroll
-  for (int r = 0; r < kColRowsPerThread; ++r) {
-    m2[0] = absmax2(m2[0], w[r].x);
-    m2[1] = absmax2(m2[1], w[r].y);
-    m2[2] = absmax2(m2[2], w[r].z);
-    m2[3] = absmax2(m2[3], w[r].w);
-  }
+  uint32_t m2[4];  // packed |.|-maxima of column pairs (0,1) (2,3) (4,5) (6,7) over this thread's rows
+  static_assert(kColRowsPerThread == 8, "the tree below takes 8 rows");
+  m2[0] = absmax2_tree8(w[0].x, w[1].x, w[2].x, w[3].x, w[4].x, w[5].x, w[6].x, w[7].x);
+  m2[1] = absmax2_tree8(w[0].y, w[1].y, w[2].y, w[3].y, w[4].y, w[5].y, w[6].y, w[7].y);
+  m2[2] = absmax2_tree8(w[0].z, w[1].z, w[2].z, w[3].z, w[4].z, w[5].z, w[6].z, w[7].z);
+  m2[3] = absmax2_tree8(w[0].w, w[1].w, w[2].w, w[3].w, w[4].w, w[5].w, w[6].w, w[7].w);
   // the two half-warps of a warp hold the same columns: combine them in registers first
 #pragma unroll
   for (int j = 0; j < 4; ++j) m2[j] = __vmaxu2(m2[j], __shfl_xor_sync(0xffffffffu, m2[j], 16));
@@ -232,7 +236,7 @@ quantize_colwise_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict
     s_scale[threadIdx.x] = sc;
     s_rcp[threadIdx.x] = __frcp_rn(sc);
     const int64_t col = int64_t(blockIdx.x) * kColPanelCols + threadIdx.x;
-    if (col < cols) scales[row_blk * s_col_ld + col] = sc;
+    if (FULL || col < cols) scales[row_blk * s_col_ld + col] = sc;
   }
   __syncthreads();
   if (!col_ok) return;
@@ -253,25 +257,54 @@ quantize_colwise_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict
     s2[j] = make_float2(s[2 * j], s[2 * j + 1]);
     nr2[j] = make_float2(-rc[2 * j], -rc[2 * j + 1]);
   }
+  uint8_t* qp = q + row0 * q_col_ld + col0;
+  const int64_t step = int64_t(kColHalfWarps) * q_col_ld;
+  if (all_finite) {
 #pragma unroll
-  for (int r = 0; r < kColRowsPerThread; ++r) {
-    const int64_t row = row0 + r * kColHalfWarps;
-    if (row >= rows) break;
-    const uint4 v = w[r];
-    uint32_t b0, b1, b2, b3;
-    if (all_finite) {
-      b0 = quantize2_sr(v.x, s2[0], nr2[0]);
-      b1 = quantize2_sr(v.y, s2[1], nr2[1]);
-      b2 = quantize2_sr(v.z, s2[2], nr2[2]);
-      b3 = quantize2_sr(v.w, s2[3], nr2[3]);
-    } else {
-      b0 = cvt_e4m3x2(__fdiv_rn(bf16lo(v.x), s[0]), __fdiv_rn(bf16hi(v.x), s[1]));
-      b1 = cvt_e4m3x2(__fdiv_rn(bf16lo(v.y), s[2]), __fdiv_rn(bf16hi(v.y), s[3]));
-      b2 = cvt_e4m3x2(__fdiv_rn(bf16lo(v.z), s[4]), __fdiv_rn(bf16hi(v.z), s[5]));
-      b3 = cvt_e4m3x2(__fdiv_rn(bf16lo(v.w), s[6]), __fdiv_rn(bf16hi(v.w), s[7]));
+    for (int r = 0; r < kColRowsPerThread; ++r, qp += step) {
+      if (!FULL && row0 + r * kColHalfWarps >= rows) break;
+      const uint4 v = w[r];
+      *reinterpret_cast<uint2*>(qp) =
+          make_uint2(cvt_e4m3x4(quotient2_sr(v.x, s2[0], nr2[0]), quotient2_sr(v.y, s2[1], nr2[1])),
+                     cvt_e4m3x4(quotient2_sr(v.z, s2[2], nr2[2]), quotient2_sr(v.w, s2[3], nr2[3])));
     }
-    *reinterpret_cast<uint2*>(q + row * q_col_ld + col0) = make_uint2(__byte_perm(b0, b1, 0x5410), __byte_perm(b2, b3, 0x5410));
+  } else {
+#pragma unroll
+    for (int r = 0; r < kColRowsPerThread; ++r, qp += step) {
+      if (!FULL && row0 + r * kColHalfWarps >= rows) break;
+      const uint4 v = w[r];
+      const uint32_t b0 = cvt_e4m3x2(__fdiv_rn(bf16lo(v.x), s[0]), __fdiv_rn(bf16hi(v.x), s[1]));
+      const uint32_t b1 = cvt_e4m3x2(__fdiv_rn(bf16lo(v.y), s[2]), __fdiv_rn(bf16hi(v.y), s[3]));
+      const uint32_t b2 = cvt_e4m3x2(__fdiv_rn(bf16lo(v.z), s[4]), __fdiv_rn(bf16hi(v.z), s[5]));
+      const uint32_t b3 = cvt_e4m3x2(__fdiv_rn(bf16lo(v.w), s[6]), __fdiv_rn(bf16hi(v.w), s[7]));
+      *reinterpret_cast<uint2*>(qp) = make_uint2(__byte_perm(b0, b1, 0x5410), __byte_perm(b2, b3, 0x5410));
+    }
   }
+}
+
+// WITH_ROWS: the same pass also emits the 1 x 128 (row-wise) quantisation of the panel -- a
+// half-warp spans exactly one row tile -- so a tensor that needs both forms (an upstream
+// gradient: row-wise for dgrad, column-wise for wgrad) is read from HBM once, not twice.
+template <bool WITH_ROWS, int ACT = TG_ACT_NONE>
+__global__ void __launch_bounds__(kColThreads, 3)
+quantize_colwise_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
+                        float* __restrict__ scales, uint8_t* __restrict__ q_row,
+                        float* __restrict__ s_row, int64_t rows, int64_t cols,
+                        const __nv_bfloat16* __restrict__ gate = nullptr, int64_t q_row_ld = 0, int64_t s_row_ld = 0,
+                        int64_t q_col_ld = 0, int64_t s_col_ld = 0) {
+  // row pitches of the outputs (0: dense): a caller may place either form inside a wider matrix, e.g. three
+  // gradients side by side for one GEMM that contracts over all of them or produces all their weight gradients
+  if (WITH_ROWS && q_row_ld == 0) { q_row_ld = cols; s_row_ld = cols / kTile; }
+  if (q_col_ld == 0) { q_col_ld = cols; s_col_ld = cols; }
+  __shared__ float s_max[kColThreads / 32][kColPanelCols];
+  __shared__ __align__(16) float s_scale[kColPanelCols], s_rcp[kColPanelCols];
+  const bool full = (int64_t(blockIdx.y) + 1) * kTile <= rows && (int64_t(blockIdx.x) + 1) * kColPanelCols <= cols;
+  if (full)
+    colwise_panel<WITH_ROWS, ACT, true>(x, q, scales, q_row, s_row, rows, cols, gate, q_row_ld, s_row_ld, q_col_ld, s_col_ld,
+                                        s_max, s_scale, s_rcp);
+  else
+    colwise_panel<WITH_ROWS, ACT, false>(x, q, scales, q_row, s_row, rows, cols, gate, q_row_ld, s_row_ld, q_col_ld,
+                                         s_col_ld, s_max, s_scale, s_rcp);
 }
 
 // ---------------------------------------------------------------------------------------
