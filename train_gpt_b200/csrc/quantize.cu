@@ -47,8 +47,8 @@ quantize_rowwise_kernel(const uint4* __restrict__ x, uint2* __restrict__ q,
 // 128-row x 128-column panel: a half-warp spans the 128 columns (16 lanes x 8 columns), so
 // each of the 16 half-warps owns every 16th row (8 rows per thread, kept in registers).
 // Column maxima are combined across the warps through shared memory (one thread per column
-// finishes the reduction and the reciprocal), then the same registers are divided and stored.  ~90 registers: two blocks per SM, so one block's loads
-// overlap the other's arithmetic.
+// finishes the reduction and the reciprocal), then the same registers are divided and stored.
+// 80 registers: three blocks per SM, so one block's loads overlap the others' arithmetic.
 // ---------------------------------------------------------------------------------------
 constexpr int kColPanelCols = 128;
 constexpr int kColThreads = 256;

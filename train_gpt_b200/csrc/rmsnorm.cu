@@ -294,11 +294,15 @@ rmsnorm_quant_staged_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bflo
         if (j < G && (FULL || col < cols) && (!ADD || q != nullptr)) scales[row * (cols / kTile) + col / kTile] = s_mine;
       }
       if (ADD && q == nullptr) continue;
+      uint8_t* qp = q + row * cols + col_base + g * G * 256;
+      if (fin) {   // one branch per group: a NaN or Inf in any of the warp's tiles is the rare case
 #pragma unroll
-      for (int u = 0; u < G; ++u) {
-        const int col = col_base + (g * G + u) * 256;
-        if (FULL || col < cols)
-          *reinterpret_cast<uint2*>(q + row * cols + col) = fin ? quantize8_sr(yo[u], s[u], r[u]) : quantize8(yo[u], s[u]);
+        for (int u = 0; u < G; ++u)
+          if (FULL || col_base + (g * G + u) * 256 < cols) *reinterpret_cast<uint2*>(qp + u * 256) = quantize8_sr(yo[u], s[u], r[u]);
+      } else {
+#pragma unroll
+        for (int u = 0; u < G; ++u)
+          if (FULL || col_base + (g * G + u) * 256 < cols) *reinterpret_cast<uint2*>(qp + u * 256) = quantize8(yo[u], s[u]);
       }
     }
   }
