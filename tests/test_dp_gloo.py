@@ -93,3 +93,25 @@ def test_single_rank_step_runs_and_lowers_the_loss():
     for _ in range(30):
         last, _ = tr.step(ids, tgt)
     assert float(last) < float(first) - 0.5
+
+
+def test_flatten_parameters_keeps_values_and_aliases_the_flat_tensors():
+    from train_gpt_b200.dp import GradBuckets
+    torch.manual_seed(0)
+    a = [torch.nn.Parameter(torch.randn(3, 5)), torch.nn.Parameter(torch.randn(7))]
+    b = [torch.nn.Parameter(torch.randn(2, 2))]
+    frozen = torch.nn.Parameter(torch.randn(4), requires_grad=False)
+    before = [p.detach().clone() for p in a + b]
+    gb = GradBuckets([a + [frozen], b, []], world_size=1)
+    flats = gb.flatten_parameters()
+    assert [f.numel() for f in flats] == [22, 4, 0]
+    for p, q in zip(a + b, before):
+        assert torch.equal(p.detach(), q)
+    assert torch.equal(flats[0], torch.cat([before[0].reshape(-1), before[1]]))
+    with torch.no_grad():
+        flats[0].add_(1.0)                       # an update of the flat tensor is an update of the parameters
+    assert torch.equal(a[0].detach(), before[0] + 1.0) and torch.equal(a[1].detach(), before[1] + 1.0)
+    assert gb.params[0] == a and gb.params[1] == b     # frozen parameters take no part
+    # gradients still land in the bucket's flat gradient tensor
+    (a[0].sum() + 2.0 * a[1].sum()).backward()
+    assert torch.equal(gb.flat[0], torch.cat([torch.ones(15), 2.0 * torch.ones(7)]))

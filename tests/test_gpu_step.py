@@ -88,6 +88,39 @@ def test_folded_residual_adds_and_single_qkv_dgrad_follow_the_separate_step():
         assert torch.allclose(got_gn, base_gn, rtol=1e-2, atol=1e-4), (kw, got_gn, base_gn)
 
 
+def test_one_adamw_launch_per_bucket_follows_the_per_tensor_optimizer_bit_for_bit():
+    """`flat_parameters=True` keeps each bucket's parameters and moments in flat tensors and updates a bucket
+    with one launch; the update is elementwise with the same hyper-parameters for every tensor, so losses,
+    gradient norms, parameters and moments equal the per-tensor path exactly.  Eager and graph-captured."""
+    from train_gpt_b200.step import StepConfig, Trainer, synthetic_batch
+    for graph in (False, True):
+        trs = []
+        for flat in (False, True):
+            cfg = StepConfig(vocab_size=512, seq_len=128, d_model=256, n_layers=2, n_heads=4, head_dim=64, d_ff=1024,
+                             mm="fp8", norm="fused", loss="fused", optimizer="fused", activation="gelu", lr=1e-3,
+                             flat_parameters=flat)
+            tr = Trainer(cfg, torch.device("cuda", 0), world_size=1, seed=0, graph=graph)
+            out = []
+            for i in range(6):
+                ids, tgt = synthetic_batch(cfg, 16, "cuda", seed=i, learnable=True)
+                loss, gn = tr.step(ids, tgt)
+                out.append((float(loss), float(gn)))
+            trs.append((tr, out))
+        (a, oa), (b, ob) = trs
+        assert oa == ob, (graph, oa, ob)
+        for pa, pb in zip(a.model.parameters(), b.model.parameters()):
+            assert torch.equal(pa, pb)
+        for ta, tb in zip(a.opt.state_tensors(), b.opt.state_tensors()):
+            assert torch.equal(ta, tb)
+        # the flat layout is real: a bucket's parameters are consecutive slices of one storage
+        params = b.buckets.params[1]
+        base = params[0].data_ptr()
+        off = 0
+        for p in params:
+            assert p.data_ptr() == base + 2 * off
+            off += p.numel()
+
+
 def test_fp8_loss_curve_matches_bf16_at_the_training_configuration():
     """The same 200-step comparison on the benchmark's training configuration itself: 24 layers, d_model 1024,
     16 heads, MLP 4096 (GELU), vocabulary 50304, sequence 1024, batch 32 on one GPU, AdamW lr 3e-4 --

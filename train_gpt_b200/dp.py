@@ -34,8 +34,10 @@ class GradBuckets:
         self._handles = []
         self._hooks = []
         self._nccl = world_size > 1 and dist.is_initialized() and dist.get_backend(group) == "nccl"
+        self.params: List[List[torch.nn.Parameter]] = []
         for bi, params in enumerate(buckets):
             params = [p for p in params if p.requires_grad]
+            self.params.append(params)
             if not params:
                 self.flat.append(torch.empty(0))
                 self._sizes.append(0)
@@ -82,6 +84,27 @@ class GradBuckets:
                 if f.numel():
                     f.mul_(1.0 / self.world_size)
         self._pending = list(self._sizes)
+
+    def flatten_parameters(self) -> List[torch.Tensor]:
+        """Move every bucket's parameters into one flat tensor per bucket, laid out like its gradients
+        (each parameter becomes a view of its slice; values are kept), and return those tensors.  An
+        elementwise optimiser whose hyper-parameters are the same for every tensor can then update a
+        bucket with one launch over (flat parameters, flat gradients) instead of one per tensor."""
+        out = []
+        for params, fg in zip(self.params, self.flat):
+            if not params:
+                out.append(torch.empty(0))
+                continue
+            fp = torch.empty_like(fg)
+            off = 0
+            with torch.no_grad():
+                for p in params:
+                    dst = fp[off:off + p.numel()].view_as(p)
+                    dst.copy_(p.data)
+                    p.data = dst
+                    off += p.numel()
+            out.append(fp)
+        return out
 
     def zero(self):
         for f in self.flat:

@@ -54,6 +54,7 @@ class StepConfig:
                                     # norm's backward (norm "fused", FP8 mm, d_model <= 2048); "separate": elementwise adds
     loss: str = "fused"             # "fused": one CUDA pass each way over the logits; "torch": op by op (CPU tests)
     optimizer: str = "fused"        # "fused": optim.ClippedAdamW (CUDA kernels); "torch": torch.optim.AdamW + tensor-op clip
+    flat_parameters: bool = True    # optimizer "fused": a bucket's parameters and moments are slices of flat tensors, one AdamW launch per bucket
     lr: float = 3e-4
     weight_decay: float = 0.1       # train.py make_optimizer default use
     clip_norm: float = 1.0
@@ -351,8 +352,11 @@ class Trainer:
         self._graph = None
         self._fused_opt = cfg.optimizer == "fused"
         if self._fused_opt:
+            flat = None
+            if cfg.flat_parameters:
+                flat = list(zip(self.buckets.flatten_parameters(), self.buckets.flat, self.buckets.params))
             self.opt = optim.ClippedAdamW(self.model.parameters(), lr=cfg.lr, weight_decay=cfg.weight_decay,
-                                          clip_norm=cfg.clip_norm)
+                                          clip_norm=cfg.clip_norm, flat=flat)
         else:
             self.opt = torch.optim.AdamW(self.model.parameters(), lr=cfg.lr, weight_decay=cfg.weight_decay,
                                          betas=(0.9, 0.999), eps=1e-8, fused=on_gpu, capturable=self._want_graph)
