@@ -115,3 +115,56 @@ def test_flatten_parameters_keeps_values_and_aliases_the_flat_tensors():
     # gradients still land in the bucket's flat gradient tensor
     (a[0].sum() + 2.0 * a[1].sum()).backward()
     assert torch.equal(gb.flat[0], torch.cat([torch.ones(15), 2.0 * torch.ones(7)]))
+
+
+def test_side_by_side_entries_and_direct_gradient_slots():
+    """A tuple entry of a bucket is laid out as column slices of one matrix; a direct slot hands out that
+    matrix (or a lone parameter's slice), its part of the bucket is not zeroed, and `ready()` counts like
+    autograd's hook."""
+    from train_gpt_b200.dp import GradBuckets
+    torch.manual_seed(1)
+    g = torch.nn.Parameter(torch.randn(8))
+    wq, wk, wv = (torch.nn.Parameter(torch.randn(4, n)) for n in (8, 8, 16))
+    wo = torch.nn.Parameter(torch.randn(8, 4))
+    before = [p.detach().clone() for p in (g, wq, wk, wv, wo)]
+    gb = GradBuckets([[g, (wq, wk, wv), wo]], world_size=1)
+    launched = []
+    gb._launch = lambda bi: launched.append(bi)
+    assert gb.flat[0].numel() == 8 + 4 * 32 + 32
+    region = gb.flat[0][8:8 + 128].view(4, 32)
+    assert wk.grad.data_ptr() == region[:, 8:16].data_ptr() and wk.grad.stride() == (32, 1)
+    flats = gb.flatten_parameters()
+    for p, q in zip((g, wq, wk, wv, wo), before):
+        assert torch.equal(p.detach(), q)
+    whole, members = wq.side_by_side
+    assert torch.equal(whole, torch.cat(before[1:4], dim=1)) and members == (wq, wk, wv)
+    assert whole.data_ptr() == flats[0][8:].data_ptr()
+    try:
+        gb.enable_direct([wq, wk])
+        assert False, "a partial group must be refused"
+    except ValueError:
+        pass
+    gb.enable_direct([wq, wk, wv, wo])
+    assert wq.grad_slot is wk.grad_slot is wv.grad_slot and wo.grad_slot is not wq.grad_slot
+    assert gb._zero_ranges[0] == [(0, 8)]
+    gb.flat[0].fill_(7.0)
+    gb.zero()
+    assert float(gb.flat[0][:8].abs().sum()) == 0.0 and float(gb.flat[0][8:].min()) == 7.0
+    out = wq.grad_slot.take()
+    assert out.shape == (4, 32) and out.data_ptr() == region.data_ptr()
+    try:
+        wq.grad_slot.take()
+        assert False, "a slot serves one write per step"
+    except RuntimeError:
+        pass
+    out.copy_(torch.arange(128.0).view(4, 32))
+    wq.grad_slot.ready()
+    assert torch.equal(wv.grad, torch.arange(128.0).view(4, 32)[:, 16:]) and not launched
+    wo.grad_slot.take().fill_(1.0)
+    wo.grad_slot.ready()
+    assert not launched
+    (3.0 * g).sum().backward()                     # the last gradient of the bucket comes through autograd
+    assert launched == [0] and torch.equal(g.grad, torch.full((8,), 3.0))
+    gb.finish()
+    gb.zero()
+    assert wq.grad_slot.take() is not None         # re-armed

@@ -88,37 +88,50 @@ def test_folded_residual_adds_and_single_qkv_dgrad_follow_the_separate_step():
         assert torch.allclose(got_gn, base_gn, rtol=1e-2, atol=1e-4), (kw, got_gn, base_gn)
 
 
-def test_one_adamw_launch_per_bucket_follows_the_per_tensor_optimizer_bit_for_bit():
+def test_flat_optimizer_state_and_direct_weight_gradients_change_no_bit():
     """`flat_parameters=True` keeps each bucket's parameters and moments in flat tensors and updates a bucket
-    with one launch; the update is elementwise with the same hyper-parameters for every tensor, so losses,
-    gradient norms, parameters and moments equal the per-tensor path exactly.  Eager and graph-captured."""
+    with one launch (the update is elementwise with the same hyper-parameters for every tensor);
+    `direct_grads=True` lets the weight-gradient GEMMs write into the gradient buckets instead of autograd
+    adding their results into zeroed ones (0 + g = g); both together lay wq, wk, wv out side by side so that the
+    single q/k/v weight-gradient GEMM writes its whole result in place.  Losses, gradient norms, parameters
+    and moments equal the plain path exactly.  Eager and graph-captured."""
     from train_gpt_b200.step import StepConfig, Trainer, synthetic_batch
+
+    def run(graph, flat, direct):
+        cfg = StepConfig(vocab_size=512, seq_len=128, d_model=256, n_layers=2, n_heads=4, head_dim=64, d_ff=1024,
+                         mm="fp8", norm="fused", loss="fused", optimizer="fused", activation="gelu", lr=1e-3,
+                         flat_parameters=flat, direct_grads=direct)
+        tr = Trainer(cfg, torch.device("cuda", 0), world_size=1, seed=0, graph=graph)
+        out = []
+        for i in range(6):
+            ids, tgt = synthetic_batch(cfg, 16, "cuda", seed=i, learnable=True)
+            loss, gn = tr.step(ids, tgt)
+            out.append((float(loss), float(gn)))
+        return tr, out
+
     for graph in (False, True):
-        trs = []
-        for flat in (False, True):
-            cfg = StepConfig(vocab_size=512, seq_len=128, d_model=256, n_layers=2, n_heads=4, head_dim=64, d_ff=1024,
-                             mm="fp8", norm="fused", loss="fused", optimizer="fused", activation="gelu", lr=1e-3,
-                             flat_parameters=flat)
-            tr = Trainer(cfg, torch.device("cuda", 0), world_size=1, seed=0, graph=graph)
-            out = []
-            for i in range(6):
-                ids, tgt = synthetic_batch(cfg, 16, "cuda", seed=i, learnable=True)
-                loss, gn = tr.step(ids, tgt)
-                out.append((float(loss), float(gn)))
-            trs.append((tr, out))
-        (a, oa), (b, ob) = trs
-        assert oa == ob, (graph, oa, ob)
-        for pa, pb in zip(a.model.parameters(), b.model.parameters()):
-            assert torch.equal(pa, pb)
-        for ta, tb in zip(a.opt.state_tensors(), b.opt.state_tensors()):
-            assert torch.equal(ta, tb)
-        # the flat layout is real: a bucket's parameters are consecutive slices of one storage
-        params = b.buckets.params[1]
-        base = params[0].data_ptr()
-        off = 0
-        for p in params:
-            assert p.data_ptr() == base + 2 * off
-            off += p.numel()
+        a, oa = run(graph, False, False)
+        assert not hasattr(a.model.layers[0]["wo"], "grad_slot")
+        for flat, direct in ((True, False), (False, True), (True, True)):
+            b, ob = run(graph, flat, direct)
+            assert oa == ob, (graph, flat, direct, oa, ob)
+            for pa, pb in zip(a.model.parameters(), b.model.parameters()):
+                assert torch.equal(pa, pb), (graph, flat, direct)
+            for ta, tb in zip(a.opt.state_tensors(), b.opt.state_tensors()):
+                assert torch.equal(ta, tb), (graph, flat, direct)
+            for fa, fb in zip(a.buckets.flat, b.buckets.flat):              # the gradients of the last step, as a multiset per bucket
+                assert torch.equal(fa.float().sort().values, fb.float().sort().values), (graph, flat, direct)
+            lp = b.model.layers[0]
+            assert hasattr(lp["wo"], "grad_slot") == direct
+            assert hasattr(lp["wq"], "grad_slot") == (direct and flat)      # three slices of one GEMM result need the side-by-side layout
+            if flat:
+                # the flat layout is real: parameters are views of one storage per bucket, in the gradients' layout
+                for bi, params in enumerate(b.buckets.params):
+                    base = params[0].data_ptr()
+                    for p_, g_ in zip(params, b.buckets.views(bi, b.buckets.flat[bi])):
+                        assert p_.data_ptr() - base == g_.data_ptr() - b.buckets.flat[bi].data_ptr()
+                        assert p_.stride() == g_.stride()
+                assert lp["wq"].is_contiguous() != direct
 
 
 def test_fp8_loss_curve_matches_bf16_at_the_training_configuration():

@@ -16,14 +16,39 @@ import torch
 import torch.distributed as dist
 
 
+class GradSlot:
+    """Where the op that computes a parameter's gradient may write it, instead of handing autograd a
+    tensor that is then added into the (zeroed) bucket: `take()` gives the destination -- the parameter's
+    slice of its bucket, or, for parameters laid out side by side, the one matrix that holds all their
+    gradients as column slices -- and `ready()` says that the gradients of `params` are now in place (what
+    autograd's post-accumulate hook says for the others).  The op then returns None as that gradient.
+    A slot serves one write per step: a parameter used twice has to go through autograd's accumulation."""
+
+    def __init__(self, owner: "GradBuckets", bi: int, params, out: torch.Tensor):
+        self.owner, self.bi, self.params, self.out, self.used = owner, bi, tuple(params), out, False
+
+    def take(self) -> torch.Tensor:
+        if self.used:
+            raise RuntimeError("a parameter with a direct gradient slot produced two gradients in one step")
+        self.used = True
+        return self.out
+
+    def ready(self) -> None:
+        for _ in self.params:
+            self.owner._one_done(self.bi)
+
+
 class GradBuckets:
     """Flat gradient buckets with overlap of all-reduce and backward.
 
     buckets: list of lists of parameters, in the order their gradients become ready LAST to
-    FIRST does not matter -- each bucket fires when its own parameters are all done.
+    FIRST does not matter -- each bucket fires when its own parameters are all done.  An entry of
+    a bucket may be a tuple of 2-D parameters with the same number of rows: these are laid out SIDE
+    BY SIDE, as column slices of one (rows, total columns) matrix, so that one GEMM can produce all
+    their gradients (their `.grad` views are then not contiguous).
     """
 
-    def __init__(self, buckets: Sequence[Sequence[torch.nn.Parameter]], world_size: int, average: bool = True,
+    def __init__(self, buckets: Sequence[Sequence], world_size: int, average: bool = True,
                  group=None):
         self.world_size = world_size
         self.average = average
@@ -35,33 +60,102 @@ class GradBuckets:
         self._hooks = []
         self._nccl = world_size > 1 and dist.is_initialized() and dist.get_backend(group) == "nccl"
         self.params: List[List[torch.nn.Parameter]] = []
-        for bi, params in enumerate(buckets):
-            params = [p for p in params if p.requires_grad]
+        self._layout: List[list] = []        # per bucket: (offset, rows, cols, (params...)) per entry; rows == 0: one contiguous parameter
+        self._where = {}                     # id(parameter) -> (bucket, entry)
+        self._slots: List[GradSlot] = []
+        for bi, entries in enumerate(buckets):
+            layout, params, off = [], [], 0
+            for e in entries:
+                grp = tuple(p for p in (e if isinstance(e, (tuple, list)) else (e,)) if p.requires_grad)
+                if not grp:
+                    continue
+                if len(grp) > 1:
+                    rows = grp[0].shape[0]
+                    if any(p.dim() != 2 or p.shape[0] != rows for p in grp):
+                        raise ValueError("parameters laid out side by side must be 2-D with the same number of rows")
+                    layout.append((off, rows, sum(p.shape[1] for p in grp), grp))
+                else:
+                    layout.append((off, 0, grp[0].numel(), grp))
+                for p in grp:
+                    self._where[id(p)] = (bi, len(layout) - 1)
+                params.extend(grp)
+                off += sum(p.numel() for p in grp)
             self.params.append(params)
+            self._layout.append(layout)
             if not params:
                 self.flat.append(torch.empty(0))
                 self._sizes.append(0)
                 self._pending.append(0)
                 continue
             dtype, device = params[0].dtype, params[0].device
-            n = sum(p.numel() for p in params)
-            flat = torch.zeros(n, dtype=dtype, device=device)
-            off = 0
-            for p in params:
-                if p.dtype != dtype:
-                    raise TypeError("all parameters of a bucket must share a dtype")
-                p.grad = flat[off:off + p.numel()].view_as(p)
-                off += p.numel()
+            if any(p.dtype != dtype for p in params):
+                raise TypeError("all parameters of a bucket must share a dtype")
+            flat = torch.zeros(off, dtype=dtype, device=device)
+            for p, view in zip(params, self.views(bi, flat)):
+                p.grad = view
                 self._hooks.append(p.register_post_accumulate_grad_hook(self._make_hook(bi)))
             self.flat.append(flat)
             self._sizes.append(len(params))
             self._pending.append(len(params))
+        self._zero_ranges = [[(0, f.numel())] if f.numel() else [] for f in self.flat]
+
+    def views(self, bi: int, flat: torch.Tensor) -> List[torch.Tensor]:
+        """Per-parameter views of `flat` (a tensor as long as bucket `bi`) in the bucket's layout, in the
+        order of `self.params[bi]`."""
+        out = []
+        for off, rows, cols, grp in self._layout[bi]:
+            if rows == 0:
+                out.append(flat[off:off + cols].view_as(grp[0]))
+                continue
+            region, c = flat[off:off + rows * cols].view(rows, cols), 0
+            for p in grp:
+                out.append(region[:, c:c + p.shape[1]])
+                c += p.shape[1]
+        return out
+
+    def enable_direct(self, params) -> None:
+        """Give these parameters a `grad_slot` (GradSlot): their gradients will be written into the bucket
+        by the op that computes them, once per step, so their part of the bucket is not zeroed before the
+        backward pass and no add into it is launched.  Parameters laid out side by side share one slot
+        (all of them must be named); only ops that look for `grad_slot` honour it, so name a parameter here
+        only if every use of it goes through one."""
+        want = {id(p) for p in params}
+        for bi, layout in enumerate(self._layout):
+            for off, rows, cols, grp in layout:
+                hit = [id(p) in want for p in grp]
+                if not any(hit):
+                    continue
+                if not all(hit):
+                    raise ValueError("parameters laid out side by side take a direct gradient slot together or not at all")
+                n = cols if rows == 0 else rows * cols
+                if (off * self.flat[bi].element_size()) % 16 or grp[0].dim() != 2:
+                    continue                 # a GEMM cannot write here (16-byte alignment; matrices only): stays with autograd
+                out = self.flat[bi][off:off + n]
+                out = out.view_as(grp[0]) if rows == 0 else out.view(rows, cols)
+                slot = GradSlot(self, bi, grp, out)
+                self._slots.append(slot)
+                for p in grp:
+                    p.grad_slot = slot
+                # what is left to zero in this bucket
+                left = []
+                for a, b in self._zero_ranges[bi]:
+                    if off >= b or off + n <= a:
+                        left.append((a, b))
+                        continue
+                    if a < off:
+                        left.append((a, off))
+                    if off + n < b:
+                        left.append((off + n, b))
+                self._zero_ranges[bi] = left
+
+    def _one_done(self, bi: int) -> None:
+        self._pending[bi] -= 1
+        if self._pending[bi] == 0:
+            self._launch(bi)
 
     def _make_hook(self, bi: int):
         def hook(_param):
-            self._pending[bi] -= 1
-            if self._pending[bi] == 0:
-                self._launch(bi)
+            self._one_done(bi)
         return hook
 
     def _launch(self, bi: int):
@@ -87,29 +181,36 @@ class GradBuckets:
 
     def flatten_parameters(self) -> List[torch.Tensor]:
         """Move every bucket's parameters into one flat tensor per bucket, laid out like its gradients
-        (each parameter becomes a view of its slice; values are kept), and return those tensors.  An
+        (each parameter becomes a view of its slice -- a column slice, not contiguous, for parameters laid
+        out side by side, which also get `side_by_side = (the whole matrix, the parameters in it)`; values
+        are kept), and return those tensors.  An
         elementwise optimiser whose hyper-parameters are the same for every tensor can then update a
         bucket with one launch over (flat parameters, flat gradients) instead of one per tensor."""
         out = []
-        for params, fg in zip(self.params, self.flat):
+        for bi, (params, fg) in enumerate(zip(self.params, self.flat)):
             if not params:
                 out.append(torch.empty(0))
                 continue
             fp = torch.empty_like(fg)
-            off = 0
             with torch.no_grad():
-                for p in params:
-                    dst = fp[off:off + p.numel()].view_as(p)
+                for p, dst in zip(params, self.views(bi, fp)):
                     dst.copy_(p.data)
                     p.data = dst
-                    off += p.numel()
+            # parameters laid out side by side can be read as the one matrix they are column slices of
+            for off, rows, cols, grp in self._layout[bi]:
+                if rows:
+                    whole = fp[off:off + rows * cols].view(rows, cols)
+                    for q in grp:
+                        q.side_by_side = (whole, grp)
             out.append(fp)
         return out
 
     def zero(self):
-        for f in self.flat:
-            if f.numel():
-                f.zero_()
+        for f, ranges in zip(self.flat, self._zero_ranges):
+            for a, b in ranges:
+                f[a:b].zero_()
+        for slot in self._slots:
+            slot.used = False
 
     def global_norm(self) -> torch.Tensor:
         """optax.global_norm (train.py:132) over all buckets, in float32."""

@@ -124,9 +124,12 @@ def _fp8_forward(a, b, block_k=DEFAULT_BLOCK_K, weight_tile=(128, 1), a_quantize
     return (y, (w_q, w_s)) if return_weight else y
 
 
-def _fp8_backward(block_k, residuals, g, weight_tile=(128, 1), mode="bf16_ste", a_quantized=None, w_quantized=None):
+def _fp8_backward(block_k, residuals, g, weight_tile=(128, 1), mode="bf16_ste", a_quantized=None, w_quantized=None,
+                  b_slot=None):
     """fp8.py:85-98 (mode "bf16_ste"), or the same two GEMMs in block-scaled e4m3.
-    `w_quantized`: the forward's 128x128-tile weight pair, reused instead of quantising again."""
+    `w_quantized`: the forward's 128x128-tile weight pair, reused instead of quantising again.
+    `b_slot`: a gradient slot of the weight (see `_BlockScaledMatmul.backward`); the FP8 modes then write the
+    weight gradient there and return None for it."""
     a, b = residuals
     K = a.shape[-1]
     N = b.shape[1]
@@ -158,10 +161,19 @@ def _fp8_backward(block_k, residuals, g, weight_tile=(128, 1), mode="bf16_ste", 
             x_qc, x_sc = a_quantized.colwise()                        # shared by every GEMM fed from this activation
         else:
             x_qc, x_sc = ops.quantize_colwise(a_2d)
+        if b_slot is not None and b.dtype == torch.bfloat16:
+            ops.gemm_wgrad(x_qc, x_sc, g_qc, g_sc, grad_tile=grad_tile, out=b_slot.take())
+            b_slot.ready()
+            return da.reshape(*leading, K).to(a.dtype), None
         db = ops.gemm_wgrad(x_qc, x_sc, g_qc, g_sc, grad_tile=grad_tile)
     else:
         raise ValueError(f"unknown backward mode {mode!r}; use 'bf16_ste', 'fp8' or 'fp8_blockgrad'")
     return da.reshape(*leading, K).to(a.dtype), db.to(b.dtype)
+
+
+def _plain_2d(b) -> bool:
+    # the direct weight-gradient write needs no padding of N (see _fp8_forward) and a weight as stored
+    return b.dim() == 2 and b.shape[1] % 16 == 0
 
 
 class _BlockScaledMatmul(torch.autograd.Function):
@@ -174,12 +186,17 @@ class _BlockScaledMatmul(torch.autograd.Function):
         ctx.aq = a_quantized if isinstance(a_quantized, QuantizedActivation) else None
         y, wq = _fp8_forward(a, b, block_k, weight_tile, a_quantized, return_weight=True)
         ctx.wq = wq if (tuple(weight_tile) == (128, 128) and backward != "bf16_ste") else None
+        ctx.b_param = b if (isinstance(b, torch.nn.Parameter) and a.dim() >= 2 and _plain_2d(b)) else None
         return y
 
     @staticmethod
     def backward(ctx, g):
         block_k, weight_tile, mode = ctx.cfg
-        da, db = _fp8_backward(block_k, ctx.saved_tensors, g, weight_tile, mode, ctx.aq, ctx.wq)
+        # A weight may carry `grad_slot` (an object with take() -> the tensor its gradient belongs in, and
+        # ready(); train_gpt_b200.dp.GradSlot): the weight-gradient GEMM then writes straight into the flat
+        # gradient bucket and autograd gets None, instead of a fresh tensor that is added into a zeroed bucket.
+        slot = getattr(ctx.b_param, "grad_slot", None) if ctx.b_param is not None else None
+        da, db = _fp8_backward(block_k, ctx.saved_tensors, g, weight_tile, mode, ctx.aq, ctx.wq, b_slot=slot)
         return da, db, None, None, None, None
 
 

@@ -478,17 +478,21 @@ def gemm_dgrad(g_q, g_s, w_q, w_s, weight_tile=(128, 1), out_dtype=torch.bfloat1
                             status=status)
 
 
-def gemm_wgrad(x_qc, x_sc, g_qc, g_sc, out_dtype=torch.bfloat16, status=None, grad_tile=(128, 1)):
+def gemm_wgrad(x_qc, x_sc, g_qc, g_sc, out_dtype=torch.bfloat16, status=None, grad_tile=(128, 1), out=None):
     """dW = x^T g (contracts the tokens).  x_qc (T,K) colwise-quantised (128 tokens x 1),
     scales (ceil(T/128),K).  g_qc (T,N) quantised either the same way, scales (ceil(T/128),N)
     [grad_tile (128,1)], or in 128x128 blocks, scales (ceil(T/128),N/128) [grad_tile (128,128)]:
     one scale per 128 output columns halves the promotion arithmetic and lets the GEMM use its
-    128x256 tile."""
+    128x256 tile.  `out`: a (K, N) bf16 or float32 tensor with unit inner stride to write into (a slice of a
+    gradient bucket, say) instead of a new one."""
     T, K = x_qc.shape
     N = g_qc.shape[1]
+    if out is not None and (tuple(out.shape) != (K, N) or out.stride(1) != 1 or not out.is_cuda
+                            or out.dtype not in (torch.bfloat16, torch.float32)):
+        raise ValueError(f"out must be a ({K}, {N}) bf16 or float32 CUDA tensor with unit inner stride")
     if tuple(grad_tile) == (128, 1):
         sb_str, gran = (1, N), 1
     else:
         sb_str, gran = (1, g_sc.shape[1]), 128
     return gemm_blockscaled(x_qc, g_qc, x_sc, g_sc, M=K, N=N, K=T, a_major=TG_MAJOR_MN, b_major=TG_MAJOR_MN,
-                            sa_strides=(1, K), sb_strides=sb_str, sb_gran_n=gran, out_dtype=out_dtype, status=status)
+                            sa_strides=(1, K), sb_strides=sb_str, sb_gran_n=gran, out_dtype=out_dtype, status=status, out=out)

@@ -23,25 +23,25 @@ class ClippedAdamW:
     def __init__(self, params: Sequence[torch.nn.Parameter], lr: float, weight_decay: float = 1e-4, clip_norm: float = 1.0,
                  b1: float = 0.9, b2: float = 0.999, eps: float = 1e-8, flat=None):
         """flat: optional list of (flat parameters, flat gradients, the parameters that are views of the
-        former, in layout order) -- `dp.GradBuckets.flatten_parameters` makes them; they must cover `params`."""
+        former, views) with views(t) = the per-parameter views of a flat tensor t in that layout --
+        `dp.GradBuckets.flatten_parameters` / `.views` make them; they must cover `params`."""
         self.params = [p for p in params if p.requires_grad]
         self.lr, self.wd, self.clip, self.b1, self.b2, self.eps = lr, weight_decay, clip_norm, b1, b2, eps
         dev = self.params[0].device
         self._flat = None
         if flat is not None:
-            groups = [(fp, fg, list(ps)) for fp, fg, ps in flat if fp.numel()]
-            covered = {id(p) for _, _, ps in groups for p in ps}
+            groups = [(fp, fg, list(ps), views) for fp, fg, ps, views in flat if fp.numel()]
+            covered = {id(p) for _, _, ps, _ in groups for p in ps}
             if covered != {id(p) for p in self.params}:
                 raise ValueError("the flat groups must hold exactly the optimised parameters")
-            self._flat = [(fp, fg, torch.zeros_like(fp), torch.zeros_like(fp)) for fp, fg, _ in groups]
-            by_id = {}
-            for (fp, fg, ps), (_, _, fm, fv) in zip(groups, self._flat):
+            self._flat, by_id = [], {}
+            for fp, fg, ps, views in groups:
                 if fp.shape != fg.shape or sum(p.numel() for p in ps) != fp.numel():
                     raise ValueError("flat parameters, flat gradients and their views must have the same length")
-                off = 0
-                for p in ps:
-                    by_id[id(p)] = (fm[off:off + p.numel()].view_as(p), fv[off:off + p.numel()].view_as(p))
-                    off += p.numel()
+                fm, fv = torch.zeros_like(fp), torch.zeros_like(fp)
+                self._flat.append((fp, fg, fm, fv))
+                for p, m, v in zip(ps, views(fm), views(fv)):
+                    by_id[id(p)] = (m, v)
             self.m = [by_id[id(p)][0] for p in self.params]           # per-parameter views of the flat moments
             self.v = [by_id[id(p)][1] for p in self.params]
         else:

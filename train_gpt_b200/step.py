@@ -55,6 +55,7 @@ class StepConfig:
     loss: str = "fused"             # "fused": one CUDA pass each way over the logits; "torch": op by op (CPU tests)
     optimizer: str = "fused"        # "fused": optim.ClippedAdamW (CUDA kernels); "torch": torch.optim.AdamW + tensor-op clip
     flat_parameters: bool = True    # optimizer "fused": a bucket's parameters and moments are slices of flat tensors, one AdamW launch per bucket
+    direct_grads: bool = True       # mm "fp8": weight-gradient GEMMs write into the gradient buckets (dp.GradSlot) instead of autograd adding into zeroed ones
     lr: float = 3e-4
     weight_decay: float = 0.1       # train.py make_optimizer default use
     clip_norm: float = 1.0
@@ -137,10 +138,19 @@ class _QKV(torch.autograd.Function):
         # the three weights side by side, quantised as one matrix (128x128 tiles never straddle two of them):
         # one forward GEMM with 3 d output columns instead of three with d (a (tokens, 1024) x (1024, 1024) launch
         # has 8 contraction blocks per tile and 7 waves: it runs at two thirds of the rate of the wide one)
-        W_q, W_s = ops.quantize_block128(torch.cat((wq, wk, wv), dim=1))
+        # (when the optimiser keeps the three side by side in one flat matrix -- dp.GradBuckets with a grouped
+        # entry -- that matrix is read as it is; otherwise they are concatenated)
+        sbs = getattr(wq, "side_by_side", None)
+        if sbs is not None and len(sbs[1]) == 3 and all(a is b for a, b in zip(sbs[1], (wq, wk, wv))):
+            W = sbs[0].detach()
+        else:
+            W = torch.cat((wq, wk, wv), dim=1)
+        W_q, W_s = ops.quantize_block128(W)
         qkv = ops.gemm_fwd(a_q, a_s, W_q, W_s, (128, 128))
         ctx.save_for_backward(h)
         ctx.stash = (hq, W_q, W_s, widths)
+        slot = getattr(wq, "grad_slot", None)       # one slot for the three: their gradients side by side (dp.GradSlot)
+        ctx.slot = slot if (slot is not None and all(a is b for a, b in zip(slot.params, (wq, wk, wv)))) else None
         outs, off = [], 0
         for n in widths:                                            # column slices: views, no copies
             outs.append(qkv[:, off:off + n].view(*h.shape[:-1], n))
@@ -166,6 +176,10 @@ class _QKV(torch.autograd.Function):
             off += n
         dh = ops.gemm_dgrad(G_q, G_s, W_q, W_s, (128, 128))
         x_qc, x_sc = hq.colwise()
+        if ctx.slot is not None:                                             # straight into the gradient bucket
+            ops.gemm_wgrad(x_qc, x_sc, Gc_q, Gc_s, out=ctx.slot.take())
+            ctx.slot.ready()
+            return (dh.reshape(h.shape), None, None, None, None)
         dW = ops.gemm_wgrad(x_qc, x_sc, Gc_q, Gc_s)                          # (d, 3 d): the three weight gradients
         dws, off = [], 0
         for n in widths:
@@ -194,6 +208,7 @@ class _FusedMLP(torch.autograd.Function):
         y = ops.gemm_fwd(r_q, r_s, wd_q, wd_s, (128, 128))
         ctx.save_for_backward(h, u)
         ctx.stash = (hq, act, c_q, c_s, wu_q, wu_s, wd_q, wd_s)
+        ctx.slots = (getattr(w_up, "grad_slot", None), getattr(w_down, "grad_slot", None))   # dp.GradSlot or None
         return y.reshape(*h.shape[:-1], w_down.shape[1])
 
     @staticmethod
@@ -203,11 +218,18 @@ class _FusedMLP(torch.autograd.Function):
         g2d = g.reshape(-1, g.shape[-1]).contiguous()
         g_q, g_s, g_qc, g_sc = ops.quantize_rowcol(g2d)
         da = ops.gemm_dgrad(g_q, g_s, wd_q, wd_s, (128, 128))                    # gradient at act(u)
-        dw_down = ops.gemm_wgrad(c_q, c_s, g_qc, g_sc)
+        s_up, s_down = ctx.slots
+        dw_down = ops.gemm_wgrad(c_q, c_s, g_qc, g_sc, out=None if s_down is None else s_down.take())
+        if s_down is not None:                                                   # written into the gradient bucket
+            s_down.ready()
+            dw_down = None
         du_q, du_s, du_qc, du_sc = ops.act_quantize_rowcol(u, act + "_bwd", da)  # da * act'(u), quantised, never stored
         dh = ops.gemm_dgrad(du_q, du_s, wu_q, wu_s, (128, 128))
         x_qc, x_sc = hq.colwise() if hq is not None else ops.quantize_colwise(h.reshape(-1, h.shape[-1]))
-        dw_up = ops.gemm_wgrad(x_qc, x_sc, du_qc, du_sc)
+        dw_up = ops.gemm_wgrad(x_qc, x_sc, du_qc, du_sc, out=None if s_up is None else s_up.take())
+        if s_up is not None:
+            s_up.ready()
+            dw_up = None
         return dh.reshape(h.shape), None, dw_up, dw_down, None
 
 
@@ -237,16 +259,25 @@ class GPT:
         self.final_norm = ones(d)
         self.unembed = normal((d, cfg.vocab_size))
 
-    def buckets(self):
-        """Gradient buckets in the order backward finishes them: head group, layers L-1..0, embeddings."""
+    def buckets(self, qkv_side_by_side: bool = False):
+        """Gradient buckets in the order backward finishes them: head group, layers L-1..0, embeddings.
+        qkv_side_by_side: wq, wk, wv of a layer form one entry (a tuple), which dp.GradBuckets lays out as
+        column slices of one matrix -- the layout in which ONE weight-gradient GEMM produces all three."""
         out = [[self.unembed, self.final_norm]]
         for lp in reversed(self.layers):
-            out.append(list(lp.values()))
+            if qkv_side_by_side:
+                out.append([lp["norm1"], (lp["wq"], lp["wk"], lp["wv"]), lp["wo"], lp["norm2"], lp["w_up"], lp["w_down"]])
+            else:
+                out.append(list(lp.values()))
         out.append([self.embed, self.pos])
         return out
 
     def parameters(self):
         return [p for b in self.buckets() for p in b]
+
+    def matrices(self):
+        """The parameters whose only use is an FP8 linear (model.py:63-72): wq, wk, wv, wo, w_up, w_down."""
+        return [lp[n] for lp in self.layers for n in ("wq", "wk", "wv", "wo", "w_up", "w_down")]
 
     # ---- the mm / norm seam (bench_fp8_norm.py:81-86) -------------------------------------
     def _mm(self, a, w, aq=None):
@@ -346,15 +377,28 @@ class Trainer:
         if torch.device(device).type == "cuda":
             ops.set_gemm_reserved_sms(RESERVED_SMS_DP if (reserve_sms is None and world_size > 1) else int(reserve_sms or 0))
         self.model = GPT(cfg, device, seed)                     # same seed on every rank: replicated weights
-        self.buckets = GradBuckets(self.model.buckets(), world_size)
         on_gpu = torch.device(device).type == "cuda"
+        self._fused_opt = cfg.optimizer == "fused"
+        # Weight gradients written straight into the buckets by their GEMMs (no zero fill of that part, no add
+        # into it): needs every use of those weights to be an FP8 linear of this package.  With q, k, v as one
+        # weight-gradient GEMM its (d, 3 d) result is the bucket entry itself, so the three are laid out side
+        # by side -- parameters and moments too, which is why that needs the flat optimiser state.
+        direct = bool(cfg.direct_grads) and on_gpu and cfg.mm == "fp8"
+        fused_qkv = cfg.qkv == "fused" and cfg.norm == "fused"
+        side_by_side = direct and fused_qkv and self._fused_opt and cfg.flat_parameters
+        self.buckets = GradBuckets(self.model.buckets(qkv_side_by_side=side_by_side), world_size)
+        if direct:
+            skip = () if (side_by_side or not fused_qkv) else ("wq", "wk", "wv")    # three slices of one GEMM result: autograd adds them
+            self.buckets.enable_direct([lp[n] for lp in self.model.layers for n in ("wq", "wk", "wv", "wo", "w_up", "w_down")
+                                        if n not in skip])
         self._want_graph = bool(graph) and on_gpu
         self._graph = None
-        self._fused_opt = cfg.optimizer == "fused"
         if self._fused_opt:
             flat = None
             if cfg.flat_parameters:
-                flat = list(zip(self.buckets.flatten_parameters(), self.buckets.flat, self.buckets.params))
+                b = self.buckets
+                flat = [(fp, fg, ps, (lambda t, bi=bi: b.views(bi, t)))
+                        for bi, (fp, fg, ps) in enumerate(zip(b.flatten_parameters(), b.flat, b.params))]
             self.opt = optim.ClippedAdamW(self.model.parameters(), lr=cfg.lr, weight_decay=cfg.weight_decay,
                                           clip_norm=cfg.clip_norm, flat=flat)
         else:
