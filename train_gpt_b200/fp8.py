@@ -67,6 +67,15 @@ class QuantizedActivation:
         self._row = None if q is None else (q.reshape(-1, K), scales.reshape(-1, K // DEFAULT_BLOCK_K))
         self._col = None if q_col is None else (q_col, scales_col)
 
+    @classmethod
+    def both(cls, a: torch.Tensor) -> "QuantizedActivation":
+        """Both forms from ONE read of `a` (ops.quantize_rowcol): for an activation whose linear layer will be
+        differentiated -- the forward GEMM takes the row form now, the weight-gradient GEMM the column form later."""
+        K = a.shape[-1]
+        a2d = a.reshape(-1, K).to(torch.bfloat16)
+        q, s, qc, sc = ops.quantize_rowcol(a2d)
+        return cls(a2d, q, s, qc, sc)
+
     def rowwise(self):
         if self._row is None:
             self._row = ops.quantize_rowwise(self.a2d.to(torch.bfloat16))

@@ -336,7 +336,10 @@ class GPT:
                 q, k, v = (self._mm(h, lp[n], hq) for n in ("wq", "wk", "wv"))
             q, k, v = (t.view(B, T, c.n_heads, c.head_dim) for t in (q, k, v))
             o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True)
-            branch = self._mm(o.transpose(1, 2).reshape(B, T, -1), lp["wo"])
+            o = o.transpose(1, 2).reshape(B, T, -1)
+            # the attention output feeds one linear: both its quantised forms from one read when a backward pass follows
+            oq = fp8.QuantizedActivation.both(o) if (c.mm == "fp8" and torch.is_grad_enabled() and o.shape[-1] % 128 == 0) else None
+            branch = self._mm(o, lp["wo"], oq)
             x, h, hq = norm_after(x, branch, lp["norm2"])                           # model.py:68, :77
             if c.mm == "fp8" and c.mlp == "fused":
                 branch = _FusedMLP.apply(h, hq, lp["w_up"], lp["w_down"], c.activation)
