@@ -172,7 +172,8 @@ def test_fp8_backward_with_block_quantised_gradient(M, K, N):
     _close(from_torch_bf16(db), db_ref)
 
 
-@pytest.mark.parametrize("K,N,T,gran", [(256, 384, 4096, 1), (512, 512, 8192, 1), (256, 512, 4096, 128)])
+@pytest.mark.parametrize("K,N,T,gran", [(256, 384, 4096, 1), (512, 512, 8192, 1), (256, 512, 4096, 128),
+                                        (256, 384, 5632, 1), (256, 512, 5632, 128)])   # 44 blocks: 5 ranges of 9, 9, 9, 9, 8
 def test_wgrad_with_split_contraction_matches_unsplit_and_oracle(K, N, T, gran):
     """Few output tiles, long contraction: the library cuts the contraction when given workspace.
     The cut changes only the float32 summation order."""

@@ -241,6 +241,14 @@ def test_decoder_layer_wgrad_at_size_split_and_unsplit(K, N):
     _wgrad_case(f"layer {K}x{N}", _normal((TOKENS, K), 1), _normal((TOKENS, N), 3), seed=K + N, plans=(True, False))
 
 
+@pytest.mark.parametrize("K,N", [(1024, 1024), (4096, 1024), (1024, 4096), (1024, 3072)])
+def test_training_configuration_wgrad_at_size_with_unequal_contraction_ranges(K, N):
+    """The weight gradients of the 24-layer training configuration (d_model 1024, MLP 4096, q/k/v side by side) at
+    32768 tokens.  256 contraction blocks over few output tiles: the planner cuts them into 3 ranges of 86, 85, 85
+    blocks for the 1024 x 1024 one (48 tiles x 3 = 144 work items on 148 SMs) -- ranges need not be equal."""
+    _wgrad_case(f"training {K}x{N}", _normal((TOKENS, K), 5), _normal((TOKENS, N), 6), seed=K + N + 1, plans=(True, False))
+
+
 # ---- benchmark configuration 4: Student-t(3) activations, squares and skinny M ---------------
 
 @pytest.mark.parametrize("n", [4096, 8192])

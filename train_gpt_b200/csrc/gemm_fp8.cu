@@ -144,6 +144,7 @@ struct GemmParams {
   void* d;              // output, row pitch ldd elements
   long long ldd;
   int M, N, nkb;        // nkb = contraction blocks per work item (all of them unless the contraction is split)
+  int nkb_rem;          // ... plus one for the first nkb_rem ranges of a split contraction (ranges need not be equal)
   int a_mn, b_mn;       // 1 = MN-major storage
   int tiles_m, tiles_n;
   int band;             // tile rows per band of the tile numbering
@@ -151,7 +152,7 @@ struct GemmParams {
   // tiles per band, rows of the last band), 0 = divide the slow way (the exactness bound x * d < 2^40
   // does not hold); rows of a full band = `band`, its reciprocal in mg_band
   unsigned long long mg_tiles, mg_per_band, mg_band, mg_last;
-  int ksplit;           // the contraction is cut into this many equal ranges; range s of a tile is its own
+  int ksplit;           // the contraction is cut into this many ranges; range s of a tile is its own
                         // work item and writes its float32 partial sums to d + s * slice_elems
   long long slice_elems;
   unsigned* status;
@@ -372,6 +373,9 @@ __device__ __forceinline__ void item_split(const GemmParams& p, int item, int n_
   ks = fast_div(item, n_tiles, p.mg_tiles);
   tile = item - ks * n_tiles;
 }
+// contraction range -> its first block and its number of blocks
+__device__ __forceinline__ int range_blocks(const GemmParams& p, int ks) { return p.nkb + (ks < p.nkb_rem ? 1 : 0); }
+__device__ __forceinline__ int range_first(const GemmParams& p, int ks) { return ks * p.nkb + min(ks, p.nkb_rem); }
 
 template <int BN_, int SB_GRAN, bool OUT_F32>
 __global__ void __launch_bounds__((Cfg<BN_, SB_GRAN, OUT_F32>::threads), 1)
@@ -446,8 +450,9 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
         item_split(p, item, n_tiles, ks, tile);
         tile_coords(p, tile, tm, tn);
         const int m0 = tm * BM, n0 = tn * BN;
-        int k0 = ks * p.nkb * BK;
-        for (int kb = 0; kb < p.nkb; ++kb, k0 += BK) {
+        int k0 = range_first(p, ks) * BK;
+        const int nkb = range_blocks(p, ks);
+        for (int kb = 0; kb < nkb; ++kb, k0 += BK) {
           ok = __all_sync(0xffffffffu, mbar_wait(empty0 + 8u * s, ph, abort_flag, p.status, 1u));
           if (!ok) break;
           if (elect_one()) {
@@ -478,9 +483,12 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const uint64_t desc_a0 = make_smem_desc(sbase), desc_b0 = make_smem_desc(sbase + kTileBytes);
       const uint32_t desc_hi = uint32_t(desc_a0 >> 32);
       const uint32_t a_lo0 = uint32_t(desc_a0), b_lo0 = uint32_t(desc_b0);
-      int my_items = 0;
-      for (int item = first_item; item < n_items; item += item_step) ++my_items;
-      const uint32_t total = uint32_t(my_items) * uint32_t(p.nkb);
+      uint32_t total = 0;                     // contraction blocks of all this block's work items
+      for (int item = first_item; item < n_items; item += item_step) {
+        int ks, tile;
+        item_split(p, item, n_tiles, ks, tile);
+        total += uint32_t(range_blocks(p, ks));
+      }
       bool ok = true;
       // A barrier operation has tens of cycles of latency even when the barrier is already complete,
       // and this loop is a chain of them: it does ONE wait instruction per block, lanes 0-15 polling
@@ -575,10 +583,11 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // misses L1 every time and the loop would run at one L2 round trip per block.  Instead lane l
     // fetches the scale of block 32 g + l once per 32 blocks and a shuffle hands each block its value.
     float sb_grp = 0.f, sb_nxt = 0.f;
+    int open_nkb = p.nkb;          // contraction blocks of the work item opened last (ranges of a split need not be equal)
     auto load_sb_lane = [&](int g) {
       float v = 0.f;
       const int kb = 32 * g + lane;
-      if (kb < p.nkb) v = ldg_f32(p.sb + sb_off + uint32_t(kb) * uint32_t(p.sb_sk));
+      if (kb < open_nkb) v = ldg_f32(p.sb + sb_off + uint32_t(kb) * uint32_t(p.sb_sk));
       return v;
     };
     auto load_sb_cols = [&]() {     // per-column scales of the block sb_off points at
@@ -590,7 +599,8 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
     auto open_tile = [&](int item) {
       int ks, tile, tm, tn;
       item_split(p, item, n_tiles, ks, tile);
-      const uint32_t kb_off = uint32_t(ks) * uint32_t(p.nkb);
+      const uint32_t kb_off = uint32_t(range_first(p, ks));
+      open_nkb = range_blocks(p, ks);
       tile_coords(p, tile, tm, tn);
       const int n0 = tn * BN;
       const int m = min(tm * BM + r, p.M - 1);       // rows past M: a valid scale, results never stored
@@ -621,7 +631,7 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
       for (int j = 0; j < kCols / 2; ++j) acc[j] = make_float2(0.f, 0.f);
 
-      const int nkb = p.nkb;
+      const int nkb = open_nkb;    // set when this item was opened (before the previous tile's epilogue)
       // One contraction block.  `bsel` says which accumulator buffer it drains: a compile-time constant
       // in the two-buffer variants (the block loop below is unrolled by two, so barrier addresses, TMEM
       // address and staging slot are immediates), the carried counter otherwise.
@@ -919,7 +929,7 @@ static int launch_gemm(const tg_gemm_args* a, GemmParams p, cudaStream_t st) {
     p.mg_band = magic(per_band, p.band);
     p.mg_last = last_rows > 0 ? magic(per_band, last_rows) : 0ull;
   }
-  if (n_items > INT32_MAX || n_items * p.nkb > INT32_MAX) return TG_ERR_TOO_LARGE;
+  if (n_items > INT32_MAX || n_items * (p.nkb + 1) > INT32_MAX) return TG_ERR_TOO_LARGE;
   const int sms = gemm_sms();
   const int grid = int(n_items < sms ? n_items : sms);
   // the attribute is per device: set it once for each device this instantiation runs on
@@ -1015,11 +1025,12 @@ static SplitPlan plan_split(const tg_gemm_args* a, int bn) {
   const int64_t tiles = ((a->M + BM - 1) / BM) * ((a->N + bn - 1) / bn);
   const int sms = gemm_sms();
   if (sms <= 0) return pl;
+  // S ranges of nkb / S blocks, the first nkb % S of them one longer; the longest sets the pace of a wave
   double best = 0.0;
-  for (int S = 1; S <= 8; S *= 2) {
-    if (nkb % S != 0 || (S > 1 && nkb / S < 8)) break;
+  for (int S = 1; S <= 8; ++S) {
+    if (S > 1 && nkb / S < 8) break;
     const int64_t waves = (tiles * S + sms - 1) / sms;
-    double cost = double(waves) * (double(nkb / S) + 3.0);
+    double cost = double(waves) * (double((nkb + S - 1) / S) + 3.0);
     if (S > 1) cost += double(4 * S + 2) * double(a->M) * double(a->N) / 4.0e6;
     if (S == 1 || cost < best * 0.98) { best = cost; pl.S = S; }
   }
@@ -1109,6 +1120,7 @@ static int run_skinny(const tg_gemm_args* a, const SkinnyPlan& sk, cudaStream_t 
   p.sb = a->sa; p.sb_sn = a->sa_stride_m; p.sb_sk = a->sa_stride_kb;
   p.d = a->workspace; p.ldd = sk.pitch;
   p.M = int(t.M); p.N = int(t.N); p.nkb = int(a->K / BK) / sk.S;
+  p.nkb_rem = 0;
   p.a_mn = t.a_major == TG_MAJOR_MN; p.b_mn = false;
   p.tiles_m = p.tiles_n = 0;
   p.band = 1;
@@ -1159,6 +1171,7 @@ extern "C" int tg_gemm_fp8_blockscaled(const tg_gemm_args* a, void* stream) {
   p.sb = a->sb; p.sb_sn = a->sb_stride_n; p.sb_sk = a->sb_stride_kb;
   p.d = a->d; p.ldd = a->ldd;
   p.M = int(a->M); p.N = int(a->N); p.nkb = int((a->K + BK - 1) / BK);
+  p.nkb_rem = 0;
   p.a_mn = a->a_major == TG_MAJOR_MN; p.b_mn = a->b_major == TG_MAJOR_MN;
   p.tiles_m = p.tiles_n = 0;
   p.band = 1;
@@ -1170,6 +1183,7 @@ extern "C" int tg_gemm_fp8_blockscaled(const tg_gemm_args* a, void* stream) {
   const SplitPlan pl = plan_split(a, bn);
   if (pl.S > 1 && a->workspace != nullptr && a->workspace_bytes >= pl.bytes && aligned16(a->workspace)) {
     p.ksplit = pl.S;
+    p.nkb_rem = p.nkb % pl.S;
     p.nkb /= pl.S;
     p.slice_elems = a->M * a->N;
     p.d = a->workspace;
