@@ -168,3 +168,26 @@ def test_side_by_side_entries_and_direct_gradient_slots():
     gb.finish()
     gb.zero()
     assert wq.grad_slot.take() is not None         # re-armed
+
+
+def test_deferred_exchange_waits_for_flush():
+    """defer=True: a finished bucket is exchanged at the next flush() (or at finish()), in the order the buckets
+    finished; without it, at once."""
+    from train_gpt_b200.dp import GradBuckets
+    a, b = torch.nn.Parameter(torch.randn(4)), torch.nn.Parameter(torch.randn(3))
+    for defer in (False, True):
+        gb = GradBuckets([[a], [b]], world_size=2, average=False, defer=defer)
+        sent = []
+        gb._exchange = lambda bi: sent.append(bi)
+        gb.zero()
+        (2.0 * b).sum().backward()
+        assert sent == ([] if defer else [1])
+        gb.flush()
+        assert sent == [1]
+        a.sum().backward()
+        assert sent == ([1] if defer else [1, 0])
+        gb.finish()
+        assert sent == [1, 0]
+        for h in gb._hooks:
+            h.remove()
+        a.grad = b.grad = None

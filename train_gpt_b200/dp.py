@@ -49,7 +49,12 @@ class GradBuckets:
     """
 
     def __init__(self, buckets: Sequence[Sequence], world_size: int, average: bool = True,
-                 group=None):
+                 group=None, defer: bool = False):
+        """defer: a finished bucket's all-reduce is not launched at once but at the next `flush()` (or at
+        `finish()`): the caller picks points of the backward pass where the collective's kernel shares the GPU
+        gracefully (see `flush`)."""
+        self.defer = defer
+        self._deferred: List[int] = []
         self.world_size = world_size
         self.average = average
         self.group = group
@@ -159,6 +164,23 @@ class GradBuckets:
         return hook
 
     def _launch(self, bi: int):
+        if self.defer and self.world_size > 1:
+            self._deferred.append(bi)
+            return
+        self._exchange(bi)
+
+    def flush(self):
+        """Launch the all-reduce of every bucket that has finished since the last call.  An all-reduce kernel
+        needs a few SMs.  Launched while a persistent GEMM holds all of them it waits for that GEMM to end, takes
+        its SMs, and the NEXT persistent GEMM then runs short of those SMs until the collective is done: the
+        blocks assigned to them start late and the whole GEMM waits for them.  Launched just before a kernel of
+        many short blocks (attention backward), it gets its SMs as blocks retire and gives them back before the
+        next GEMM."""
+        pending, self._deferred = self._deferred, []
+        for bi in pending:
+            self._exchange(bi)
+
+    def _exchange(self, bi: int):
         if self.world_size > 1:
             # NCCL averages inside the collective; gloo (the CPU tests) has no AVG: sum, then scale in finish()
             op = dist.ReduceOp.AVG if (self.average and self._nccl) else dist.ReduceOp.SUM
@@ -166,10 +188,11 @@ class GradBuckets:
 
     def finish(self):
         """Wait for every bucket's exchange, turn sums into means, re-arm for the next step."""
+        self.flush()
         for bi, left in enumerate(self._pending):
             if left != 0 and self._sizes[bi] != 0:
                 # a parameter that got no gradient this step: exchange what there is
-                self._launch(bi)
+                self._exchange(bi)
         for h in self._handles:
             h.wait()
         self._handles.clear()

@@ -55,6 +55,7 @@ class StepConfig:
     loss: str = "fused"             # "fused": one CUDA pass each way over the logits; "torch": op by op (CPU tests)
     optimizer: str = "fused"        # "fused": optim.ClippedAdamW (CUDA kernels); "torch": torch.optim.AdamW + tensor-op clip
     flat_parameters: bool = True    # optimizer "fused": a bucket's parameters and moments are slices of flat tensors, one AdamW launch per bucket
+    defer_exchange: bool = True     # more than one rank: a finished bucket's all-reduce is launched just before the next attention backward, not at once
     direct_grads: bool = True       # mm "fp8": weight-gradient GEMMs write into the gradient buckets (dp.GradSlot) instead of autograd adding into zeroed ones
     lr: float = 3e-4
     weight_decay: float = 0.1       # train.py make_optimizer default use
@@ -119,6 +120,23 @@ class _AddNormQuant(torch.autograd.Function):
             d, dgamma = ops.rmsnorm_bwd(s, gamma, g_h.contiguous(), ctx.eps,
                                         addend=None if g_s is None else g_s.contiguous())
         return d, d, dgamma, None, None
+
+
+class _ExchangePoint(torch.autograd.Function):
+    """Identity whose backward tells the gradient buckets to launch the all-reduces that are due
+    (dp.GradBuckets.flush): placed on the attention output, so that this happens just before the
+    attention backward kernels of a layer -- many short blocks, beside which a collective's kernel gets SMs
+    and returns them without holding up a persistent GEMM."""
+
+    @staticmethod
+    def forward(ctx, x, buckets):
+        ctx.buckets = buckets
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        ctx.buckets.flush()
+        return g, None
 
 
 class _QKV(torch.autograd.Function):
@@ -258,6 +276,7 @@ class GPT:
                 "w_down": normal((ff, d), proj_std)})
         self.final_norm = ones(d)
         self.unembed = normal((d, cfg.vocab_size))
+        self.exchange = None            # gradient buckets with a deferred exchange (data-parallel training): see _ExchangePoint
 
     def buckets(self, qkv_side_by_side: bool = False):
         """Gradient buckets in the order backward finishes them: head group, layers L-1..0, embeddings.
@@ -336,6 +355,8 @@ class GPT:
                 q, k, v = (self._mm(h, lp[n], hq) for n in ("wq", "wk", "wv"))
             q, k, v = (t.view(B, T, c.n_heads, c.head_dim) for t in (q, k, v))
             o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True)
+            if self.exchange is not None and torch.is_grad_enabled():
+                o = _ExchangePoint.apply(o, self.exchange)
             o = o.transpose(1, 2).reshape(B, T, -1)
             # the attention output feeds one linear: both its quantised forms from one read when a backward pass follows
             oq = fp8.QuantizedActivation.both(o) if (c.mm == "fp8" and torch.is_grad_enabled() and o.shape[-1] % 128 == 0) else None
@@ -389,7 +410,10 @@ class Trainer:
         direct = bool(cfg.direct_grads) and on_gpu and cfg.mm == "fp8"
         fused_qkv = cfg.qkv == "fused" and cfg.norm == "fused"
         side_by_side = direct and fused_qkv and self._fused_opt and cfg.flat_parameters
-        self.buckets = GradBuckets(self.model.buckets(qkv_side_by_side=side_by_side), world_size)
+        defer = bool(cfg.defer_exchange) and world_size > 1 and on_gpu
+        self.buckets = GradBuckets(self.model.buckets(qkv_side_by_side=side_by_side), world_size, defer=defer)
+        if defer:
+            self.model.exchange = self.buckets
         if direct:
             skip = () if (side_by_side or not fused_qkv) else ("wq", "wk", "wv")    # three slices of one GEMM result: autograd adds them
             self.buckets.enable_direct([lp[n] for lp in self.model.layers for n in ("wq", "wk", "wv", "wo", "w_up", "w_down")
