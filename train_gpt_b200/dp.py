@@ -5,8 +5,14 @@ has.  train-gpt itself is single-device (train.py:1); the exchange belongs betwe
 Gradients of one bucket (one decoder layer, or the embedding / head group) live in ONE flat
 buffer; every parameter's `.grad` is a view into it.  When the last gradient of a bucket has
 been accumulated during backward, the bucket's all-reduce is launched asynchronously, so the
-exchange of layer l overlaps the backward of layers l-1 .. 0.  NCCL (NVLink/NVSwitch) on GPUs,
+exchange of layer l overlaps the backward of layers l-1 .. 0 (at once, or -- `defer=True` -- at
+points of the backward pass the caller picks with `flush()`).  NCCL (NVLink/NVSwitch) on GPUs,
 gloo on CPU -- the class only uses `torch.distributed`.
+
+Two options serve the CUDA step (train_gpt_b200.step): the buckets can hand out gradient slots
+(`enable_direct`, `GradSlot`) that a weight-gradient GEMM writes into, and they can lay a bucket's
+parameters out like its gradients (`flatten_parameters`) for an optimiser that updates a bucket
+with one launch.
 """
 from __future__ import annotations
 
