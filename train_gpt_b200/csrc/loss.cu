@@ -74,7 +74,8 @@ __device__ __forceinline__ void lse_merge(float& m, float& s, float m2, float s2
 // f32x2 operations on the two halves of each loaded word: the exact quotient x / c (one reciprocal multiply and one
 // correction step, as in the quantisers), one rounding to a bf16 pair, two table loads, the cap multiply and its
 // rounding, and the online softmax.
-// 512 threads, three blocks per SM (the table is 64 KB): 1.57 ms at 32768 x 50304; 256 / 384 / 768 threads measured 1.98 / 1.66 / 1.65
+// 512 threads, three blocks per SM (the table is 64 KB): 1.57 ms at 32768 x 50304 (1.50 with the prefetch below); 256 / 384 / 768
+// threads measured 1.98 / 1.66 / 1.65
 constexpr int kLossFwdThreads = 512;
 
 __global__ void __launch_bounds__(kLossFwdThreads)
@@ -91,8 +92,12 @@ softcap_ce_fwd_kernel(const __nv_bfloat16* __restrict__ logits, const int32_t* _
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
     const __nv_bfloat16* p = logits + row * ld;
     float m = -3.0e38f, s = 0.f;
+    // the next piece is loaded before this one is worked on: the kernel's top stall was the wait for its
+    // one 16-byte load per thread
+    uint4 w_next = threadIdx.x * 8 < vocab ? ld_nc_v4(p + threadIdx.x * 8) : make_uint4(0u, 0u, 0u, 0u);
     for (int i = threadIdx.x * 8; i < vocab; i += kLossFwdThreads * 8) {
-      const uint4 w = ld_nc_v4(p + i);
+      const uint4 w = w_next;
+      if (i + kLossFwdThreads * 8 < vocab) w_next = ld_nc_v4(p + i + kLossFwdThreads * 8);
       const uint32_t xi[4] = {w.x, w.y, w.z, w.w};
       float2 z[4];
       uint4 to;
