@@ -39,9 +39,14 @@ def _worker(rank, world, port, out_dir):
     launched = []
     orig = tr.buckets._launch
     tr.buckets._launch = lambda bi: (launched.append(bi), orig(bi))[1]
+    exchanged, pending_at_exchange = [], []
+    orig_x = tr.buckets._exchange
+    tr.buckets._exchange = lambda bi: (exchanged.append(bi), pending_at_exchange.append(len(launched)), orig_x(bi))[2]
+    assert tr.buckets.defer and tr.model.exchange is tr.buckets      # more than one rank: the exchange is deferred
     loss, gnorm = tr.step(ids, tgt)
     torch.save({"loss": loss, "gnorm": gnorm, "grads": [f.clone() for f in tr.buckets.flat],
-                "params": [p.detach().clone() for p in tr.model.parameters()], "launched": launched},
+                "params": [p.detach().clone() for p in tr.model.parameters()], "launched": launched,
+                "exchanged": exchanged, "pending_at_exchange": pending_at_exchange},
                os.path.join(out_dir, f"rank{rank}.pt"))
     dist.barrier()
     dist.destroy_process_group()
@@ -56,6 +61,10 @@ def test_two_rank_gradient_exchange_matches_full_batch(tmp_path):
     # every bucket fired exactly once, in backward order (head group first, embeddings last)
     n_buckets = 2 + _cfg().n_layers
     assert r0["launched"] == list(range(n_buckets)) and r1["launched"] == r0["launched"]
+    # ... and was exchanged once, in the same order, at a flush point (the attention backward of a later layer) or
+    # at the end of the backward pass: never before it had finished
+    assert r0["exchanged"] == r0["launched"] and r1["exchanged"] == r0["launched"]
+    assert all(n > bi for bi, n in zip(r0["exchanged"], r0["pending_at_exchange"]))
     # both ranks hold the same reduced gradients, norm and updated parameters
     for a, b in zip(r0["grads"], r1["grads"]):
         assert torch.equal(a, b)

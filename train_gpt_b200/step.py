@@ -410,7 +410,7 @@ class Trainer:
         direct = bool(cfg.direct_grads) and on_gpu and cfg.mm == "fp8"
         fused_qkv = cfg.qkv == "fused" and cfg.norm == "fused"
         side_by_side = direct and fused_qkv and self._fused_opt and cfg.flat_parameters
-        defer = bool(cfg.defer_exchange) and world_size > 1 and on_gpu
+        defer = bool(cfg.defer_exchange) and world_size > 1
         self.buckets = GradBuckets(self.model.buckets(qkv_side_by_side=side_by_side), world_size, defer=defer)
         if defer:
             self.model.exchange = self.buckets
