@@ -48,7 +48,7 @@ quantize_rowwise_kernel(const uint4* __restrict__ x, uint2* __restrict__ q,
 // each of the 16 half-warps owns every 16th row (8 rows per thread, kept in registers).
 // Column maxima are combined across the warps through shared memory (one thread per column
 // finishes the reduction and the reciprocal), then the same registers are divided and stored.
-// 80 registers: three blocks per SM, so one block's loads overlap the others' arithmetic.
+// 64 registers: four blocks per SM, so one block's loads overlap the others' arithmetic.
 // ---------------------------------------------------------------------------------------
 constexpr int kColPanelCols = 128;
 constexpr int kColThreads = 256;
@@ -286,9 +286,11 @@ __device__ __forceinline__ void colwise_panel(const __nv_bfloat16* __restrict__ 
 // half-warp spans exactly one row tile -- so a tensor that needs both forms (an upstream
 // gradient: row-wise for dgrad, column-wise for wgrad) is read from HBM once, not twice.
 template <bool WITH_ROWS, int ACT = TG_ACT_NONE>
-// (the GELU cotangent variant, the one with the most live values, runs 2 % faster with 128 registers and two blocks per SM
-// than with 80 and three, spilling; the GELU forward variant 5 % slower, the plain one 15 % slower)
-__global__ void __launch_bounds__(kColThreads, ACT == TG_ACT_GELU_BWD ? 2 : 3)
+// Blocks per SM: the plain variants fit 64 registers without a spill and run four (8-14 % faster than three: the
+// top stall is the wait for the panel's loads, and a fourth block is a third more of them in flight); the
+// activation variants take 80 registers and three; the GELU cotangent variant, the one with the most live
+// values, runs 2 % faster with 128 registers and two blocks than with 80 and three, spilling.
+__global__ void __launch_bounds__(kColThreads, ACT == TG_ACT_GELU_BWD ? 2 : (ACT == TG_ACT_NONE ? 4 : 3))
 quantize_colwise_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
                         float* __restrict__ scales, uint8_t* __restrict__ q_row,
                         float* __restrict__ s_row, int64_t rows, int64_t cols,
